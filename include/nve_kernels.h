@@ -1,0 +1,240 @@
+/*
+ * libnve_kernels.so -- C ABI of the B200 (sm_100a) quantized decode kernels for NVE.
+ *
+ * Part 1 re-declares, with identical names, argument order and meaning, every symbol the
+ * reference project exports from cuda/nve_kernels.cu and binds in src/cuda_kernels.rs:57-289.
+ * A library exporting these symbols is what the reference's build.rs:33-41 links when
+ * NVE_KERNELS_PREBUILT points at its directory.  Each declaration cites the reference
+ * definition it replaces (file:line in the reference project).
+ *
+ * Part 2 declares additive entry points (prefix nve_b200_) that the reference does not have:
+ * status reporting, bf16/f32 I/O, fused prologues/epilogues, the batched tensor-core GEMM,
+ * on-device weight preparation and tensor-parallel helpers.
+ *
+ * Conventions (same as the reference, src/cuda_kernels.rs:296-339):
+ *   - every pointer is a raw device address owned by the caller unless stated otherwise;
+ *   - 16-bit floats travel as uint16_t; int8 codes as int8_t; scales as float;
+ *   - every launcher enqueues on `stream` and returns; NULL is the legacy default stream;
+ *   - launchers allocate nothing and are legal inside stream capture;
+ *   - the reference-signature launchers return void and silently skip unsupported shapes,
+ *     as the reference does (cuda/nve_kernels.cu:582,1188); the reason is recorded and can be
+ *     read with nve_b200_last_status().
+ *
+ * Weight format (src/quantize.rs:437-463, cuda/nve_kernels.cu:330-361):
+ *   nibbles [N, K/2] u8 row-major, byte j of 32-wide block b = q[j] | q[j+16] << 4, q in [0,15],
+ *   weight value = (q - 8) * scales[n, b];  scales [N, K/32] f32;  K % 32 == 0.
+ */
+#ifndef NVE_KERNELS_H
+#define NVE_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported symbols (the library is built with hidden default visibility). */
+#if defined(__GNUC__)
+#define NVE_API __attribute__((visibility("default")))
+#else
+#define NVE_API
+#endif
+
+/* Opaque CUDA stream handle (cudaStream_t) so that C callers need no CUDA headers. */
+typedef void* nve_stream_t;
+
+/* ======================================================================================== */
+/* Part 1: the reference ABI                                                                */
+/* ======================================================================================== */
+
+/* cuda/nve_kernels.cu:63-76.  out = f16(x * rsqrt(mean(x^2)+eps) * w), n elements. */
+NVE_API void nve_rms_norm_f16(const uint16_t* x, const uint16_t* weight, uint16_t* out, int n, float eps,
+                      nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:120-134.  LayerNorm with optional bias (bias may be NULL). */
+NVE_API void nve_layer_norm_f16(const uint16_t* x, const uint16_t* weight, const uint16_t* bias, uint16_t* out, int n,
+                        float eps, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:182-200.  Half-split RoPE on q [nh,hd] and k [nkv,hd] in place; cos/sin [hd/2]. */
+NVE_API void nve_rope_f16_decode(uint16_t* q, uint16_t* k, const uint16_t* cos, const uint16_t* sin, int num_heads,
+                         int num_kv_heads, int head_dim, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:246-262.  RoPE for seq_len tokens; tables [max_seq, hd/2]; q [seq,nh,hd]. */
+NVE_API void nve_rope_f16_prefill(uint16_t* q, uint16_t* k, const uint16_t* cos, const uint16_t* sin, int seq_len,
+                          int num_heads, int num_kv_heads, int head_dim, int start_pos, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:1049-1065.  As nve_rope_f16_decode but the position is read from *d_pos and the
+ * full tables [max_seq, hd/2] are passed. */
+NVE_API void nve_rope_f16_decode_dyn(uint16_t* q, uint16_t* k, const uint16_t* cos_tab, const uint16_t* sin_tab,
+                             int num_heads, int num_kv_heads, int head_dim, const int* d_pos,
+                             nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:300-314.  Dense f16 GEMV out[N] = W[N,K] . x[K]. */
+NVE_API void nve_matvec_f16(const uint16_t* x, const uint16_t* W, uint16_t* out, int N, int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:373-388.  W4A16 GEMV: out[n] = f16(sum_k x[k] [*awq[k]] (q-8) scale[n,k/32]);
+ * awq may be NULL. */
+NVE_API void nve_matvec_w4a16(const uint16_t* x, const uint8_t* nibbles, const float* scales, const float* awq,
+                      uint16_t* out, int N, int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:420-433.  Full dequantisation W_f16[N,K] = (q-8)*scale [*awq[k]]. */
+NVE_API void nve_dequant_w4a16(const uint8_t* nibbles, const float* scales, const float* awq, uint16_t* out, int N,
+                       int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:680-700.  W4A16 GEMV over three matrices sharing x, one launch. */
+NVE_API void nve_qkv_matvec_w4a16(const uint16_t* x,
+                          const uint8_t* q_nibbles, const float* q_scales, const float* q_awq, int Nq,
+                          const uint8_t* k_nibbles, const float* k_scales, const float* k_awq, int Nk,
+                          const uint8_t* v_nibbles, const float* v_scales, const float* v_awq, int Nv,
+                          uint16_t* q_out, uint16_t* k_out, uint16_t* v_out, int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:747-757.  Per-group-32 absmax int8 quantisation of f16 activations:
+ * scale = amax > 0 ? amax/127 : 1 ; xq = clamp(rint(x / scale), -127, 127). */
+NVE_API void nve_quantize_f16_q8(const uint16_t* x, int8_t* xq, float* scales, int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:880-894.  W4A8 GEMV: out[n] = f16(sum_b wt_scales[n,b] * xq_scales[b] * I[n,b]),
+ * I[n,b] = sum_e (q-8) * xq[32b+e] (exact int32). */
+NVE_API void nve_matvec_w4a8(const int8_t* xq, const float* xq_scales, const uint8_t* nibbles, const float* wt_scales,
+                     uint16_t* out, int N, int K, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:574-591.  Single-query GQA attention; caches [nkv, seq_len, hd]; needs hd%32==0, hd<=512. */
+NVE_API void nve_flash_decode_f16(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out,
+                          int num_heads, int num_kv_heads, int seq_len, int head_dim, float scale,
+                          nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:1177-1197.  As above with the length in *d_seq_len and caches [nkv, max_seq_len, hd]. */
+NVE_API void nve_flash_decode_dyn(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out,
+                          int num_heads, int num_kv_heads, const int* d_seq_len, int head_dim, float scale,
+                          int max_seq_len, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:931-946.  cache[kvh, *d_pos, :] = new[kvh, :] for K and V. */
+NVE_API void nve_kv_cache_write_f16(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new, uint16_t* v_cache,
+                            const int* d_pos, int num_kv_heads, int head_dim, int max_seq_len,
+                            nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:963-969.  dst[i] = f16(f32(dst[i]) + f32(src[i])). */
+NVE_API void nve_add_inplace_f16(uint16_t* dst, const uint16_t* src, int n, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:989-995.  gate[i] = f16(silu(gate[i]) * up[i]). */
+NVE_API void nve_silu_mul_f16(uint16_t* gate, const uint16_t* up, int n, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:1203-1205.  Device-to-device async copy. */
+NVE_API void nve_d2d_copy(void* dst, const void* src, size_t bytes, nve_stream_t stream);
+
+/* cuda/nve_kernels.cu:1230-1299.  Process-global decode-graph manager: one capture stream, pinned
+ * pos/seq_len scalars copied to device scalars by the first two nodes of the graph. */
+NVE_API void nve_graph_init(void);
+NVE_API void nve_graph_begin_capture(void);
+NVE_API void nve_graph_end_capture(void);
+NVE_API void nve_graph_launch(int pos, int seq_len, nve_stream_t stream);
+NVE_API int nve_graph_ready(void);
+NVE_API void nve_graph_destroy(void);
+NVE_API const int* nve_graph_d_pos(void);
+NVE_API const int* nve_graph_d_seqlen(void);
+NVE_API nve_stream_t nve_graph_capture_stream(void);
+
+/* cuda/nve_kernels.cu:1306-1413.  Event-timed microbenchmark of the decode kernels; prints to stdout. */
+NVE_API void nve_run_microbench(int hidden, int intermediate, int num_heads, int num_kv_heads, int head_dim, int iters);
+
+/* ======================================================================================== */
+/* Part 2: additive entry points (no counterpart in the reference unless cited)             */
+/* ======================================================================================== */
+
+/* 16-bit / 32-bit element types accepted by the *_ex entry points. */
+#define NVE_DT_F16 0
+#define NVE_DT_BF16 1
+#define NVE_DT_F32 2
+
+/* Status codes.  Every nve_b200_* launcher returns one; 0 is success. */
+#define NVE_OK 0
+#define NVE_ERR_BAD_SHAPE 1      /* K % 32 != 0, non-positive sizes, unsupported head_dim ... */
+#define NVE_ERR_BAD_POINTER 2    /* NULL where data is required */
+#define NVE_ERR_BAD_ALIGNMENT 3  /* pointer not aligned for the kernel's vector accesses */
+#define NVE_ERR_BAD_DTYPE 4
+#define NVE_ERR_TOO_LARGE 5      /* exceeds a documented limit (shared memory, static scratch) */
+#define NVE_ERR_CUDA 6           /* a CUDA runtime call failed; see nve_b200_last_cuda_error() */
+#define NVE_ERR_TIMEOUT 7        /* a bounded device-side wait expired */
+
+/* Status of the most recent launcher call on this thread (reference-signature calls included). */
+NVE_API int nve_b200_last_status(void);
+/* cudaError_t (as int) recorded with the last NVE_ERR_CUDA. */
+NVE_API int nve_b200_last_cuda_error(void);
+/* Library build tag, e.g. "nve-b200 sm_100a". */
+NVE_API const char* nve_b200_version(void);
+/* Number of kernels this library has launched from this process (all threads). */
+NVE_API unsigned long long nve_b200_launch_count(void);
+/* Enable (1) / disable (0) programmatic dependent launch on the GEMV launches; returns the old value. */
+NVE_API int nve_b200_set_pdl(int enabled);
+
+/* Activation quantizer with selectable input type (NVE_DT_F16 or NVE_DT_BF16); arithmetic as
+ * nve_quantize_f16_q8 (cuda/nve_kernels.cu:712-745). */
+NVE_API int nve_b200_quantize_q8(const void* x, int8_t* xq, float* scales, int K, int x_dtype, nve_stream_t stream);
+
+/* Fused RMSNorm -> 16-bit round -> int8 quantisation (the two launches at src/gpu_layer.rs:1032-1038,658
+ * in one).  normed_out may be NULL when only the codes are needed. */
+NVE_API int nve_b200_rmsnorm_quantize_q8(const void* x, const void* weight, void* normed_out, int8_t* xq, float* scales,
+                                 int n, float eps, int dtype, nve_stream_t stream);
+
+/* RMSNorm with selectable 16-bit type (cuda/nve_kernels.cu:26-60 arithmetic, fixed summation order). */
+NVE_API int nve_b200_rms_norm(const void* x, const void* weight, void* out, int n, float eps, int dtype,
+                      nve_stream_t stream);
+
+/* Fused silu(gate)*up -> 16-bit round -> int8 quantisation (src/gpu_layer.rs:942-946 in one launch).
+ * mid_out may be NULL. */
+NVE_API int nve_b200_silu_mul_quantize_q8(const void* gate, const void* up, void* mid_out, int8_t* xq, float* scales,
+                                  int n, int dtype, nve_stream_t stream);
+
+/* silu(gate)*up and residual add with selectable 16-bit type. */
+NVE_API int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_stream_t stream);
+NVE_API int nve_b200_add_inplace(void* dst, const void* src, int n, int dtype, nve_stream_t stream);
+
+/* One matrix of a fused multi-matrix GEMV (all share the activation vector and K). */
+typedef struct {
+    const uint8_t* nibbles; /* [N, K/2]  */
+    const float* scales;    /* [N, K/32] */
+    void* out;              /* [N] of out_dtype */
+    const void* residual;   /* NULL, or [N] of out_dtype: out = residual + y (may alias out) */
+    int N;
+} nve_b200_w4_matrix;
+
+/* W4A8 GEMV over 1..3 matrices in one launch (q/k/v, or gate/up), selectable output type and optional
+ * fused residual add.  Arithmetic as nve_matvec_w4a8 (cuda/nve_kernels.cu:796-878). */
+NVE_API int nve_b200_matvec_w4a8_multi(const int8_t* xq, const float* xq_scales, const nve_b200_w4_matrix* mats,
+                               int num_mats, int K, int out_dtype, nve_stream_t stream);
+
+/* W4A16 GEMV over 1..3 matrices in one launch; x of x_dtype (f16/bf16), awq may be NULL (shared by all
+ * matrices of the call).  Arithmetic as nve_matvec_w4a16 (cuda/nve_kernels.cu:349-370). */
+NVE_API int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mats,
+                                int num_mats, int K, int out_dtype, nve_stream_t stream);
+
+/* Exact per-block integer dot products I[N, K/32] (int32) of the W4A8 GEMV, for bit-level checks. */
+NVE_API int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int32_t* I, int N, int K, nve_stream_t stream);
+
+/* Dequantisation with selectable 16-bit output type (cuda/nve_kernels.cu:397-433 arithmetic). */
+NVE_API int nve_b200_dequant_w4a16(const uint8_t* nibbles, const float* scales, const float* awq, void* out, int N,
+                           int K, int out_dtype, nve_stream_t stream);
+
+/* On-device weight preparation, bit-identical to src/quantize.rs:711-731 (quantize_block_q4) followed by
+ * src/quantize.rs:437-463 (extract_for_gpu): W [N,K] f32 row-major -> nibbles, scales.  awq_scales
+ * (may be NULL) multiplies each column before quantisation as src/quantize.rs:283-286 does. */
+NVE_API int nve_b200_q4_quantize(const float* W, const float* awq_scales, uint8_t* nibbles, float* scales, int N, int K,
+                         nve_stream_t stream);
+
+/* Repack reference CPU blocks (20 bytes: f32 scale + 16 bytes of {2i, 2i+1} pairs) already copied to the
+ * device into the device layout (src/quantize.rs:437-463). */
+NVE_API int nve_b200_q4_repack_blocks(const uint8_t* cpu_blocks, uint8_t* nibbles, float* scales, int N, int K,
+                              nve_stream_t stream);
+
+/* Counter-based synthetic generator: out[i] = normal(seed, stream_id, first+i) * scale (f32), the same
+ * integer recipe as the test oracle so host and device inputs agree bit for bit. */
+NVE_API int nve_b200_fill_normal(float* out, long long n, unsigned long long seed, unsigned long long stream_id,
+                         unsigned long long first, float scale, nve_stream_t stream);
+/* Same values rounded to a 16-bit type. */
+NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long seed, unsigned long long stream_id,
+                            unsigned long long first, float scale, int dtype, nve_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVE_KERNELS_H */

@@ -1,0 +1,244 @@
+"""Decode-layer call site: per-layer W4A8 / W4A16 routing and the order of kernel calls.
+
+Mirrors the reference's src/gpu_layer.rs for the quantized decode path only: `GpuW4` (:199-205),
+`GpuLayerWeights`, the routing predicate of `gpu_layer_forward_decode` (:1005-1025), the attention
+sub-layer `gpu_attn_decode` (:633-775) and the SwiGLU FFN `gpu_ffn` (:914-997).  Everything else in that
+file (F16 / dequantised weights, prefill, non-Llama FFN types, biases) is outside this package.
+
+Two schedules compute the same thing:
+  * ``fused=False`` issues exactly the reference's sequence of kernels (one launch per reference call);
+  * ``fused=True`` uses the fused entry points (RMSNorm->quantise, q/k/v and gate/up in one launch,
+    SiLU*up->quantise, residual add in the GEMV epilogue).  Both give bit-identical hidden states.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import cuda_kernels as ck
+
+Tensor = torch.Tensor
+
+
+@dataclass
+class GpuW4:
+    """src/gpu_layer.rs:199-205: packed nibbles [n, k/2] u8, scales [n, k/32] f32, optional awq [k] f32."""
+
+    nibbles: Tensor
+    scales: Tensor
+    awq_scales: Optional[Tensor]
+    n: int
+    k: int
+
+    def triple(self):
+        return (self.nibbles, self.scales, self.n)
+
+
+@dataclass
+class GpuLayerWeights:
+    """The W4 subset of src/gpu_layer.rs GpuLayerWeights (Llama-style block, no biases)."""
+
+    q_proj: GpuW4
+    k_proj: GpuW4
+    v_proj: GpuW4
+    o_proj: GpuW4
+    gate_proj: GpuW4
+    up_proj: GpuW4
+    down_proj: GpuW4
+    input_norm: Tensor
+    post_attn_norm: Tensor
+
+
+@dataclass
+class RoutingConfig:
+    """Precision routing inputs of src/gpu_layer.rs:1017-1025, read once instead of per call."""
+
+    no_w4a8: bool = False
+    threshold: float = 0.7
+
+    @staticmethod
+    def from_env(env=os.environ) -> "RoutingConfig":
+        no = "NVE_NO_W4A8" in env
+        try:
+            thr = float(env.get("NVE_W4A8_THRESHOLD", "0.7"))
+        except ValueError:
+            thr = 0.7  # the reference falls back to the default when the value does not parse
+        return RoutingConfig(no, thr)
+
+    def use_w4a8(self, layer_importance: float) -> bool:
+        """use_w4a8 = !NVE_NO_W4A8 && importance < threshold (strict)."""
+        if self.no_w4a8:
+            return False
+        return layer_importance < self.threshold
+
+
+def normalize_importance(scores: Sequence[float]) -> List[float]:
+    """src/main.rs:891-898: min-max normalisation to [0,1]; all 0.5 when the range is <= 1e-9."""
+    mn, mx = min(scores), max(scores)
+    rng = mx - mn
+    if rng > 1e-9:
+        return [(s - mn) / rng for s in scores]
+    return [0.5] * len(scores)
+
+
+class GpuKvCache:
+    """Static per-layer K/V buffers [nkv, max_seq, hd] (the layout of src/decode_graph.rs:183-184).
+
+    The reference's eager path grows its cache with Tensor::cat on every token (src/gpu_layer.rs:468-483);
+    here both the eager and the captured path write into pre-allocated buffers.
+    """
+
+    def __init__(self, num_layers: int, num_kv_heads: int, max_seq: int, head_dim: int, device, dtype=torch.float16):
+        self.max_seq = max_seq
+        self.k = [torch.zeros((num_kv_heads, max_seq, head_dim), dtype=dtype, device=device) for _ in range(num_layers)]
+        self.v = [torch.zeros((num_kv_heads, max_seq, head_dim), dtype=dtype, device=device) for _ in range(num_layers)]
+
+    def reset(self) -> None:
+        pass  # positions are overwritten; the valid length travels with every call
+
+
+@dataclass
+class GpuInferenceState:
+    """The fields of src/gpu_layer.rs GpuInferenceState that the quantized decode path reads."""
+
+    layer_weights: List[GpuLayerWeights]
+    kv_cache: GpuKvCache
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    norm_eps: float
+    rope_cos: Tensor  # [max_seq, hd/2] f16
+    rope_sin: Tensor
+    routing: RoutingConfig = field(default_factory=RoutingConfig)
+    fused: bool = True
+    # device scalars for position / valid length of the eager path
+    d_pos: Optional[Tensor] = None
+    d_seqlen: Optional[Tensor] = None
+
+    def set_position(self, pos: int) -> None:
+        if self.d_pos is None:
+            dev = self.rope_cos.device
+            self.d_pos = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.d_seqlen = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.d_pos.fill_(pos)
+        self.d_seqlen.fill_(min(pos + 1, self.kv_cache.max_seq))
+
+
+def gpu_attn_decode(normed_or_q8, w: GpuLayerWeights, state: GpuInferenceState, layer_idx: int, d_pos: int,
+                    d_seqlen: int, use_w4a8: bool, residual: Optional[Tensor] = None) -> Tensor:
+    """src/gpu_layer.rs:633-743 for W4 weights.  `normed_or_q8` is the normed f16 activations (W4A16 route,
+    or W4A8 unfused) or an (xq, scales) pair already quantised by the fused prologue.  Returns the o_proj
+    output [1, hidden]; with `residual` the residual add is fused into the o_proj epilogue."""
+    nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+    fused = state.fused
+    if use_w4a8:
+        if isinstance(normed_or_q8, tuple):
+            xq, xs = normed_or_q8
+        else:
+            xq, xs = ck.quantize_f16_q8(normed_or_q8)  # :658
+        if fused:
+            q, k, v = ck.matvec_w4a8_multi(xq, xs, [w.q_proj.triple(), w.k_proj.triple(), w.v_proj.triple()], w.q_proj.k)
+        else:  # :659-661
+            q = ck.matvec_w4a8(xq, xs, w.q_proj.nibbles, w.q_proj.scales, w.q_proj.n, w.q_proj.k)
+            k = ck.matvec_w4a8(xq, xs, w.k_proj.nibbles, w.k_proj.scales, w.k_proj.n, w.k_proj.k)
+            v = ck.matvec_w4a8(xq, xs, w.v_proj.nibbles, w.v_proj.scales, w.v_proj.n, w.v_proj.k)
+    else:  # :665-672
+        q, k, v = ck.fused_qkv_matvec_w4a16(
+            normed_or_q8,
+            w.q_proj.nibbles, w.q_proj.scales, w.q_proj.awq_scales, w.q_proj.n,
+            w.k_proj.nibbles, w.k_proj.scales, w.k_proj.awq_scales, w.k_proj.n,
+            w.v_proj.nibbles, w.v_proj.scales, w.v_proj.awq_scales, w.v_proj.n,
+            w.q_proj.k)
+    q = q.view(nh, hd)
+    k = k.view(nkv, hd)
+    v = v.view(nkv, hd)
+    ck.rope_decode_dyn_inplace(q, k, state.rope_cos, state.rope_sin, nh, nkv, hd, d_pos)  # :697-711
+    kc, vc = state.kv_cache.k[layer_idx], state.kv_cache.v[layer_idx]
+    ck.kv_cache_write(k, kc, v, vc, d_pos, nkv, hd, state.kv_cache.max_seq)  # :714
+    attn = torch.empty((nh, hd), dtype=torch.float16, device=q.device)
+    ck.flash_decode_dyn_into(q, kc, vc, attn, nh, nkv, d_seqlen, hd, float(hd) ** -0.5, state.kv_cache.max_seq)  # :723
+    attn = attn.view(1, nh * hd)
+    wo = w.o_proj
+    if use_w4a8:  # :737-741
+        xq2, xs2 = ck.quantize_f16_q8(attn)
+        if fused and residual is not None:
+            return ck.matvec_w4a8_multi(xq2, xs2, [wo.triple()], wo.k, residuals=[residual])[0]
+        out = ck.matvec_w4a8(xq2, xs2, wo.nibbles, wo.scales, wo.n, wo.k)
+    else:  # :743 -> matmul_x -> fused_matvec_w4a16
+        if fused and residual is not None:
+            return ck.matvec_w4a16_multi(attn, wo.awq_scales, [wo.triple()], wo.k, residuals=[residual])[0]
+        out = ck.fused_matvec_w4a16(attn, wo.nibbles, wo.scales, wo.awq_scales, wo.n, wo.k)
+    if residual is not None:
+        tmp = residual.clone()
+        ck.add_inplace(tmp, out)  # :1073
+        return tmp
+    return out
+
+
+def gpu_ffn(normed_or_q8, w: GpuLayerWeights, state: GpuInferenceState, use_w4a8: bool,
+            residual: Optional[Tensor] = None) -> Tensor:
+    """src/gpu_layer.rs:914-996 for SwiGLU with W4 weights at batch 1."""
+    fused = state.fused
+    wg, wu, wd = w.gate_proj, w.up_proj, w.down_proj
+    if use_w4a8:  # :937-947
+        if isinstance(normed_or_q8, tuple):
+            xq, xs = normed_or_q8
+        else:
+            xq, xs = ck.quantize_f16_q8(normed_or_q8)
+        if fused:
+            gate, up = ck.matvec_w4a8_multi(xq, xs, [wg.triple(), wu.triple()], wg.k)
+            xq2, xs2, _ = ck.silu_mul_quantize_q8(gate, up)
+            if residual is not None:
+                return ck.matvec_w4a8_multi(xq2, xs2, [wd.triple()], wd.k, residuals=[residual])[0]
+            return ck.matvec_w4a8(xq2, xs2, wd.nibbles, wd.scales, wd.n, wd.k)
+        gate = ck.matvec_w4a8(xq, xs, wg.nibbles, wg.scales, wg.n, wg.k)
+        up = ck.matvec_w4a8(xq, xs, wu.nibbles, wu.scales, wu.n, wu.k)
+        ck.silu_mul_inplace(gate, up)
+        xq2, xs2 = ck.quantize_f16_q8(gate)
+        out = ck.matvec_w4a8(xq2, xs2, wd.nibbles, wd.scales, wd.n, wd.k)
+    else:  # :977-981
+        x = normed_or_q8
+        same_awq = (wg.awq_scales is None and wu.awq_scales is None)
+        if fused and same_awq:
+            gate, up = ck.matvec_w4a16_multi(x, None, [wg.triple(), wu.triple()], wg.k)
+        else:
+            gate = ck.fused_matvec_w4a16(x, wg.nibbles, wg.scales, wg.awq_scales, wg.n, wg.k)
+            up = ck.fused_matvec_w4a16(x, wu.nibbles, wu.scales, wu.awq_scales, wu.n, wu.k)
+        ck.silu_mul_inplace(gate, up)
+        if fused and residual is not None:
+            return ck.matvec_w4a16_multi(gate, wd.awq_scales, [wd.triple()], wd.k, residuals=[residual])[0]
+        out = ck.fused_matvec_w4a16(gate, wd.nibbles, wd.scales, wd.awq_scales, wd.n, wd.k)
+    if residual is not None:
+        tmp = residual.clone()
+        ck.add_inplace(tmp, out)  # :1082
+        return tmp
+    return out
+
+
+def gpu_layer_forward_decode(hidden: Tensor, layer_idx: int, state: GpuInferenceState, pos: int,
+                             parallel_attn_ffn: bool = False, layer_importance: float = 0.0,
+                             d_pos: Optional[int] = None, d_seqlen: Optional[int] = None) -> Tensor:
+    """src/gpu_layer.rs:1005-1084: one token through one layer.  hidden [1, hidden] f16 -> same shape.
+
+    `d_pos` / `d_seqlen` are device addresses of the position and valid-length scalars; when omitted the
+    state's own scalars are set from `pos` (eager use)."""
+    if parallel_attn_ffn:
+        raise NotImplementedError("parallel attention+FFN blocks are outside the quantized Llama decode path")
+    use_w4a8 = state.routing.use_w4a8(layer_importance)
+    w = state.layer_weights[layer_idx]
+    if d_pos is None:
+        state.set_position(pos)
+        d_pos, d_seqlen = state.d_pos.data_ptr(), state.d_seqlen.data_ptr()
+    eps = state.norm_eps
+    if state.fused and use_w4a8:
+        xq, xs, _ = ck.rmsnorm_quantize_q8(hidden, w.input_norm, eps)
+        h = gpu_attn_decode((xq, xs), w, state, layer_idx, d_pos, d_seqlen, True, residual=hidden)
+        xq, xs, _ = ck.rmsnorm_quantize_q8(h, w.post_attn_norm, eps)
+        return gpu_ffn((xq, xs), w, state, True, residual=h)
+    normed = ck.fused_rms_norm(hidden, w.input_norm, eps)  # :1032-1038
+    h = gpu_attn_decode(normed, w, state, layer_idx, d_pos, d_seqlen, use_w4a8, residual=hidden)
+    normed2 = ck.fused_rms_norm(h, w.post_attn_norm, eps)  # :1074-1080
+    return gpu_ffn(normed2, w, state, use_w4a8, residual=h)

@@ -227,6 +227,42 @@ def w4a8_matvec_reforder(xq, xs, nibbles, wsc) -> np.ndarray:
     return y
 
 
+def w4a8_matvec_b200(xq, xs, nibbles, wsc) -> np.ndarray:
+    """orc_w4a8_matvec_b200: f32 result in the CUDA library's own summation order (bit-level check)."""
+    xq = _c(xq, np.int8)
+    xs = _c(xs, np.float32)
+    nibbles = _c(nibbles, np.uint8)
+    wsc = _c(wsc, np.float32)
+    N = nibbles.shape[0]
+    y = np.empty(N, np.float32)
+    lib().orc_w4a8_matvec_b200(_p(xq), _p(xs), _p(nibbles), _p(wsc), _l(N), _l(xq.size), _p(y))
+    return y
+
+
+def x16_fixedpoint(x16, bf16: bool = False, awq=None):
+    """orc_x16_fixedpoint: the library's 16-bit fixed-point activation codes (int32 [K]) and scales."""
+    x16 = _c(x16, np.uint16)
+    K = x16.size
+    a = _c(awq, np.float32) if awq is not None else None
+    v = np.empty(K, np.int32)
+    sc = np.empty(K // 32, np.float32)
+    lib().orc_x16_fixedpoint(_p(x16), _l(K), C.c_int(int(bf16)), _p(a) if a is not None else None, _p(v), _p(sc))
+    return v, sc
+
+
+def w4a16_matvec_b200(x16, nibbles, wsc, awq=None, bf16: bool = False) -> np.ndarray:
+    """orc_w4a16_matvec_b200: f32 result exactly as the CUDA library computes it."""
+    x16 = _c(x16, np.uint16)
+    nibbles = _c(nibbles, np.uint8)
+    wsc = _c(wsc, np.float32)
+    a = _c(awq, np.float32) if awq is not None else None
+    N = nibbles.shape[0]
+    y = np.empty(N, np.float32)
+    lib().orc_w4a16_matvec_b200(_p(x16), C.c_int(int(bf16)), _p(a) if a is not None else None, _p(nibbles), _p(wsc),
+                                _l(N), _l(x16.size), _p(y))
+    return y
+
+
 def w4a8_matvec_mt(xq, xs, nibbles, wsc) -> np.ndarray:
     xq = _c(xq, np.int8)
     xs = _c(xs, np.float32)

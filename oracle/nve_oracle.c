@@ -607,6 +607,100 @@ void orc_w4a8_matvec_mt(const int8_t* xq, const float* xs, const uint8_t* nibble
 }
 
 /* ------------------------------------------------------------------------- */
+/* Restatement of the CUDA library's own f32 summation order (bit-level checks) */
+/* ------------------------------------------------------------------------- */
+
+/* The library adds the 32 lane values of one (row, 32-block column set) with a xor butterfly
+ * (pairs l^16, then ^8, ^4, ^2, ^1) and then adds the column-set partials in ascending order. */
+static float lane_tree32(const float* v) {
+    float a[32];
+    memcpy(a, v, sizeof(a));
+    for (int m = 16; m > 0; m >>= 1)
+        for (int l = 0; l < m; l++) a[l] = a[l] + a[l + m];
+    return a[0];
+}
+
+/* W4A8 GEMV with the library's order: v = (wsc*xs) * (float)I per block (two roundings), lane tree per
+ * column set, ascending sum over column sets.  The integer part is cuda/nve_kernels.cu:817-862. */
+void orc_w4a8_matvec_b200(const int8_t* xq, const float* xs, const uint8_t* nibbles, const float* wsc, long N, long K,
+                          float* y) {
+    long nb = K / Q4_BLOCK;
+    long S = (nb + 31) / 32;
+    for (long n = 0; n < N; n++) {
+        float tot = 0.0f;
+        for (long s = 0; s < S; s++) {
+            float v[32];
+            for (int l = 0; l < 32; l++) {
+                long b = s * 32 + l;
+                v[l] = 0.0f;
+                if (b < nb) {
+                    int32_t I = 0;
+                    for (int e = 0; e < Q4_BLOCK; e++) I += gpu_q(nibbles, n, nb, b, e) * (int32_t)xq[b * Q4_BLOCK + e];
+                    v[l] = (wsc[n * nb + b] * xs[b]) * (float)I;
+                }
+            }
+            float part = lane_tree32(v);
+            tot = (s == 0) ? part : tot + part;
+        }
+        y[n] = tot;
+    }
+}
+
+/* The library's W4A16 activation staging: per 32-wide block a 16-bit fixed-point code
+ *   xe = f32(x) [* awq] ; amax = max|xe| ; scale = amax > 0 ? amax/32767 : 1 ; v = clamp(rint(xe * (1/scale)), +-32767). */
+void orc_x16_fixedpoint(const uint16_t* x16, long K, int is_bf16, const float* awq, int32_t* v, float* scales) {
+    for (long g = 0; g < K / 32; g++) {
+        float xe[32];
+        float amax = 0.0f;
+        for (int e = 0; e < 32; e++) {
+            xe[e] = act16_to_f32(x16[g * 32 + e], is_bf16);
+            if (awq) xe[e] = xe[e] * awq[g * 32 + e];
+            amax = fmaxf(amax, fabsf(xe[e]));
+        }
+        float scale = amax > 0.0f ? amax / 32767.0f : 1.0f;
+        float inv = 1.0f / scale;
+        scales[g] = scale;
+        for (int e = 0; e < 32; e++) {
+            long q = lrintf(xe[e] * inv);
+            if (q < -32767) q = -32767;
+            if (q > 32767) q = 32767;
+            v[g * 32 + e] = (int32_t)q;
+        }
+    }
+}
+
+/* W4A16 GEMV as the library computes it: integer dot of (q-8) with the fixed-point codes, then the same
+ * scaling and summation order as orc_w4a8_matvec_b200. */
+void orc_w4a16_matvec_b200(const uint16_t* x16, int is_bf16, const float* awq, const uint8_t* nibbles,
+                           const float* wsc, long N, long K, float* y) {
+    long nb = K / Q4_BLOCK;
+    long S = (nb + 31) / 32;
+    int32_t* v16 = (int32_t*)malloc(sizeof(int32_t) * (size_t)K);
+    float* xs = (float*)malloc(sizeof(float) * (size_t)nb);
+    orc_x16_fixedpoint(x16, K, is_bf16, awq, v16, xs);
+    for (long n = 0; n < N; n++) {
+        float tot = 0.0f;
+        for (long s = 0; s < S; s++) {
+            float v[32];
+            for (int l = 0; l < 32; l++) {
+                long b = s * 32 + l;
+                v[l] = 0.0f;
+                if (b < nb) {
+                    int64_t I = 0;
+                    for (int e = 0; e < Q4_BLOCK; e++) I += (int64_t)gpu_q(nibbles, n, nb, b, e) * v16[b * Q4_BLOCK + e];
+                    v[l] = (wsc[n * nb + b] * xs[b]) * (float)(int32_t)I;
+                }
+            }
+            float part = lane_tree32(v);
+            tot = (s == 0) ? part : tot + part;
+        }
+        y[n] = tot;
+    }
+    free(v16);
+    free(xs);
+}
+
+/* ------------------------------------------------------------------------- */
 /* Decode glue (norm, activation, RoPE, attention)                            */
 /* ------------------------------------------------------------------------- */
 
@@ -618,19 +712,23 @@ void orc_rms_norm_f64(const float* x, const float* w, long n, double eps, float*
     for (long i = 0; i < n; i++) out[i] = (float)((double)x[i] * inv * (double)w[i]);
 }
 
-/* cuda/nve_kernels.cu:26-60 with a fixed f32 summation order, the order the CUDA library uses for its
- * norm kernels so that the 16-bit result can be compared bit for bit:
- *   256 partial sums p[t] = sum over i = t, t+256, ... of x[i]^2 (fma chain, ascending i);
+/* cuda/nve_kernels.cu:26-60 with a fixed f32 summation order -- the order the CUDA library under test
+ * uses for its norm kernels, restated here so that the 16-bit result can be compared bit for bit:
+ *   256 threads; thread t adds x[i]^2 (fma chain, ascending i) over the 8-element chunks t, t+256, ...;
  *   per 32-lane group a xor butterfly 16,8,4,2,1; the 8 group sums are added in ascending order;
  *   r = 1 / sqrt(sum / n + eps) with IEEE sqrt and divide;
  *   out[i] = round16((x[i] * r) * w[i]). */
 void orc_rms_norm_16(const uint16_t* x16, const uint16_t* w16, long n, float eps, int is_bf16, uint16_t* out16) {
     float p[256];
+    long chunks = (n + 7) / 8;
     for (int t = 0; t < 256; t++) {
         float a = 0.0f;
-        for (long i = t; i < n; i += 256) {
-            float v = act16_to_f32(x16[i], is_bf16);
-            a = fmaf(v, v, a);
+        for (long c = t; c < chunks; c += 256) {
+            for (int e = 0; e < 8; e++) {
+                long i = c * 8 + e;
+                float v = i < n ? act16_to_f32(x16[i], is_bf16) : 0.0f;
+                a = fmaf(v, v, a);
+            }
         }
         p[t] = a;
     }
@@ -643,7 +741,7 @@ void orc_rms_norm_16(const uint16_t* x16, const uint16_t* w16, long n, float eps
             for (int l = 0; l < 32; l++) nxt[l] = lane[l] + lane[l ^ m];
             memcpy(lane, nxt, sizeof(lane));
         }
-        total += lane[0];
+        total = (w == 0) ? lane[0] : total + lane[0];
     }
     float r = 1.0f / sqrtf(total / (float)n + eps);
     for (long i = 0; i < n; i++) {

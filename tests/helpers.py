@@ -1,0 +1,23 @@
+"""Small helpers shared by the GPU parity tests."""
+import numpy as np
+import torch
+
+
+def dev(a: np.ndarray, dtype=None) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.view(dtype)
+
+
+def f16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def rel_rms_err(y, ref) -> float:
+    """max |y - ref| / RMS(ref): the tolerance form stated for W4A16 and scaled outputs."""
+    y = np.asarray(y, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    rms = np.sqrt(np.mean(ref * ref))
+    return float(np.max(np.abs(y - ref)) / max(rms, 1e-30))
+
+
+TOL = 1e-2  # max-abs <= 1e-2 * RMS(reference output), fp32 accumulation

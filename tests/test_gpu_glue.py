@@ -1,0 +1,282 @@
+"""GPU parity tests for the activation-side and attention-side kernels, the decode layer and the graph."""
+import numpy as np
+import pytest
+
+from helpers import TOL, dev, f16_bits, rel_rms_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [32, 64, 2048, 4096, 8192, 14336])
+@pytest.mark.parametrize("bf", [False, True])
+def test_rms_norm_bit_exact_and_fused_quantize(cuda, orc, n, bf):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    dt = torch.bfloat16 if bf else torch.float16
+    x16 = orc.to_act16(orc.fill_normal(n, 21, n) * 1.7, bf)
+    w16 = orc.to_act16(1.0 + 0.1 * orc.fill_normal(n, 22, n), bf)
+    exp = orc.rms_norm_16(x16, w16, 1e-5, bf)
+    dx, dw = dev(x16, dt), dev(w16, dt)
+    out = ck.rms_norm(dx, dw, 1e-5)
+    assert np.array_equal(f16_bits(out), exp)
+    # against the reference CPU form (f64 accumulation): one 16-bit rounding apart
+    ref = orc.rms_norm_f64(orc.from_act16(x16, bf), orc.from_act16(w16, bf), 1e-5)
+    assert rel_rms_err(out.float().cpu().numpy(), ref) < (2e-2 if bf else 3e-3)
+    # fused RMSNorm -> quantise == the two launches of the reference call site
+    xq, xs, normed = ck.rmsnorm_quantize_q8(dx, dw, 1e-5, want_normed=True)
+    eq, es = orc.quantize_q8(exp, bf)
+    assert np.array_equal(f16_bits(normed), exp)
+    assert np.array_equal(xq.cpu().numpy(), eq) and np.array_equal(xs.cpu().numpy().view(np.uint32), es.view(np.uint32))
+    if not bf:
+        out2 = ck.fused_rms_norm(dx, dw, 1e-5)  # reference-signature entry point
+        assert torch.equal(out2, out)
+
+
+def test_rms_norm_ragged_length(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    n = 1000 + 3
+    x16 = orc.to_act16(orc.fill_normal(n, 23, 1))
+    w16 = orc.to_act16(np.ones(n, np.float32))
+    out = ck.fused_rms_norm(dev(x16, torch.float16), dev(w16, torch.float16), 1e-5)
+    assert np.array_equal(f16_bits(out), orc.rms_norm_16(x16, w16, 1e-5))
+
+
+@pytest.mark.parametrize("n", [64, 8192, 14336])
+def test_silu_mul_and_fused_quantize(cuda, orc, n):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    g16 = orc.to_act16(orc.fill_normal(n, 31, 1) * 2.0)
+    u16 = orc.to_act16(orc.fill_normal(n, 31, 2))
+    exp = orc.from_act16(orc.silu_mul_16(g16, u16))
+    gate = dev(g16, torch.float16)
+    up = dev(u16, torch.float16)
+    got = gate.clone()
+    ck.silu_mul_inplace(got, up)
+    # expf differs in the last place between host and device libm: allow one f16 ulp of the result
+    gotf = got.float().cpu().numpy()
+    assert np.all(np.abs(gotf - exp) <= np.maximum(np.abs(exp) * 2.0**-10, 2.0**-24))
+    assert np.mean(f16_bits(got) == orc.to_act16(exp)) > 0.99
+    # fused silu*up -> quantise == silu_mul then quantize on the same device values
+    xq, xs, mid = ck.silu_mul_quantize_q8(gate, up, want_mid=True)
+    assert torch.equal(mid, got)
+    eq, es = orc.quantize_q8(f16_bits(got))
+    assert np.array_equal(xq.cpu().numpy(), eq) and np.array_equal(xs.cpu().numpy().view(np.uint32), es.view(np.uint32))
+
+
+def test_add_inplace_and_layer_norm(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    n = 4096
+    a16, b16 = orc.to_act16(orc.fill_normal(n, 41, 1)), orc.to_act16(orc.fill_normal(n, 41, 2))
+    a = dev(a16, torch.float16)
+    ck.add_inplace(a, dev(b16, torch.float16))
+    assert np.array_equal(f16_bits(a), orc.to_act16(orc.from_act16(a16) + orc.from_act16(b16)))
+    x = orc.from_act16(a16).astype(np.float64)
+    w = orc.from_act16(b16).astype(np.float64)
+    ln = (x - x.mean()) / np.sqrt(x.var() + 1e-5) * w + 0.25
+    bias = torch.full((n,), 0.25, dtype=torch.float16, device="cuda")
+    out = ck.fused_layer_norm(dev(a16, torch.float16), dev(b16, torch.float16), bias, 1e-5)
+    assert rel_rms_err(out.float().cpu().numpy(), ln) < 5e-3
+
+
+def _rope_tables(orc, torch, hd, max_seq, theta=10000.0):
+    cos, sin = orc.rope_tables_f32(hd, max_seq, theta)
+    c16, s16 = orc.to_act16(cos), orc.to_act16(sin)
+    return c16, s16, dev(c16, torch.float16), dev(s16, torch.float16)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 8, 64), (32, 8, 128), (64, 8, 128)])
+def test_rope_variants_bit_exact(cuda, orc, nh, nkv, hd):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    max_seq, pos = 64, 37
+    c16, s16, dc, ds = _rope_tables(orc, torch, hd, max_seq)
+    q16 = orc.to_act16(orc.fill_normal(nh * hd, 51, 1))
+    k16 = orc.to_act16(orc.fill_normal(nkv * hd, 51, 2))
+    cr, sr = orc.from_act16(c16[pos]), orc.from_act16(s16[pos])
+    eq = orc.to_act16(orc.rope_apply(orc.from_act16(q16), nh, hd, cr, sr))
+    ek = orc.to_act16(orc.rope_apply(orc.from_act16(k16), nkv, hd, cr, sr))
+    q, k = dev(q16, torch.float16).view(nh, hd), dev(k16, torch.float16).view(nkv, hd)
+    ck.fused_rope_decode(q, k, dc[pos].contiguous(), ds[pos].contiguous(), nh, nkv, hd)
+    assert np.array_equal(f16_bits(q), eq) and np.array_equal(f16_bits(k), ek)
+    q2, k2 = dev(q16, torch.float16).view(nh, hd), dev(k16, torch.float16).view(nkv, hd)
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    ck.rope_decode_dyn_inplace(q2, k2, dc, ds, nh, nkv, hd, d_pos.data_ptr())
+    assert torch.equal(q2, q) and torch.equal(k2, k)
+    # prefill: 3 tokens starting at position 5
+    T, start = 3, 5
+    qp16 = orc.to_act16(orc.fill_normal(T * nh * hd, 52, 1))
+    kp16 = orc.to_act16(orc.fill_normal(T * nkv * hd, 52, 2))
+    qp, kp = dev(qp16, torch.float16).view(T, nh, hd), dev(kp16, torch.float16).view(T, nkv, hd)
+    ck.fused_rope_prefill(qp, kp, dc, ds, T, nh, nkv, hd, start)
+    for t in range(T):
+        cr, sr = orc.from_act16(c16[start + t]), orc.from_act16(s16[start + t])
+        e = orc.to_act16(orc.rope_apply(orc.from_act16(qp16.reshape(T, -1)[t]), nh, hd, cr, sr))
+        assert np.array_equal(f16_bits(qp[t]), e)
+        e = orc.to_act16(orc.rope_apply(orc.from_act16(kp16.reshape(T, -1)[t]), nkv, hd, cr, sr))
+        assert np.array_equal(f16_bits(kp[t]), e)
+
+
+def test_kv_cache_write(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    nkv, hd, max_seq, pos = 8, 128, 32, 17
+    kc = torch.zeros((nkv, max_seq, hd), dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    kn = dev(orc.to_act16(orc.fill_normal(nkv * hd, 61, 1)), torch.float16).view(nkv, hd)
+    vn = dev(orc.to_act16(orc.fill_normal(nkv * hd, 61, 2)), torch.float16).view(nkv, hd)
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    ck.kv_cache_write(kn, kc, vn, vc, d_pos.data_ptr(), nkv, hd, max_seq)
+    assert torch.equal(kc[:, pos], kn) and torch.equal(vc[:, pos], vn)
+    assert torch.count_nonzero(kc) == torch.count_nonzero(kn)
+    # an out-of-range position is skipped, never written out of bounds
+    d_pos.fill_(max_seq)
+    before = kc.clone()
+    ck.kv_cache_write(kn, kc, vn, vc, d_pos.data_ptr(), nkv, hd, max_seq)
+    assert torch.equal(kc, before)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,seq", [(32, 8, 64, 1), (32, 8, 64, 77), (32, 8, 128, 1024), (64, 8, 128, 300),
+                                           (4, 4, 256, 33), (2, 1, 512, 19), (8, 8, 32, 5)])
+def test_flash_decode(cuda, orc, nh, nkv, hd, seq):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    q16 = orc.to_act16(orc.fill_normal(nh * hd, 71, 1))
+    k16 = orc.to_act16(orc.fill_normal(nkv * seq * hd, 71, 2))
+    v16 = orc.to_act16(orc.fill_normal(nkv * seq * hd, 71, 3))
+    scale = hd ** -0.5
+    ref = orc.attn_decode(orc.from_act16(q16).reshape(nh, hd), orc.from_act16(k16).reshape(nkv, seq, hd),
+                          orc.from_act16(v16).reshape(nkv, seq, hd), seq, scale)
+    q = dev(q16, torch.float16).view(nh, hd)
+    kc = dev(k16, torch.float16).view(nkv, seq, hd)
+    vc = dev(v16, torch.float16).view(nkv, seq, hd)
+    out = ck.flash_decode_f16(q, kc, vc, nh, nkv, scale)
+    assert rel_rms_err(out.float().cpu().numpy(), ref) < 5e-3
+    # device-length form over a larger static cache
+    max_seq = seq + 13
+    kbig = torch.zeros((nkv, max_seq, hd), dtype=torch.float16, device="cuda")
+    vbig = torch.zeros_like(kbig)
+    kbig[:, :seq] = kc
+    vbig[:, :seq] = vc
+    kbig[:, seq:] = 100.0  # must not be read
+    out2 = torch.empty_like(out)
+    d_len = torch.tensor([seq], dtype=torch.int32, device="cuda")
+    ck.flash_decode_dyn_into(q, kbig, vbig, out2, nh, nkv, d_len.data_ptr(), hd, scale, max_seq)
+    assert torch.equal(out2, out)
+
+
+# ------------------------------------------------------------------ decode layer and graph
+def _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, seed, fused):
+    from nve_b200 import cuda_kernels as ck
+    from nve_b200.gpu_layer import GpuInferenceState, GpuKvCache, GpuLayerWeights, GpuW4, RoutingConfig
+
+    def w4(n, k, sid):
+        W = ck.fill_normal(n * k, seed, sid, scale=0.02).view(n, k)
+        nib, sc = ck.q4_quantize(W)
+        return GpuW4(nib, sc, None, n, k)
+
+    lw = []
+    for li in range(layers):
+        b = 100 * li
+        ones = torch.ones(hidden, dtype=torch.float16, device="cuda")
+        lw.append(GpuLayerWeights(w4(nh * hd, hidden, b + 1), w4(nkv * hd, hidden, b + 2), w4(nkv * hd, hidden, b + 3),
+                                  w4(hidden, nh * hd, b + 4), w4(ffn, hidden, b + 5), w4(ffn, hidden, b + 6),
+                                  w4(hidden, ffn, b + 7), ones, ones.clone()))
+    cos, sin = orc.rope_tables_f32(hd, max_seq, 10000.0)
+    kv = GpuKvCache(layers, nkv, max_seq, hd, "cuda")
+    return GpuInferenceState(lw, kv, nh, nkv, hd, 1e-5, dev(orc.to_act16(cos), torch.float16),
+                             dev(orc.to_act16(sin), torch.float16), RoutingConfig(False, 0.7), fused)
+
+
+def _oracle_layer(orc, h16, w, kc_f32, vc_f32, pos, nh, nkv, hd, cos16, sin16, use_w4a8):
+    """One decode layer on the host with the oracle pieces, mirroring src/gpu_layer.rs:1027-1083 (16-bit
+    activations between kernels, as the device path has them)."""
+    def cpu(t):
+        return t.cpu().numpy()
+
+    def gemv(x16, p):
+        nib, sc = cpu(p.nibbles), cpu(p.scales)
+        if use_w4a8:
+            xq, xs = orc.quantize_q8(x16)
+            return orc.to_act16(orc.w4a8_matvec_f64(xq, xs, nib, sc).astype(np.float32))
+        return orc.to_act16(orc.w4a16_matvec_f64(orc.from_act16(x16), nib, sc).astype(np.float32))
+
+    ones = orc.to_act16(np.ones(h16.size, np.float32))
+    n1 = orc.rms_norm_16(h16, ones, 1e-5)
+    q = orc.from_act16(gemv(n1, w.q_proj))
+    k = orc.from_act16(gemv(n1, w.k_proj))
+    v16 = gemv(n1, w.v_proj)
+    cr, sr = orc.from_act16(cos16[pos]), orc.from_act16(sin16[pos])
+    q = orc.from_act16(orc.to_act16(orc.rope_apply(q, nh, hd, cr, sr)))
+    k = orc.from_act16(orc.to_act16(orc.rope_apply(k, nkv, hd, cr, sr)))
+    kc_f32[:, pos] = k.reshape(nkv, hd)
+    vc_f32[:, pos] = orc.from_act16(v16).reshape(nkv, hd)
+    attn = orc.to_act16(orc.attn_decode(q.reshape(nh, hd), kc_f32, vc_f32, pos + 1, hd ** -0.5).reshape(-1))
+    o = gemv(attn, w.o_proj)
+    h1 = orc.to_act16(orc.from_act16(h16) + orc.from_act16(o))
+    n2 = orc.rms_norm_16(h1, ones, 1e-5)
+    g, u = gemv(n2, w.gate_proj), gemv(n2, w.up_proj)
+    mid = orc.silu_mul_16(g, u)
+    d = gemv(mid, w.down_proj)
+    return orc.to_act16(orc.from_act16(h1) + orc.from_act16(d))
+
+
+@pytest.mark.parametrize("use_w4a8", [True, False])
+def test_decode_layer_fused_equals_reference_sequence_and_oracle(cuda, orc, use_w4a8):
+    from nve_b200.gpu_layer import gpu_layer_forward_decode
+
+    torch = cuda
+    hidden, ffn, nh, nkv, hd, max_seq = 512, 1024, 8, 2, 64, 16
+    importance = 0.0 if use_w4a8 else 1.0
+    states = [_make_state(torch, orc, hidden, ffn, nh, nkv, hd, 1, max_seq, 81, fused) for fused in (True, False)]
+    h16 = orc.to_act16(orc.fill_normal(hidden, 82, 1))
+    cos, sin = orc.rope_tables_f32(hd, max_seq, 10000.0)
+    cos16, sin16 = orc.to_act16(cos), orc.to_act16(sin)
+    kc = np.zeros((nkv, max_seq, hd), np.float32)
+    vc = np.zeros_like(kc)
+    hs = [dev(h16, torch.float16).view(1, -1) for _ in states]
+    h_or = h16
+    for pos in range(3):
+        outs = [gpu_layer_forward_decode(h, 0, st, pos, False, importance) for h, st in zip(hs, states)]
+        assert torch.equal(outs[0], outs[1])  # fused schedule == the reference's kernel sequence, bit for bit
+        h_or = _oracle_layer(orc, h_or, states[0].layer_weights[0], kc, vc, pos, nh, nkv, hd, cos16, sin16, use_w4a8)
+        assert rel_rms_err(outs[0].float().cpu().numpy(), orc.from_act16(h_or)) < TOL
+        hs = outs
+
+
+def test_graph_replay_equals_eager_mixed_routing(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+    from nve_b200.decode_graph import StaticDecodeGraph
+    from nve_b200.gpu_layer import RoutingConfig, gpu_layer_forward_decode
+
+    torch = cuda
+    hidden, ffn, nh, nkv, hd, layers, max_seq = 512, 1024, 8, 2, 64, 4, 16
+    imp = [0.1, 0.9, 0.4, 1.0]  # threshold 0.7: layers 0 and 2 run W4A8, 1 and 3 run W4A16
+    st_e = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 91, True)
+    st_g = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 91, True)
+    graph = StaticDecodeGraph(st_g, hidden, ffn, imp)
+    assert graph.routes == [True, False, True, False]
+    graph.capture()
+    assert graph.launches_per_replay == 10 * layers
+    try:
+        for pos in range(4):
+            h_in = dev(orc.to_act16(orc.fill_normal(hidden, 92, pos)), torch.float16).view(1, -1)
+            h = h_in
+            for li in range(layers):
+                h = gpu_layer_forward_decode(h, li, st_e, pos, False, imp[li])
+            out = graph.replay(h_in, pos)
+            torch.cuda.synchronize()
+            assert torch.equal(out, h)
+        for li in range(layers):
+            assert torch.equal(st_e.kv_cache.k[li], st_g.kv_cache.k[li])
+    finally:
+        graph.destroy()
+    assert not ck.graph_ready()
