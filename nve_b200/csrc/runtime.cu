@@ -94,6 +94,8 @@ struct GraphState {
     int* dev_seqlen = nullptr;
     int ready = 0;
     bool capturing = false;
+    unsigned long long launches_at_begin = 0;
+    unsigned long long kernels_in_graph = 0;
 };
 GraphState g_graph;
 }  // namespace
@@ -136,6 +138,7 @@ extern "C" void nve_graph_begin_capture(void) {
     if (e == cudaSuccess) e = cudaStreamBeginCapture(g.cap_stream, cudaStreamCaptureModeThreadLocal);
     if (e == cudaSuccess) {
         g.capturing = true;
+        g.launches_at_begin = g_launches.load(std::memory_order_relaxed);
         // The scalar copies are the first nodes, so every replay starts by refreshing pos / seq_len.
         e = cudaMemcpyAsync(g.dev_pos, g.pin_pos, sizeof(int), cudaMemcpyHostToDevice, g.cap_stream);
         if (e == cudaSuccess)
@@ -155,6 +158,7 @@ extern "C" void nve_graph_end_capture(void) {
         return;
     }
     g.capturing = false;
+    g.kernels_in_graph = g_launches.load(std::memory_order_relaxed) - g.launches_at_begin;
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamEndCapture(g.cap_stream, &graph);
     if (e == cudaSuccess && graph != nullptr) {
@@ -173,6 +177,8 @@ extern "C" void nve_graph_launch(int pos, int seq_len, nve_stream_t stream) {
     }
     *g.pin_pos = pos;
     *g.pin_seqlen = seq_len;
+    // every replay runs the kernels recorded between begin_capture and end_capture
+    count_launch(static_cast<int>(g.kernels_in_graph));
     set_cuda_status(cudaGraphLaunch(g.exec, static_cast<cudaStream_t>(stream)));
 }
 

@@ -21,3 +21,19 @@ def rel_rms_err(y, ref) -> float:
 
 
 TOL = 1e-2  # max-abs <= 1e-2 * RMS(reference output), fp32 accumulation
+
+
+def same_f16(a_bits: np.ndarray, b_bits: np.ndarray, bf16: bool = False) -> bool:
+    """Bit equality of two 16-bit float arrays, except that any NaN equals any NaN (host and device
+    conversions pick different NaN payloads)."""
+    a = np.asarray(a_bits, np.uint16).reshape(-1)
+    b = np.asarray(b_bits, np.uint16).reshape(-1)
+    if a.shape != b.shape:
+        return False
+    if bf16:
+        nan_a = ((a & 0x7F80) == 0x7F80) & ((a & 0x007F) != 0)
+        nan_b = ((b & 0x7F80) == 0x7F80) & ((b & 0x007F) != 0)
+    else:
+        nan_a = ((a & 0x7C00) == 0x7C00) & ((a & 0x03FF) != 0)
+        nan_b = ((b & 0x7C00) == 0x7C00) & ((b & 0x03FF) != 0)
+    return bool(np.all((a == b) | (nan_a & nan_b)))

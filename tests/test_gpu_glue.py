@@ -265,7 +265,8 @@ def test_graph_replay_equals_eager_mixed_routing(cuda, orc):
     graph = StaticDecodeGraph(st_g, hidden, ffn, imp)
     assert graph.routes == [True, False, True, False]
     graph.capture()
-    assert graph.launches_per_replay == 10 * layers
+    # 11 launches on a W4A8 layer (one extra activation quantise before o_proj), 10 on a W4A16 layer
+    assert graph.launches_per_replay == 11 * 2 + 10 * 2
     try:
         for pos in range(4):
             h_in = dev(orc.to_act16(orc.fill_normal(hidden, 92, pos)), torch.float16).view(1, -1)

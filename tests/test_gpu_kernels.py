@@ -7,7 +7,7 @@ held to max|y - ref| <= 1e-2 * RMS(ref) against the reference's CPU path (f32 ac
 import numpy as np
 import pytest
 
-from helpers import TOL, dev, f16_bits, rel_rms_err
+from helpers import TOL, dev, f16_bits, rel_rms_err, same_f16
 
 pytestmark = pytest.mark.gpu
 
@@ -123,12 +123,17 @@ def test_w4a16_reference_entry_points(cuda, orc, golden):
     N, K = g["g_nibbles"].shape[0], g["g_x16"].size
     dx = dev(g["g_x16"], torch.float16).view(1, K)
     y = ck.fused_matvec_w4a16(dx, dev(g["g_nibbles"]), dev(g["g_scales"]), None, N, K)
-    assert np.array_equal(f16_bits(y).reshape(-1), orc.f32_to_f16_bits(g["g_y_w4a16_b200"]))
-    assert rel_rms_err(y.float().cpu().numpy(), g["g_y_cpu_scalar"]) < TOL
+    # row 6 holds weights near the f32 maximum: its scaled sum overflows to NaN on host and device alike
+    assert same_f16(f16_bits(y), orc.f32_to_f16_bits(g["g_y_w4a16_b200"]))
+    fin = np.isfinite(g["g_y_cpu_scalar"]) & np.isfinite(g["g_y_w4a16_b200"])
+    assert fin.sum() >= N - 1
+    assert rel_rms_err(y.float().cpu().numpy().reshape(-1)[fin], g["g_y_cpu_scalar"][fin]) < TOL
     # AWQ: x is multiplied by the inverse scales before the dot (weights were quantised pre-scaled)
     ya = ck.fused_matvec_w4a16(dx, dev(g["g_awq_nibbles"]), dev(g["g_awq_scales"]), dev(g["g_awq_inv"]), N, K)
-    assert np.array_equal(f16_bits(ya).reshape(-1), orc.f32_to_f16_bits(g["g_y_awq_b200"]))
-    assert rel_rms_err(ya.float().cpu().numpy(), g["g_y_awq_cpu_scalar"]) < TOL
+    assert same_f16(f16_bits(ya), orc.f32_to_f16_bits(g["g_y_awq_b200"]))
+    fin = np.isfinite(g["g_y_awq_cpu_scalar"]) & np.isfinite(g["g_y_awq_b200"])
+    assert fin.sum() >= N - 1
+    assert rel_rms_err(ya.float().cpu().numpy().reshape(-1)[fin], g["g_y_awq_cpu_scalar"][fin]) < TOL
     # q/k/v in one launch equals three launches
     n1, n2 = 32, 16
     nib, sc = dev(g["g_nibbles"]), dev(g["g_scales"])
@@ -137,7 +142,7 @@ def test_w4a16_reference_entry_points(cuda, orc, golden):
     q, k, v = ck.fused_qkv_matvec_w4a16(dx, parts[0][0], parts[0][1], None, n1, parts[1][0], parts[1][1], None, n2,
                                         parts[2][0], parts[2][1], None, N - n1 - n2, K)
     joined = torch.cat([q, k, v], dim=1)
-    assert np.array_equal(f16_bits(joined).reshape(-1), f16_bits(y).reshape(-1))
+    assert same_f16(f16_bits(joined), f16_bits(y))
 
 
 def test_config1_w4a16_up_proj(cuda, orc, golden):
@@ -297,10 +302,11 @@ def test_dequant_bit_exact(cuda, orc, golden, bf):
     g = golden
     N, K = g["g_nibbles"].shape[0], g["g_x16"].size
     out = ck.dequant_w4a16_any(dev(g["g_nibbles"]), dev(g["g_scales"]), None, N, K, torch.bfloat16 if bf else torch.float16)
-    assert np.array_equal(f16_bits(out), orc.dequant_w4a16(g["g_nibbles"], g["g_scales"], None, bf))
+    assert same_f16(f16_bits(out), orc.dequant_w4a16(g["g_nibbles"], g["g_scales"], None, bf), bf)
     if not bf:
         out2 = ck.dequant_w4a16(dev(g["g_awq_nibbles"]), dev(g["g_awq_scales"]), dev(g["g_awq_inv"]), N, K)
-        assert np.array_equal(f16_bits(out2), orc.dequant_w4a16(g["g_awq_nibbles"], g["g_awq_scales"], g["g_awq_inv"]))
+        # the pre-scaled near-maximum row overflows: scale inf, codes 0, dequantised value NaN on both sides
+        assert same_f16(f16_bits(out2), orc.dequant_w4a16(g["g_awq_nibbles"], g["g_awq_scales"], g["g_awq_inv"]))
 
 
 def test_generator_bit_exact(cuda, orc):
