@@ -208,6 +208,30 @@ NVE_API int nve_b200_matvec_w4a8_multi(const int8_t* xq, const float* xq_scales,
 NVE_API int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mats,
                                 int num_mats, int K, int out_dtype, nve_stream_t stream);
 
+/* The same GEMVs with the RMSNorm of the input fused into the kernel prologue: h is the un-normalised
+ * 16-bit hidden state (act_dtype f16/bf16), norm_weight its RMSNorm weight.  Every CTA recomputes the norm
+ * in the library's fixed order, rounds to 16 bits and then quantises (W4A8) or stages (W4A16) exactly as the
+ * separate kernels do, so results are bit-identical to nve_b200_rmsnorm_quantize_q8 / nve_b200_rms_norm
+ * followed by the plain GEMV (src/gpu_layer.rs:1032-1038 + :656-672 in one launch). */
+NVE_API int nve_b200_rmsnorm_matvec_w4a8_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                               const nve_b200_w4_matrix* mats, int num_mats, int K, int out_dtype,
+                                               nve_stream_t stream);
+NVE_API int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                const float* awq, const nve_b200_w4_matrix* mats, int num_mats, int K,
+                                                int out_dtype, nve_stream_t stream);
+
+/* RoPE of q and the new k at position *d_pos, the KV-cache write of the new row and single-query GQA
+ * attention over the first *d_seq_len positions, in one launch (src/gpu_layer.rs:697-735 /
+ * src/decode_graph.rs:247-283).  q [nh,hd] and k_new/v_new [nkv,hd] are read, not modified; caches are
+ * [nkv, max_seq_len, hd]; tables [max_seq_len, hd/2]; out [nh,hd] f16.  When out_q / out_scales are given
+ * the output is also quantised to int8 per group of 32 (the call at src/gpu_layer.rs:739).  head_dim 64 or
+ * 128.  Results are bit-identical to the separate RoPE, KV-write, flash-decode and quantise launches. */
+NVE_API int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
+                                       uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
+                                       const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,
+                                       int8_t* out_q, float* out_scales, int num_heads, int num_kv_heads,
+                                       int head_dim, int max_seq_len, float scale, nve_stream_t stream);
+
 /* Exact per-block integer dot products I[N, K/32] (int32) of the W4A8 GEMV, for bit-level checks. */
 NVE_API int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int32_t* I, int N, int K, nve_stream_t stream);
 

@@ -1,0 +1,353 @@
+// Single-query GQA attention for decode, optionally fused with RoPE, the KV-cache write and the int8
+// quantisation of its output.
+//
+// Replaces cuda/nve_kernels.cu:462-591 / :1075-1197 (flash decode) of the reference project and, in the
+// fused form, also :1006-1065 (RoPE at a device position), :909-946 (KV scatter) and the activation
+// quantiser call that precedes o_proj on the W4A8 route (src/gpu_layer.rs:697-741 in one launch).
+//
+// Design (head_dim 64 or 128; other sizes use the generic kernel in attn_glue.cu):
+//   * A thread-block cluster of 8 CTAs serves QH query heads that share one KV head; CTA `rank` owns the
+//     positions [rank*chunk, (rank+1)*chunk).  K and V rows are read once per cluster with 128-bit loads.
+//   * 256 threads = PL position lanes x DC dim chunks (DC = head_dim/8 lanes hold one 16-byte slice of a
+//     row).  Each thread loads K and V of 4 positions per iteration (8 loads in flight), reduces the QH dot
+//     products over its DC lanes with xor shuffles and keeps a private online-softmax state.
+//   * The 256 thread states are merged through shared memory, the 8 CTA partials through distributed
+//     shared memory by rank 0 -- no global scratch, no second launch.
+//   * Fused form: q and the new k are rotated in-kernel (same IEEE operations and 16-bit rounding as the
+//     stand-alone RoPE kernel); the CTA that owns position `pos` takes the fresh k/v from shared memory
+//     instead of the cache, and one CTA per KV head writes them to the cache.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace nve {
+
+constexpr int kAdCluster = 8;
+constexpr int kAdThreads = 256;
+constexpr int kAdUnroll = 4;
+
+struct AttnParams {
+    const uint16_t* q;        // [nh, hd]
+    const uint16_t* k_new;    // [nkv, hd] (fused form)
+    const uint16_t* v_new;    // [nkv, hd]
+    uint16_t* k_cache;        // [nkv, kv_stride, hd]
+    uint16_t* v_cache;
+    const uint16_t* cos_tab;  // [max_seq, hd/2]
+    const uint16_t* sin_tab;
+    const int* d_pos;         // fused form: position of the new token
+    const int* d_seq_len;     // valid length (device scalar) or NULL
+    int seq_len;              // valid length when d_seq_len == NULL
+    uint16_t* out;            // [nh, hd] f16
+    int8_t* out_q;            // optional int8 codes of out, group 32
+    float* out_scales;        // [nh*hd/32]
+    int num_heads, num_kv_heads, kv_stride;
+    float scale;
+};
+
+__device__ __forceinline__ void unpack8_f32(const uint4& raw, float (&o)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        o[2 * j] = Act16<NVE_DT_F16>::to_f32(static_cast<uint16_t>(w[j] & 0xFFFFu));
+        o[2 * j + 1] = Act16<NVE_DT_F16>::to_f32(static_cast<uint16_t>(w[j] >> 16));
+    }
+}
+
+template <int HD, int QH> struct AdCtaPartial {
+    float m[QH];
+    float s[QH];
+    float acc[QH][HD];
+};
+
+template <int HD, int QH, bool FUSED>
+__global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParams p) {
+    constexpr int DC = HD / 8;            // lanes per row
+    constexpr int PL = kAdThreads / DC;   // position lanes
+    constexpr int HALF = HD / 2;
+    cg::cluster_group cluster = cg::this_cluster();
+
+    __shared__ float q_s[QH][HD];
+    __shared__ __align__(16) uint16_t knew_s[HD];
+    __shared__ __align__(16) uint16_t vnew_s[HD];
+    __shared__ float pm[PL][QH], ps[PL][QH];
+    __shared__ float pacc[PL][QH][HD];
+    __shared__ AdCtaPartial<HD, QH> cta_part;
+
+    pdl_wait();
+    const int tid = threadIdx.x;
+    const int dc = tid % DC, pl = tid / DC;
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int cluster_id = blockIdx.x / kAdCluster;
+    const int groups = p.num_heads / p.num_kv_heads;
+    const int clusters_per_kv = groups / QH;
+    const int kvh = cluster_id / clusters_per_kv;
+    const int h0 = kvh * groups + (cluster_id % clusters_per_kv) * QH;  // first query head of this cluster
+
+    int seq_len = p.d_seq_len != nullptr ? *p.d_seq_len : p.seq_len;
+    seq_len = max(0, min(seq_len, p.kv_stride));
+    int pos = -1;
+    if constexpr (FUSED) pos = *p.d_pos;
+    const bool pos_ok = FUSED && pos >= 0 && pos < p.kv_stride;
+
+    // ---- stage q (rotated in the fused form) and the new k / v row
+    if constexpr (FUSED) {
+        const uint16_t* cr = p.cos_tab + static_cast<long long>(pos_ok ? pos : 0) * HALF;
+        const uint16_t* sr = p.sin_tab + static_cast<long long>(pos_ok ? pos : 0) * HALF;
+        for (int i = tid; i < QH * HALF; i += kAdThreads) {
+            const int h = i / HALF, e = i % HALF;
+            const uint16_t* qp = p.q + static_cast<long long>(h0 + h) * HD;
+            const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
+            const float x0 = Act16<NVE_DT_F16>::to_f32(qp[e]), x1 = Act16<NVE_DT_F16>::to_f32(qp[e + HALF]);
+            const uint16_t r0 = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+            const uint16_t r1 = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+            q_s[h][e] = Act16<NVE_DT_F16>::to_f32(r0);
+            q_s[h][e + HALF] = Act16<NVE_DT_F16>::to_f32(r1);
+        }
+        for (int e = tid; e < HALF; e += kAdThreads) {
+            const uint16_t* kp = p.k_new + static_cast<long long>(kvh) * HD;
+            const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
+            const float x0 = Act16<NVE_DT_F16>::to_f32(kp[e]), x1 = Act16<NVE_DT_F16>::to_f32(kp[e + HALF]);
+            knew_s[e] = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+            knew_s[e + HALF] = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+        }
+        for (int e = tid; e < HD; e += kAdThreads) vnew_s[e] = p.v_new[static_cast<long long>(kvh) * HD + e];
+    } else {
+        for (int i = tid; i < QH * HD; i += kAdThreads)
+            q_s[i / HD][i % HD] = Act16<NVE_DT_F16>::to_f32(p.q[static_cast<long long>(h0) * HD + i]);
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    float qr[QH][8];
+#pragma unroll
+    for (int h = 0; h < QH; h++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) qr[h][i] = q_s[h][dc * 8 + i];
+
+    const int chunk = (seq_len + kAdCluster - 1) / kAdCluster;
+    const int t_begin = rank * chunk;
+    const int t_end = min(seq_len, t_begin + chunk);
+    const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
+    const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
+
+    // one CTA per KV head stores the new row; every CTA that covers `pos` reads it from shared memory
+    if constexpr (FUSED) {
+        if (pos_ok && rank == 0 && (cluster_id % clusters_per_kv) == 0 && tid < 2 * DC) {
+            const int which = tid / DC, d = tid % DC;
+            uint16_t* dst = (which == 0 ? p.k_cache : p.v_cache) + (static_cast<long long>(kvh) * p.kv_stride + pos) * HD;
+            reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? knew_s : vnew_s)[d];
+        }
+    }
+
+    float m[QH], s[QH], acc[QH][8];
+#pragma unroll
+    for (int h = 0; h < QH; h++) {
+        m[h] = -1e30f;
+        s[h] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[h][i] = 0.0f;
+    }
+
+    const int span = PL * kAdUnroll;
+    const int iters = (max(0, t_end - t_begin) + span - 1) / span;  // uniform over the CTA
+    for (int it = 0; it < iters; it++) {
+        uint4 kraw[kAdUnroll], vraw[kAdUnroll];
+        bool valid[kAdUnroll];
+#pragma unroll
+        for (int u = 0; u < kAdUnroll; u++) {
+            const int t = t_begin + it * span + u * PL + pl;
+            valid[u] = t < t_end;
+            const int tc = valid[u] ? t : t_begin;
+            if (FUSED && tc == pos) {
+                kraw[u] = reinterpret_cast<const uint4*>(knew_s)[dc];
+                vraw[u] = reinterpret_cast<const uint4*>(vnew_s)[dc];
+            } else {
+                kraw[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
+                vraw[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
+            }
+        }
+        float sc[kAdUnroll][QH];
+#pragma unroll
+        for (int u = 0; u < kAdUnroll; u++) {
+            float kf[8];
+            unpack8_f32(kraw[u], kf);
+#pragma unroll
+            for (int h = 0; h < QH; h++) {
+                float d = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) d = fmaf(qr[h][i], kf[i], d);
+#pragma unroll
+                for (int msk = DC / 2; msk > 0; msk >>= 1) d += __shfl_xor_sync(0xffffffffu, d, msk);
+                sc[u][h] = valid[u] ? d * p.scale : -1e30f;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < QH; h++) {
+            float new_m = m[h];
+#pragma unroll
+            for (int u = 0; u < kAdUnroll; u++) new_m = fmaxf(new_m, sc[u][h]);
+            const float corr = expf(m[h] - new_m);
+            float pe[kAdUnroll];
+            float psum = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kAdUnroll; u++) {
+                pe[u] = valid[u] ? expf(sc[u][h] - new_m) : 0.0f;
+                psum += pe[u];
+            }
+            s[h] = fmaf(s[h], corr, psum);
+            m[h] = new_m;
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[h][i] *= corr;
+#pragma unroll
+            for (int u = 0; u < kAdUnroll; u++) {
+                float vf[8];
+                unpack8_f32(vraw[u], vf);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[h][i] = fmaf(pe[u], vf[i], acc[h][i]);
+            }
+        }
+    }
+
+    // ---- merge the position lanes of this CTA
+#pragma unroll
+    for (int h = 0; h < QH; h++) {
+        if (dc == 0) { pm[pl][h] = m[h]; ps[pl][h] = s[h]; }
+#pragma unroll
+        for (int i = 0; i < 8; i++) pacc[pl][h][dc * 8 + i] = acc[h][i];
+    }
+    __syncthreads();
+    for (int i = tid; i < QH * HD; i += kAdThreads) {
+        const int h = i / HD, d = i % HD;
+        float mm = -1e30f;
+        for (int l = 0; l < PL; l++) mm = fmaxf(mm, pm[l][h]);
+        float ss = 0.0f, a = 0.0f;
+        for (int l = 0; l < PL; l++) {
+            const float c = expf(pm[l][h] - mm);
+            ss = fmaf(ps[l][h], c, ss);
+            a = fmaf(pacc[l][h][d], c, a);
+        }
+        cta_part.acc[h][d] = a;
+        if (d == 0) { cta_part.m[h] = mm; cta_part.s[h] = ss; }
+    }
+    cluster.sync();
+
+    // ---- rank 0 merges the CTA partials through distributed shared memory, normalises and stores
+    if (rank == 0) {
+        for (int i = tid; i < QH * HD; i += kAdThreads) {
+            const int h = i / HD, d = i % HD;
+            float mm = -1e30f;
+#pragma unroll
+            for (int r = 0; r < kAdCluster; r++) mm = fmaxf(mm, cluster.map_shared_rank(&cta_part, r)->m[h]);
+            float ss = 0.0f, a = 0.0f;
+#pragma unroll
+            for (int r = 0; r < kAdCluster; r++) {
+                const AdCtaPartial<HD, QH>* rp = cluster.map_shared_rank(&cta_part, r);
+                const float c = expf(rp->m[h] - mm);
+                ss = fmaf(rp->s[h], c, ss);
+                a = fmaf(rp->acc[h][d], c, a);
+            }
+            const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
+            const uint16_t o16 = Act16<NVE_DT_F16>::from_f32(a * inv);
+            const long long oi = static_cast<long long>(h0 + h) * HD + d;
+            p.out[oi] = o16;
+            if (p.out_q != nullptr) {
+                // i advances by whole warps and HD is a multiple of 32: the 32 lanes of a warp hold one group
+                const float v = Act16<NVE_DT_F16>::to_f32(o16);
+                const float amax = warp_max(fabsf(v));
+                const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+                int qv = __float2int_rn(__fmul_rn(v, __fdiv_rn(1.0f, scale)));
+                qv = max(-127, min(127, qv));
+                p.out_q[oi] = static_cast<int8_t>(qv);
+                if ((tid & 31) == 0) p.out_scales[oi >> 5] = scale;
+            }
+        }
+    }
+    cluster.sync();  // keep every CTA's shared memory alive until rank 0 has read it
+}
+
+template <int HD, int QH, bool FUSED> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
+    const int clusters = p.num_heads / QH;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(clusters * kAdCluster);
+    cfg.blockDim = dim3(kAdThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kAdCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (pdl_enabled()) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, QH, FUSED>, p);
+}
+
+// Returns false when the shape is not covered (the caller then uses the generic kernel).
+template <bool FUSED> static bool attn_decode_dispatch(const AttnParams& p, int hd, cudaStream_t st, cudaError_t& err) {
+    const int groups = p.num_heads / p.num_kv_heads;
+    if (!aligned(p.k_cache, 16) || !aligned(p.v_cache, 16)) return false;
+    const int qh = (groups % 2 == 0) ? 2 : 1;
+    if (hd == 128) {
+        err = qh == 2 ? launch_ad<128, 2, FUSED>(p, st) : launch_ad<128, 1, FUSED>(p, st);
+        return true;
+    }
+    if (hd == 64) {
+        err = qh == 2 ? launch_ad<64, 2, FUSED>(p, st) : launch_ad<64, 1, FUSED>(p, st);
+        return true;
+    }
+    return false;
+}
+
+// Used by the reference-signature flash-decode entry points (attn_glue.cu).
+bool attn_decode_try(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, uint16_t* out, int nh, int nkv, int seq_len,
+                     const int* d_seq_len, int kv_stride, int hd, float scale, cudaStream_t st) {
+    AttnParams p = {};
+    p.q = q;
+    p.k_cache = const_cast<uint16_t*>(kc);
+    p.v_cache = const_cast<uint16_t*>(vc);
+    p.d_seq_len = d_seq_len;
+    p.seq_len = seq_len;
+    p.out = out;
+    p.num_heads = nh;
+    p.num_kv_heads = nkv;
+    p.kv_stride = kv_stride;
+    p.scale = scale;
+    cudaError_t e = cudaSuccess;
+    if (!attn_decode_dispatch<false>(p, hd, st, e)) return false;
+    count_launch();
+    set_cuda_status(e);
+    return true;
+}
+
+}  // namespace nve
+
+using namespace nve;
+
+extern "C" int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new, uint16_t* k_cache,
+                                          uint16_t* v_cache, const uint16_t* cos_tab, const uint16_t* sin_tab,
+                                          const int* d_pos, const int* d_seq_len, uint16_t* out, int8_t* out_q,
+                                          float* out_scales, int num_heads, int num_kv_heads, int head_dim,
+                                          int max_seq_len, float scale, nve_stream_t stream) {
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !cos_tab || !sin_tab || !d_pos || !d_seq_len || !out)
+        return set_status(NVE_ERR_BAD_POINTER);
+    if ((out_q == nullptr) != (out_scales == nullptr)) return set_status(NVE_ERR_BAD_POINTER);
+    if (num_heads <= 0 || num_kv_heads <= 0 || (num_heads % num_kv_heads) != 0 || max_seq_len <= 0)
+        return set_status(NVE_ERR_BAD_SHAPE);
+    if (head_dim != 64 && head_dim != 128) return set_status(NVE_ERR_BAD_SHAPE);
+    if (!aligned(k_cache, 16) || !aligned(v_cache, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    AttnParams p = {};
+    p.q = q; p.k_new = k_new; p.v_new = v_new; p.k_cache = k_cache; p.v_cache = v_cache;
+    p.cos_tab = cos_tab; p.sin_tab = sin_tab; p.d_pos = d_pos; p.d_seq_len = d_seq_len; p.seq_len = 0;
+    p.out = out; p.out_q = out_q; p.out_scales = out_scales;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.kv_stride = max_seq_len; p.scale = scale;
+    cudaError_t e = cudaSuccess;
+    if (!attn_decode_dispatch<true>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
+    count_launch();
+    return set_cuda_status(e);
+}

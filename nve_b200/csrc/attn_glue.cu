@@ -273,6 +273,10 @@ static cudaError_t launch_fd(const uint16_t* q, const uint16_t* kc, const uint16
                               kv_stride, scale);
 }
 
+// Fast path for head_dim 64 / 128 (attn_decode.cu); returns false when the shape is not covered.
+bool attn_decode_try(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, uint16_t* out, int nh, int nkv, int seq_len,
+                     const int* d_seq_len, int kv_stride, int hd, float scale, cudaStream_t st);
+
 static void flash_decode(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, uint16_t* out, int nh, int nkv,
                          int seq_len, const int* d_seq_len, int kv_stride, int hd, float scale, cudaStream_t st) {
     if (!q || !kc || !vc || !out) { set_status(NVE_ERR_BAD_POINTER); return; }
@@ -281,6 +285,7 @@ static void flash_decode(const uint16_t* q, const uint16_t* kc, const uint16_t* 
         set_status(NVE_ERR_BAD_SHAPE);
         return;
     }
+    if (attn_decode_try(q, kc, vc, out, nh, nkv, seq_len, d_seq_len, kv_stride, hd, scale, st)) return;
     cudaError_t e;
     switch (hd / 32) {
         case 1: e = launch_fd<1>(q, kc, vc, out, nh, nkv, seq_len, d_seq_len, kv_stride, scale, st); break;

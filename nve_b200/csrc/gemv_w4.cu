@@ -48,6 +48,8 @@ struct GemvParams {
     const float* xs;    // W4A8 scales
     const void* x16;    // W4A16 activations
     const float* awq;   // optional per-column multiplier (W4A16)
+    const void* norm_w; // RMSNorm weight of the fused prologue (16-bit, same type as x16)
+    float eps;
     int32_t* idot;      // debug: per-block integer dots [n_total, nb]
 };
 
@@ -175,64 +177,174 @@ __device__ __forceinline__ void stage_q8(const GemvParams& p, Smem<1>& sm) {
     }
 }
 
-// Convert 16-bit activations to two int8 planes of a per-block 16-bit fixed-point value (W4A16).
-//   xe = f32(x) [* awq] ; amax = max|xe| ; scale = amax > 0 ? amax / 32767 : 1 ; v = clamp(rint(xe / scale))
-//   low plane = v & 0xFF (unsigned), high plane = v >> 8 (signed) ; bias = 8 * sum(v)
-// A non-finite amax makes the scale NaN so that the affected outputs are NaN, as an f32 path would give.
-template <int XDT> __device__ __forceinline__ void stage_x16(const GemvParams& p, Smem<2>& sm) {
-    const uint16_t* x = static_cast<const uint16_t*>(p.x16);
-    for (int b = threadIdx.x; b < sm.nbp; b += blockDim.x) {
-        uint32_t lo_pl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        uint32_t hi_pl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        float xs = 0.0f;
-        int bias = 0;
-        if (b < p.nb) {
-            float xe[32];
-            const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * 32);
+// ---- chunk-wise staging -------------------------------------------------------------------------------
+// A chunk is 8 consecutive activations held by one thread; the 4 threads of a quad hold one 32-wide block.
+// Plane words of chunk c = 4b + j: half j/2 of block b, bytes (j%2)*8 .. (j%2)*8+7 of that 16-byte half.
+
+template <int PLANES> __device__ __forceinline__ void store_chunk_planes(Smem<PLANES>& sm, int c, int pl, uint32_t w0,
+                                                                        uint32_t w1) {
+    const int b = c >> 2, j = c & 3;
+    uint2* dst = reinterpret_cast<uint2*>(&sm.plane[(pl * 2 + (j >> 1)) * sm.nbp + b]);
+    dst[j & 1] = make_uint2(w0, w1);
+}
+
+// W4A8 codes from 8 already-rounded 16-bit values per thread (same arithmetic as the stand-alone quantizer:
+// scale = amax > 0 ? amax/127 : 1 ; q = clamp(rint(v * (1/scale)), -127, 127)).
+__device__ __forceinline__ void stage_chunk_q8(Smem<1>& sm, int c, const float (&v)[8], bool active) {
+    float amax = 0.0f;
 #pragma unroll
-            for (int v4 = 0; v4 < 4; v4++) {
-                const uint4 raw = src[v4];
-                const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    uint32_t w0 = 0, w1 = 0;
+    int sum = 0;
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    xe[v4 * 8 + 2 * j] = Act16<XDT>::to_f32(static_cast<uint16_t>(wv[j] & 0xFFFFu));
-                    xe[v4 * 8 + 2 * j + 1] = Act16<XDT>::to_f32(static_cast<uint16_t>(wv[j] >> 16));
-                }
-            }
-            if (p.awq != nullptr) {
-#pragma unroll
-                for (int e = 0; e < 32; e++) xe[e] = __fmul_rn(xe[e], p.awq[b * 32 + e]);
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int e = 0; e < 32; e++) amax = fmaxf(amax, fabsf(xe[e]));
-            float scale = amax > 0.0f ? __fdiv_rn(amax, 32767.0f) : 1.0f;
-            if (!(amax <= 3.0e38f)) scale = __int_as_float(0x7FC00000);
-            const float inv = __fdiv_rn(1.0f, scale);
-            int sum = 0;
-#pragma unroll
-            for (int e = 0; e < 32; e++) {
-                int v = __float2int_rn(__fmul_rn(xe[e], inv));
-                v = max(-32767, min(32767, v));
-                sum += v;
-                const uint32_t lo8 = static_cast<uint32_t>(v) & 0xFFu;
-                const uint32_t hi8 = static_cast<uint32_t>(v >> 8) & 0xFFu;
-                lo_pl[e >> 2] |= lo8 << (8 * (e & 3));
-                hi_pl[e >> 2] |= hi8 << (8 * (e & 3));
-            }
-            xs = scale;
-            bias = 8 * sum;
+    for (int e = 0; e < 8; e++) {
+        int q = __float2int_rn(__fmul_rn(v[e], inv));
+        q = max(-127, min(127, q));
+        sum += q;
+        const uint32_t byte = static_cast<uint32_t>(q) & 0xFFu;
+        if (e < 4) w0 |= byte << (8 * e);
+        else w1 |= byte << (8 * (e - 4));
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (active) {
+        store_chunk_planes<1>(sm, c, 0, w0, w1);
+        if ((c & 3) == 0) {
+            sm.xs[c >> 2] = scale;
+            sm.bias[c >> 2] = 8 * sum;
         }
-        sm.plane[(0 * 2 + 0) * sm.nbp + b] = make_uint4(lo_pl[0], lo_pl[1], lo_pl[2], lo_pl[3]);
-        sm.plane[(0 * 2 + 1) * sm.nbp + b] = make_uint4(lo_pl[4], lo_pl[5], lo_pl[6], lo_pl[7]);
-        sm.plane[(1 * 2 + 0) * sm.nbp + b] = make_uint4(hi_pl[0], hi_pl[1], hi_pl[2], hi_pl[3]);
-        sm.plane[(1 * 2 + 1) * sm.nbp + b] = make_uint4(hi_pl[4], hi_pl[5], hi_pl[6], hi_pl[7]);
-        sm.xs[b] = xs;
-        sm.bias[b] = bias;
     }
 }
 
-template <int PLANES, int XDT, int ODT, bool IDOT>
+// W4A16: 16-bit fixed-point planes from 8 f32 values per thread.
+//   amax = max|xe| over the block ; scale = amax > 0 ? amax / 32767 : 1 ; v = clamp(rint(xe * (1/scale)), +-32767)
+//   low plane = v & 0xFF (unsigned), high plane = v >> 8 (signed) ; bias = 8 * sum(v)
+// A non-finite amax makes the scale NaN so that the affected outputs are NaN, as an f32 path would give.
+__device__ __forceinline__ void stage_chunk_x16(Smem<2>& sm, int c, const float (&xe)[8], bool active) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(xe[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float scale = amax > 0.0f ? __fdiv_rn(amax, 32767.0f) : 1.0f;
+    if (!(amax <= 3.0e38f)) scale = __int_as_float(0x7FC00000);
+    const float inv = __fdiv_rn(1.0f, scale);
+    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;
+    int sum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        int q = __float2int_rn(__fmul_rn(xe[e], inv));
+        q = max(-32767, min(32767, q));
+        sum += q;
+        const uint32_t lo8 = static_cast<uint32_t>(q) & 0xFFu;
+        const uint32_t hi8 = static_cast<uint32_t>(q >> 8) & 0xFFu;
+        if (e < 4) { l0 |= lo8 << (8 * e); h0 |= hi8 << (8 * e); }
+        else { l1 |= lo8 << (8 * (e - 4)); h1 |= hi8 << (8 * (e - 4)); }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (active) {
+        store_chunk_planes<2>(sm, c, 0, l0, l1);
+        store_chunk_planes<2>(sm, c, 1, h0, h1);
+        if ((c & 3) == 0) {
+            sm.xs[c >> 2] = scale;
+            sm.bias[c >> 2] = 8 * sum;
+        }
+    }
+}
+
+__device__ __forceinline__ void load8(const uint16_t* p, int c, uint16_t (&h)[8]) {
+    const uint4 raw = reinterpret_cast<const uint4*>(p)[c];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        h[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
+        h[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
+    }
+}
+
+// Zero the padding blocks [nb, nbp) so that idle lanes contribute exactly 0.
+template <int PLANES> __device__ __forceinline__ void zero_padding(const GemvParams& p, Smem<PLANES>& sm) {
+    for (int b = p.nb + threadIdx.x; b < sm.nbp; b += blockDim.x) {
+#pragma unroll
+        for (int q = 0; q < PLANES * 2; q++) sm.plane[q * sm.nbp + b] = make_uint4(0, 0, 0, 0);
+        sm.xs[b] = 0.0f;
+        sm.bias[b] = 0;
+    }
+}
+
+// Stage the activations.  PRO = 0: the caller's vector (int8 codes for W4A8, 16-bit values for W4A16).
+// PRO = 1: RMSNorm of the caller's 16-bit vector first, in the library's fixed order (256 threads; thread t
+// adds x^2 over the 8-element chunks t, t+256, ... ; xor butterfly per warp; warp sums added in ascending
+// order; r = 1/sqrt(sum/n + eps); o = round16((x*r)*w)), then quantised exactly as the separate kernels do.
+template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_activations(const GemvParams& p,
+                                                                                           Smem<PLANES>& sm) {
+    zero_padding<PLANES>(p, sm);
+    if constexpr (PLANES == 1 && PRO == 0) {
+        stage_q8(p, sm);
+        return;
+    } else {
+        const uint16_t* x = static_cast<const uint16_t*>(p.x16);
+        const int chunks = p.K >> 3;
+        float r = 1.0f;
+        if constexpr (PRO == 1) {
+            __shared__ float warp_part[kGemvThreads / 32];
+            float acc = 0.0f;
+            for (int c = threadIdx.x; c < chunks; c += kGemvThreads) {
+                uint16_t h[8];
+                load8(x, c, h);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float v = Act16<XDT>::to_f32(h[e]);
+                    acc = __fmaf_rn(v, v, acc);
+                }
+            }
+            acc = warp_sum(acc);
+            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            float total = warp_part[0];
+#pragma unroll
+            for (int w = 1; w < kGemvThreads / 32; w++) total = __fadd_rn(total, warp_part[w]);
+            r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.K)), p.eps)));
+        }
+        const int iters = (chunks + kGemvThreads - 1) / kGemvThreads;
+        for (int it = 0; it < iters; it++) {
+            const int c = it * kGemvThreads + threadIdx.x;
+            const bool active = c < chunks;
+            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (active) {
+                uint16_t h[8];
+                load8(x, c, h);
+                if constexpr (PRO == 1) {
+                    uint16_t hw[8];
+                    load8(static_cast<const uint16_t*>(p.norm_w), c, hw);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const float o = __fmul_rn(__fmul_rn(Act16<XDT>::to_f32(h[e]), r), Act16<XDT>::to_f32(hw[e]));
+                        v[e] = Act16<XDT>::to_f32(Act16<XDT>::from_f32(o));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) v[e] = Act16<XDT>::to_f32(h[e]);
+                }
+                if constexpr (PLANES == 2) {
+                    if (p.awq != nullptr) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
+                    }
+                }
+            }
+            if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);
+            else stage_chunk_x16(sm, c, v, active);
+        }
+    }
+}
+
+template <int PLANES, int XDT, int ODT, bool IDOT, int PRO>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -254,8 +366,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     if (chunk_tiles > 0 && t < chunk_tiles) load_wtile(p, chunk0 + t, s, lane, cur);
 
     pdl_wait();
-    if constexpr (PLANES == 1) stage_q8(p, sm);
-    else stage_x16<XDT>(p, sm);
+    stage_activations<PLANES, XDT, PRO>(p, sm);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -428,26 +539,31 @@ template <typename Kern> static int launch_gemv(Kern kern, const GemvParams& p, 
     return set_cuda_status(e);
 }
 
-static bool all_aligned(const GemvParams& p, int num_mats, int planes) {
+static bool all_aligned(const GemvParams& p, int num_mats, int planes, int pro) {
     for (int m = 0; m < num_mats; m++)
         if (!aligned(p.nib[m], 16)) return false;
-    if (planes == 1) return aligned(p.xq, 16);
+    if (pro == 1 && !aligned(p.norm_w, 16)) return false;
+    if (planes == 1 && pro == 0) return aligned(p.xq, 16);
     return aligned(p.x16, 16);
 }
 
-template <int PLANES, int XDT, int ODT> static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
-    if (all_aligned(p, num_mats, PLANES)) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false>, p, PLANES, st);
-    const int wpb = 8;
-    gemv_w4_unaligned_kernel<PLANES, XDT, ODT><<<(p.n_total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
-    count_launch();
-    return check_launch();
+template <int PLANES, int XDT, int ODT, int PRO> static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
+    if (all_aligned(p, num_mats, PLANES, PRO)) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO>, p, PLANES, st);
+    if constexpr (PRO != 0) {
+        return set_status(NVE_ERR_BAD_ALIGNMENT);  // the fused prologue needs 16-byte aligned vectors
+    } else {
+        const int wpb = 8;
+        gemv_w4_unaligned_kernel<PLANES, XDT, ODT><<<(p.n_total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
+        count_launch();
+        return check_launch();
+    }
 }
 
-template <int PLANES, int XDT> static int dispatch_out(const GemvParams& p, int num_mats, int odt, cudaStream_t st) {
+template <int PLANES, int XDT, int PRO> static int dispatch_out(const GemvParams& p, int num_mats, int odt, cudaStream_t st) {
     switch (odt) {
-        case NVE_DT_F16: return dispatch_aligned<PLANES, XDT, NVE_DT_F16>(p, num_mats, st);
-        case NVE_DT_BF16: return dispatch_aligned<PLANES, XDT, NVE_DT_BF16>(p, num_mats, st);
-        case NVE_DT_F32: return dispatch_aligned<PLANES, XDT, NVE_DT_F32>(p, num_mats, st);
+        case NVE_DT_F16: return dispatch_aligned<PLANES, XDT, NVE_DT_F16, PRO>(p, num_mats, st);
+        case NVE_DT_BF16: return dispatch_aligned<PLANES, XDT, NVE_DT_BF16, PRO>(p, num_mats, st);
+        case NVE_DT_F32: return dispatch_aligned<PLANES, XDT, NVE_DT_F32, PRO>(p, num_mats, st);
         default: return set_status(NVE_ERR_BAD_DTYPE);
     }
 }
@@ -476,6 +592,7 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.S = (p.nb + kWarp - 1) / kWarp;
     p.tiles = (p.n_total + kRows - 1) / kRows;
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.awq = nullptr; p.idot = nullptr;
+    p.norm_w = nullptr; p.eps = 0.0f;
     return NVE_OK;
 }
 
@@ -491,7 +608,7 @@ extern "C" int nve_b200_matvec_w4a8_multi(const int8_t* xq, const float* xq_scal
     if (!xq || !xq_scales) return set_status(NVE_ERR_BAD_POINTER);
     p.xq = xq;
     p.xs = xq_scales;
-    return dispatch_out<1, NVE_DT_F16>(p, num_mats, out_dtype, static_cast<cudaStream_t>(stream));
+    return dispatch_out<1, NVE_DT_F16, 0>(p, num_mats, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mats,
@@ -503,8 +620,8 @@ extern "C" int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const flo
     p.x16 = x;
     p.awq = awq;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (x_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16>(p, num_mats, out_dtype, cs);
-    if (x_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16>(p, num_mats, out_dtype, cs);
+    if (x_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 0>(p, num_mats, out_dtype, cs);
+    if (x_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 0>(p, num_mats, out_dtype, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
 }
 
@@ -519,7 +636,40 @@ extern "C" int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int3
     p.xq = xq;
     p.xs = nullptr;
     p.idot = I;
-    return launch_gemv(gemv_w4_kernel<1, NVE_DT_F16, NVE_DT_F32, true>, p, 1, static_cast<cudaStream_t>(stream));
+    return launch_gemv(gemv_w4_kernel<1, NVE_DT_F16, NVE_DT_F32, true, 0>, p, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nve_b200_rmsnorm_matvec_w4a8_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                  const nve_b200_w4_matrix* mats, int num_mats, int K, int out_dtype,
+                                                  nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mats, num_mats, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h;
+    p.norm_w = norm_weight;
+    p.eps = eps;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_out<1, NVE_DT_F16, 1>(p, num_mats, out_dtype, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_out<1, NVE_DT_BF16, 1>(p, num_mats, out_dtype, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+extern "C" int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                   const float* awq, const nve_b200_w4_matrix* mats, int num_mats, int K,
+                                                   int out_dtype, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mats, num_mats, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h;
+    p.norm_w = norm_weight;
+    p.eps = eps;
+    p.awq = awq;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 1>(p, num_mats, out_dtype, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 1>(p, num_mats, out_dtype, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
 }
 
 // ---- reference-signature launchers ---------------------------------------------------------------

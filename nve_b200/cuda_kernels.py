@@ -408,6 +408,46 @@ def matvec_w4a16_multi(x: Tensor, awq: Optional[Tensor], weights: Sequence, k: i
     return list(outs)
 
 
+def rmsnorm_matvec_w4a8_multi(h: Tensor, norm_weight: Tensor, eps: float, weights: Sequence, k: int,
+                              out_dtype=torch.float16, outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """RMSNorm -> int8 quantise -> W4A8 GEMV over 1..3 matrices, one launch (bit-identical to the separate calls)."""
+    if outs is None:
+        outs = [torch.empty((1, n), dtype=out_dtype, device=h.device) for (_, _, n) in weights]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_rmsnorm_matvec_w4a8_multi",
+               _lib().nve_b200_rmsnorm_matvec_w4a8_multi(_ptr(h, (torch.float16, torch.bfloat16), "h"),
+                                                         _ptr(norm_weight, h.dtype, "norm_weight"), float(eps), _dt(h), arr,
+                                                         len(weights), k, _TORCH_DT[out_dtype], stream()))
+    return list(outs)
+
+
+def rmsnorm_matvec_w4a16_multi(h: Tensor, norm_weight: Tensor, eps: float, awq: Optional[Tensor], weights: Sequence,
+                               k: int, out_dtype=torch.float16, outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """RMSNorm -> W4A16 GEMV over 1..3 matrices, one launch (bit-identical to the separate calls)."""
+    if outs is None:
+        outs = [torch.empty((1, n), dtype=out_dtype, device=h.device) for (_, _, n) in weights]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_rmsnorm_matvec_w4a16_multi",
+               _lib().nve_b200_rmsnorm_matvec_w4a16_multi(_ptr(h, (torch.float16, torch.bfloat16), "h"),
+                                                          _ptr(norm_weight, h.dtype, "norm_weight"), float(eps), _dt(h),
+                                                          _ptr(awq, torch.float32), arr, len(weights), k,
+                                                          _TORCH_DT[out_dtype], stream()))
+    return list(outs)
+
+
+def attn_decode_fused(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, cos_tab: Tensor,
+                      sin_tab: Tensor, d_pos: int, d_seq_len: int, out: Tensor, num_heads: int, num_kv_heads: int,
+                      head_dim: int, max_seq_len: int, scale: float, out_q: Optional[Tensor] = None,
+                      out_scales: Optional[Tensor] = None) -> None:
+    """RoPE + KV-cache write + flash decode (+ int8 quantisation of the output) in one launch."""
+    _ffi.check("nve_b200_attn_decode_fused",
+               _lib().nve_b200_attn_decode_fused(_ptr(q, _F16, "q"), _ptr(k_new, _F16, "k_new"), _ptr(v_new, _F16, "v_new"),
+                                                 _ptr(k_cache, _F16), _ptr(v_cache, _F16), _ptr(cos_tab, _F16),
+                                                 _ptr(sin_tab, _F16), d_pos, d_seq_len, _ptr(out, _F16, "out"),
+                                                 _ptr(out_q, _Q8), _ptr(out_scales, torch.float32), num_heads,
+                                                 num_kv_heads, head_dim, max_seq_len, float(scale), stream()))
+
+
 def w4a8_idot(xq: Tensor, nibbles: Tensor, n: int, k: int) -> Tensor:
     """Exact per-block integer dots I[n, k/32] (int32)."""
     out = torch.empty((n, k // 32), dtype=torch.int32, device=xq.device)

@@ -6,7 +6,7 @@ copies the input row into `hidden_buf`, sets pos / seq_len and launches.  Two di
 caller side of the C ABI:
   * the reference records W4A16 kernels only (:218-342); here each layer is recorded on the route its
     importance score selects (src/gpu_layer.rs:1017-1025), so a mixed W4A8 / W4A16 stack replays as one graph;
-  * the fused entry points shorten a layer from 12 recorded steps to 10 launches.
+  * the fused entry points shorten a layer from 12 recorded steps to 6 launches.
 """
 from __future__ import annotations
 
@@ -76,43 +76,11 @@ class StaticDecodeGraph:
 
     # ------------------------------------------------------------------ recording
     def _record_layer(self, li: int, d_pos: int, d_seqlen: int) -> None:
-        st, s = self.state, self.s
-        w = st.layer_weights[li]
-        nh, nkv, hd = st.num_heads, st.num_kv_heads, st.head_dim
-        h = self.hidden_buf
-        kc, vc = st.kv_cache.k[li], st.kv_cache.v[li]
-        max_seq = st.kv_cache.max_seq
-        eps = st.norm_eps
-        qv, kv, vv = s.q.view(1, -1), s.k.view(1, -1), s.v.view(1, -1)
-        if self.routes[li]:
-            ck.rmsnorm_quantize_q8(h, w.input_norm, eps, xq=s.xq_h, scales=s.xs_h)
-            ck.matvec_w4a8_multi(s.xq_h, s.xs_h, [w.q_proj.triple(), w.k_proj.triple(), w.v_proj.triple()], w.q_proj.k,
-                                 outs=[qv, kv, vv])
-        else:
-            ck.fused_rms_norm_into(h, w.input_norm, s.normed, eps)
-            ck.matvec_w4a16_multi(s.normed, w.q_proj.awq_scales,
-                                  [w.q_proj.triple(), w.k_proj.triple(), w.v_proj.triple()], w.q_proj.k, outs=[qv, kv, vv])
-        ck.rope_decode_dyn_inplace(s.q, s.k, st.rope_cos, st.rope_sin, nh, nkv, hd, d_pos)
-        ck.kv_cache_write(s.k, kc, s.v, vc, d_pos, nkv, hd, max_seq)
-        ck.flash_decode_dyn_into(s.q, kc, vc, s.attn.view(nh, hd), nh, nkv, d_seqlen, hd, float(hd) ** -0.5, max_seq)
-        if self.routes[li]:
-            xq, xs = s.xq_a, s.xs_a
-            ck._ffi.check("nve_b200_quantize_q8", ck._lib().nve_b200_quantize_q8(
-                s.attn.data_ptr(), xq.data_ptr(), xs.data_ptr(), s.attn.numel(), ck.NVE_DT_F16, ck.stream()))
-            ck.matvec_w4a8_multi(xq, xs, [w.o_proj.triple()], w.o_proj.k, outs=[h], residuals=[h])
-            ck.rmsnorm_quantize_q8(h, w.post_attn_norm, eps, xq=s.xq_h, scales=s.xs_h)
-            ck.matvec_w4a8_multi(s.xq_h, s.xs_h, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
-                                 outs=[s.gate, s.up])
-            ck.silu_mul_quantize_q8(s.gate, s.up, xq=s.xq_f, scales=s.xs_f)
-            ck.matvec_w4a8_multi(s.xq_f, s.xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h], residuals=[h])
-        else:
-            ck.matvec_w4a16_multi(s.attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h], residuals=[h])
-            ck.fused_rms_norm_into(h, w.post_attn_norm, s.normed, eps)
-            ck.matvec_w4a16_multi(s.normed, w.gate_proj.awq_scales, [w.gate_proj.triple(), w.up_proj.triple()],
-                                  w.gate_proj.k, outs=[s.gate, s.up])
-            ck.silu_mul_inplace(s.gate, s.up)
-            ck.matvec_w4a16_multi(s.gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h],
-                                  residuals=[h])
+        from .gpu_layer import _layer_forward_fused
+
+        st = self.state
+        _layer_forward_fused(self.hidden_buf, st.layer_weights[li], st, li, d_pos, d_seqlen, self.routes[li],
+                             out=self.hidden_buf, scratch=self.s)
 
     def capture(self) -> None:
         """src/decode_graph.rs:138-370."""

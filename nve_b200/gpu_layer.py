@@ -7,8 +7,9 @@ file (F16 / dequantised weights, prefill, non-Llama FFN types, biases) is outsid
 
 Two schedules compute the same thing:
   * ``fused=False`` issues exactly the reference's sequence of kernels (one launch per reference call);
-  * ``fused=True`` uses the fused entry points (RMSNorm->quantise, q/k/v and gate/up in one launch,
-    SiLU*up->quantise, residual add in the GEMV epilogue).  Both give bit-identical hidden states.
+  * ``fused=True`` uses the fused entry points (RMSNorm inside the q/k/v and gate/up GEMV prologue, RoPE +
+    KV write + attention + quantise in one kernel, SiLU*up->quantise, residual add in the GEMV epilogue):
+    six launches per layer.  Both give bit-identical hidden states.
 """
 from __future__ import annotations
 
@@ -218,6 +219,57 @@ def gpu_ffn(normed_or_q8, w: GpuLayerWeights, state: GpuInferenceState, use_w4a8
     return out
 
 
+def _fused_attention_supported(state: "GpuInferenceState") -> bool:
+    return state.head_dim in (64, 128)
+
+
+def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInferenceState, layer_idx: int, d_pos: int,
+                         d_seqlen: int, use_w4a8: bool, out: Optional[Tensor] = None, scratch=None) -> Tensor:
+    """Six launches per layer: [RMSNorm + q/k/v GEMV], [RoPE + KV write + attention (+ quantise)], [o_proj GEMV +
+    residual], [RMSNorm + gate/up GEMV], [SiLU*up (+ quantise)], [down GEMV + residual].  `scratch` supplies
+    pre-allocated buffers (graph capture); `out` receives the new hidden state (may alias `hidden`)."""
+    nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+    dev, f16 = hidden.device, torch.float16
+    hidden_size = hidden.numel()
+    ffn = w.gate_proj.n
+    s = scratch
+
+    def buf(name, shape, dtype=f16):
+        return getattr(s, name) if s is not None else torch.empty(shape, dtype=dtype, device=dev)
+
+    q, k, v = buf("q", (nh, hd)), buf("k", (nkv, hd)), buf("v", (nkv, hd))
+    attn = buf("attn", (1, nh * hd))
+    gate, up = buf("gate", (1, ffn)), buf("up", (1, ffn))
+    h1 = out if out is not None else torch.empty_like(hidden)
+    qkv_w = [w.q_proj.triple(), w.k_proj.triple(), w.v_proj.triple()]
+    qkv_o = [q.view(1, -1), k.view(1, -1), v.view(1, -1)]
+    kc, vc = state.kv_cache.k[layer_idx], state.kv_cache.v[layer_idx]
+    max_seq = state.kv_cache.max_seq
+    eps, scale = state.norm_eps, float(hd) ** -0.5
+    if use_w4a8:
+        xq_a, xs_a = buf("xq_a", (nh * hd,), torch.int8), buf("xs_a", (nh * hd // 32,), torch.float32)
+        xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
+        ck.rmsnorm_matvec_w4a8_multi(hidden, w.input_norm, eps, qkv_w, w.q_proj.k, outs=qkv_o)
+        ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv,
+                             hd, max_seq, scale, out_q=xq_a, out_scales=xs_a)
+        ck.matvec_w4a8_multi(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        ck.rmsnorm_matvec_w4a8_multi(h1, w.post_attn_norm, eps, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
+                                     outs=[gate, up])
+        ck.silu_mul_quantize_q8(gate, up, xq=xq_f, scales=xs_f)
+        ck.matvec_w4a8_multi(xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
+    else:
+        ck.rmsnorm_matvec_w4a16_multi(hidden, w.input_norm, eps, w.q_proj.awq_scales, qkv_w, w.q_proj.k, outs=qkv_o)
+        ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv,
+                             hd, max_seq, scale)
+        ck.matvec_w4a16_multi(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
+                                      [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
+        ck.silu_mul_inplace(gate, up)
+        ck.matvec_w4a16_multi(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1],
+                              residuals=[h1])
+    return h1
+
+
 def gpu_layer_forward_decode(hidden: Tensor, layer_idx: int, state: GpuInferenceState, pos: int,
                              parallel_attn_ffn: bool = False, layer_importance: float = 0.0,
                              d_pos: Optional[int] = None, d_seqlen: Optional[int] = None) -> Tensor:
@@ -233,6 +285,10 @@ def gpu_layer_forward_decode(hidden: Tensor, layer_idx: int, state: GpuInference
         state.set_position(pos)
         d_pos, d_seqlen = state.d_pos.data_ptr(), state.d_seqlen.data_ptr()
     eps = state.norm_eps
+    same_awq = (w.q_proj.awq_scales is w.k_proj.awq_scales is w.v_proj.awq_scales) and \
+        (w.gate_proj.awq_scales is w.up_proj.awq_scales)
+    if state.fused and _fused_attention_supported(state) and (use_w4a8 or same_awq):
+        return _layer_forward_fused(hidden, w, state, layer_idx, d_pos, d_seqlen, use_w4a8)
     if state.fused and use_w4a8:
         xq, xs, _ = ck.rmsnorm_quantize_q8(hidden, w.input_norm, eps)
         h = gpu_attn_decode((xq, xs), w, state, layer_idx, d_pos, d_seqlen, True, residual=hidden)

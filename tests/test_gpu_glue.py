@@ -173,6 +173,69 @@ def test_flash_decode(cuda, orc, nh, nkv, hd, seq):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,pos", [(32, 8, 64, 0), (32, 8, 128, 100), (64, 8, 128, 1023), (8, 8, 64, 5), (6, 2, 128, 40)])
+def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
+    """RoPE + KV write + attention + quantise in one launch == the four separate launches, bit for bit."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    max_seq = 1024
+    c16, s16, dc, ds = _rope_tables(orc, torch, hd, max_seq)
+    q = dev(orc.to_act16(orc.fill_normal(nh * hd, 75, 1)), torch.float16).view(nh, hd)
+    k = dev(orc.to_act16(orc.fill_normal(nkv * hd, 75, 2)), torch.float16).view(nkv, hd)
+    v = dev(orc.to_act16(orc.fill_normal(nkv * hd, 75, 3)), torch.float16).view(nkv, hd)
+    kc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 75, 4)), torch.float16).view(nkv, max_seq, hd)
+    vc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 75, 5)), torch.float16).view(nkv, max_seq, hd)
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    d_len = torch.tensor([pos + 1], dtype=torch.int32, device="cuda")
+    scale = hd ** -0.5
+    # separate launches (the reference's sequence)
+    q1, k1, kc1, vc1 = q.clone(), k.clone(), kc.clone(), vc.clone()
+    ck.rope_decode_dyn_inplace(q1, k1, dc, ds, nh, nkv, hd, d_pos.data_ptr())
+    ck.kv_cache_write(k1, kc1, v, vc1, d_pos.data_ptr(), nkv, hd, max_seq)
+    out1 = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
+    ck.flash_decode_dyn_into(q1, kc1, vc1, out1, nh, nkv, d_len.data_ptr(), hd, scale, max_seq)
+    xq1, xs1 = ck.quantize_f16_q8(out1)
+    # one launch
+    kc2, vc2 = kc.clone(), vc.clone()
+    out2 = torch.empty_like(out1)
+    xq2 = torch.empty(nh * hd, dtype=torch.int8, device="cuda")
+    xs2 = torch.empty(nh * hd // 32, dtype=torch.float32, device="cuda")
+    ck.attn_decode_fused(q, k, v, kc2, vc2, dc, ds, d_pos.data_ptr(), d_len.data_ptr(), out2, nh, nkv, hd, max_seq, scale,
+                         out_q=xq2, out_scales=xs2)
+    assert torch.equal(out2, out1) and torch.equal(kc2, kc1) and torch.equal(vc2, vc1)
+    assert torch.equal(xq2, xq1) and torch.equal(xs2, xs1)
+    # and against the oracle
+    ref = orc.attn_decode(orc.from_act16(f16_bits(q1)).reshape(nh, hd), kc1.float().cpu().numpy(), vc1.float().cpu().numpy(),
+                          pos + 1, scale)
+    assert rel_rms_err(out2.float().cpu().numpy(), ref) < 5e-3
+
+
+@pytest.mark.parametrize("route", ["w4a8", "w4a16"])
+def test_rmsnorm_prologue_gemv_equals_separate_launches(cuda, orc, route):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    K = 4096
+    mats = []
+    for i, N in enumerate((1024, 256, 256)):
+        W = orc.fill_normal(N * K, 77, i, scale=0.02).reshape(N, K)
+        nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+        mats.append((dev(nib), dev(sc), N))
+    h = dev(orc.to_act16(orc.fill_normal(K, 77, 9) * 3.0), torch.float16).view(1, -1)
+    w = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(K, 77, 10)), torch.float16)
+    if route == "w4a8":
+        xq, xs, _ = ck.rmsnorm_quantize_q8(h, w, 1e-5)
+        sep = ck.matvec_w4a8_multi(xq, xs, mats, K)
+        fused = ck.rmsnorm_matvec_w4a8_multi(h, w, 1e-5, mats, K)
+    else:
+        normed = ck.fused_rms_norm(h, w, 1e-5)
+        sep = ck.matvec_w4a16_multi(normed, None, mats, K)
+        fused = ck.rmsnorm_matvec_w4a16_multi(h, w, 1e-5, None, mats, K)
+    for a, b in zip(sep, fused):
+        assert torch.equal(a, b)
+
+
 # ------------------------------------------------------------------ decode layer and graph
 def _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, seed, fused):
     from nve_b200 import cuda_kernels as ck
@@ -265,8 +328,7 @@ def test_graph_replay_equals_eager_mixed_routing(cuda, orc):
     graph = StaticDecodeGraph(st_g, hidden, ffn, imp)
     assert graph.routes == [True, False, True, False]
     graph.capture()
-    # 11 launches on a W4A8 layer (one extra activation quantise before o_proj), 10 on a W4A16 layer
-    assert graph.launches_per_replay == 11 * 2 + 10 * 2
+    assert graph.launches_per_replay == 6 * layers
     try:
         for pos in range(4):
             h_in = dev(orc.to_act16(orc.fill_normal(hidden, 92, pos)), torch.float16).view(1, -1)
