@@ -14,356 +14,78 @@
 //               an unsigned low byte plane, so the dot product stays on the integer dp4a pipe and is
 //               exact in int32; the only approximation is the fixed-point step amax/65534 per element,
 //               far below the 16-bit rounding of the output.
-//   * A warp task is (4 rows) x (32 consecutive blocks = 1024 weights per row): every lane issues one
-//     128-bit load of packed nibbles and one 32-bit load of the block scale per row, i.e. 512 contiguous
-//     bytes per row per warp.  The next task's loads are issued before the current one is reduced.
-//   * Per lane: 8 (W4A8) or 16 (W4A16) dp4a on raw nibbles 0..15, minus the precomputed 8*sum(x) bias,
-//     one int->float conversion and one multiply by (weight scale * activation scale).
-//   * The 32 lane values of a (row, column-set) are added by a fixed xor butterfly and stored to shared
-//     memory; a final pass adds the column-set partials of each row in ascending order.  The result is
-//     therefore independent of grid size and warp scheduling, and bit-reproducible.
+//   * A column set is 32 consecutive blocks (1024 weights) of a row; lane l owns block l of it.  A warp item
+//     is 2 rows x 4 column sets (8 blocks per lane; 4 x 2 or 8 x 1 when a row has only 2 or 1 column sets):
+//     every lane issues eight 128-bit loads of packed nibbles and eight 32-bit loads of block scales at
+//     once -- 512 contiguous bytes per row and column set -- so 16 warps keep about 80 KB in flight per SM.
+//     The next item's loads are issued before the current one is reduced; the first item's before the
+//     kernel waits for its producer (weights do not depend on it).
+//   * Per lane and block: 8 (W4A8) or 16 (W4A16) dp4a on raw nibbles (the high nibbles stay in place as
+//     16*q, removed by one exact shift), minus the precomputed 8*sum(x) bias, one int->float conversion and
+//     one multiply by (weight scale * activation scale).
+//   * Summation order (fixed, so results are bit-reproducible and independent of the launch geometry): per
+//     lane the column sets of a group of four are added in ascending order; the 32 lane values of a
+//     (row, group) are added by a xor butterfly (pairs l^16, ^8, ^4, ^2, ^1); the groups of a row are added
+//     in ascending order.
 //
 // Algorithmic bytes per launch: N*K/2 nibbles + N*K/8 scale bytes + activations + outputs.
-#include "common.cuh"
+#include "gemv_w4.cuh"
 
 namespace nve {
 
-constexpr int kRows = 4;           // rows per warp task
-constexpr int kGemvThreads = 256;  // 8 warps
-constexpr int kPartFloats = 4096;  // shared-memory floats for column-set partial sums
-constexpr int kMaxGemvSmem = 200 * 1024;  // dynamic shared memory a GEMV CTA may ask for
-
-struct GemvParams {
-    const uint8_t* nib[3];
-    const float* sc[3];
-    void* out[3];
-    const void* res[3];
-    int row_end[3];  // cumulative row ends of the (up to three) matrices
-    int n_total;     // rows over all matrices
-    int K;
-    int nb;          // K / 32
-    int S;           // column sets = ceil(nb / 32)
-    int tiles;       // ceil(n_total / kRows)
-    const int8_t* xq;   // W4A8 codes
-    const float* xs;    // W4A8 scales
-    const void* x16;    // W4A16 activations
-    const float* awq;   // optional per-column multiplier (W4A16)
-    const void* norm_w; // RMSNorm weight of the fused prologue (16-bit, same type as x16)
-    float eps;
-    int32_t* idot;      // debug: per-block integer dots [n_total, nb]
+// One warp item: R rows x C consecutive column sets (R * C = 8 blocks per lane), all 16 loads in flight at once.
+template <int R, int C> struct WItem {
+    uint4 w[C][R];
+    float s[C][R];
+    int row0;  // global first row
 };
 
-template <int PLANES> struct XTile {
-    uint4 lo[PLANES];
-    uint4 hi[PLANES];
-    float xs;
-    int bias;
-};
-
-struct WTile {
-    uint4 w[kRows];
-    float s[kRows];
-    int row0;   // global first row of the tile
-    int b;      // block index of this lane (may be >= nb: lane idle)
-};
-
-__device__ __forceinline__ void locate(const GemvParams& p, int grow, const uint8_t*& nib, const float*& sc, int& lrow,
-                                       int& lend) {
-    if (grow < p.row_end[0]) {
-        nib = p.nib[0]; sc = p.sc[0]; lrow = grow; lend = p.row_end[0];
-    } else if (grow < p.row_end[1]) {
-        nib = p.nib[1]; sc = p.sc[1]; lrow = grow - p.row_end[0]; lend = p.row_end[1] - p.row_end[0];
-    } else {
-        nib = p.nib[2]; sc = p.sc[2]; lrow = grow - p.row_end[1]; lend = p.row_end[2] - p.row_end[1];
-    }
-}
-
-__device__ __forceinline__ void load_wtile(const GemvParams& p, int tile, int s, int lane, WTile& t) {
-    t.row0 = tile * kRows;
-    t.b = s * kWarp + lane;
+template <int R, int C>
+__device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg, int lane, WItem<R, C>& t) {
+    t.row0 = tile * R;
     const uint8_t* nib;
     const float* sc;
     int lrow, lend;
     locate(p, t.row0, nib, sc, lrow, lend);
-    const bool lane_ok = t.b < p.nb;
 #pragma unroll
-    for (int r = 0; r < kRows; r++) {
+    for (int r = 0; r < R; r++) {
         // rows past the end of a matrix are clamped for the load and discarded at the store
-        const int row = min(lrow + r, lend - 1);
-        if (lane_ok) {
-            t.w[r] = ld_stream_u4(nib + (static_cast<long long>(row) * p.nb + t.b) * 16);
-            t.s[r] = ld_stream_f32(sc + static_cast<long long>(row) * p.nb + t.b);
-        } else {
-            t.w[r] = make_uint4(0, 0, 0, 0);
-            t.s[r] = 0.0f;
-        }
-    }
-}
-
-template <int PLANES> __device__ __forceinline__ int block_dot(const uint4& w, const XTile<PLANES>& x) {
-    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
-    if constexpr (PLANES == 1) {
-        const int xl[4] = {(int)x.lo[0].x, (int)x.lo[0].y, (int)x.lo[0].z, (int)x.lo[0].w};
-        const int xh[4] = {(int)x.hi[0].x, (int)x.hi[0].y, (int)x.hi[0].z, (int)x.hi[0].w};
-        int acc = 0;
+        const long long rb = static_cast<long long>(min(lrow + r, lend - 1)) * p.nb;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            acc = dp4a_us(wv[j] & 0x0F0F0F0Fu, xl[j], acc);
-            acc = dp4a_us((wv[j] >> 4) & 0x0F0F0F0Fu, xh[j], acc);
-        }
-        return acc - x.bias;
-    } else {
-        // plane 0: unsigned low bytes, plane 1: signed high bytes of the 16-bit fixed-point activations
-        const uint32_t l0[4] = {x.lo[0].x, x.lo[0].y, x.lo[0].z, x.lo[0].w};
-        const uint32_t h0[4] = {x.hi[0].x, x.hi[0].y, x.hi[0].z, x.hi[0].w};
-        const int l1[4] = {(int)x.lo[1].x, (int)x.lo[1].y, (int)x.lo[1].z, (int)x.lo[1].w};
-        const int h1[4] = {(int)x.hi[1].x, (int)x.hi[1].y, (int)x.hi[1].z, (int)x.hi[1].w};
-        int acc_lo = 0, acc_hi = 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t nl = wv[j] & 0x0F0F0F0Fu;
-            const uint32_t nh = (wv[j] >> 4) & 0x0F0F0F0Fu;
-            acc_lo = dp4a_uu(nl, l0[j], acc_lo);
-            acc_lo = dp4a_uu(nh, h0[j], acc_lo);
-            acc_hi = dp4a_us(nl, l1[j], acc_hi);
-            acc_hi = dp4a_us(nh, h1[j], acc_hi);
-        }
-        return acc_hi * 256 + acc_lo - x.bias;
-    }
-}
-
-// Shared-memory layout: planes[PLANES][2][nbp] uint4, xs[nbp] f32, bias[nbp] i32, part[kPartFloats] f32
-template <int PLANES> struct Smem {
-    uint4* plane;  // index ((pl * 2 + half) * nbp + b)
-    float* xs;
-    int* bias;
-    float* part;
-    int nbp;
-    __device__ Smem(unsigned char* base, int nbp_) : nbp(nbp_) {
-        plane = reinterpret_cast<uint4*>(base);
-        xs = reinterpret_cast<float*>(plane + static_cast<size_t>(PLANES) * 2 * nbp);
-        bias = reinterpret_cast<int*>(xs + nbp);
-        part = reinterpret_cast<float*>(bias + nbp);
-    }
-};
-
-static size_t gemv_smem_bytes(int planes, int S) {
-    const size_t nbp = static_cast<size_t>(S) * kWarp;
-    return nbp * (32 * planes + 8) + kPartFloats * sizeof(float);
-}
-
-// Stage the caller's int8 codes (W4A8).
-__device__ __forceinline__ void stage_q8(const GemvParams& p, Smem<1>& sm) {
-    for (int b = threadIdx.x; b < sm.nbp; b += blockDim.x) {
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        float xs = 0.0f;
-        int bias = 0;
-        if (b < p.nb) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.xq + static_cast<long long>(b) * 32);
-            lo = src[0];
-            hi = src[1];
-            xs = p.xs != nullptr ? p.xs[b] : 1.0f;
-            int sum = 0;
-            sum = __dp4a((int)lo.x, 0x01010101, sum); sum = __dp4a((int)lo.y, 0x01010101, sum);
-            sum = __dp4a((int)lo.z, 0x01010101, sum); sum = __dp4a((int)lo.w, 0x01010101, sum);
-            sum = __dp4a((int)hi.x, 0x01010101, sum); sum = __dp4a((int)hi.y, 0x01010101, sum);
-            sum = __dp4a((int)hi.z, 0x01010101, sum); sum = __dp4a((int)hi.w, 0x01010101, sum);
-            bias = 8 * sum;
-        }
-        sm.plane[b] = lo;
-        sm.plane[sm.nbp + b] = hi;
-        sm.xs[b] = xs;
-        sm.bias[b] = bias;
-    }
-}
-
-// ---- chunk-wise staging -------------------------------------------------------------------------------
-// A chunk is 8 consecutive activations held by one thread; the 4 threads of a quad hold one 32-wide block.
-// Plane words of chunk c = 4b + j: half j/2 of block b, bytes (j%2)*8 .. (j%2)*8+7 of that 16-byte half.
-
-template <int PLANES> __device__ __forceinline__ void store_chunk_planes(Smem<PLANES>& sm, int c, int pl, uint32_t w0,
-                                                                        uint32_t w1) {
-    const int b = c >> 2, j = c & 3;
-    uint2* dst = reinterpret_cast<uint2*>(&sm.plane[(pl * 2 + (j >> 1)) * sm.nbp + b]);
-    dst[j & 1] = make_uint2(w0, w1);
-}
-
-// W4A8 codes from 8 already-rounded 16-bit values per thread (same arithmetic as the stand-alone quantizer:
-// scale = amax > 0 ? amax/127 : 1 ; q = clamp(rint(v * (1/scale)), -127, 127)).
-__device__ __forceinline__ void stage_chunk_q8(Smem<1>& sm, int c, const float (&v)[8], bool active) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-    const float inv = __fdiv_rn(1.0f, scale);
-    uint32_t w0 = 0, w1 = 0;
-    int sum = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        int q = __float2int_rn(__fmul_rn(v[e], inv));
-        q = max(-127, min(127, q));
-        sum += q;
-        const uint32_t byte = static_cast<uint32_t>(q) & 0xFFu;
-        if (e < 4) w0 |= byte << (8 * e);
-        else w1 |= byte << (8 * (e - 4));
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (active) {
-        store_chunk_planes<1>(sm, c, 0, w0, w1);
-        if ((c & 3) == 0) {
-            sm.xs[c >> 2] = scale;
-            sm.bias[c >> 2] = 8 * sum;
-        }
-    }
-}
-
-// W4A16: 16-bit fixed-point planes from 8 f32 values per thread.
-//   amax = max|xe| over the block ; scale = amax > 0 ? amax / 32767 : 1 ; v = clamp(rint(xe * (1/scale)), +-32767)
-//   low plane = v & 0xFF (unsigned), high plane = v >> 8 (signed) ; bias = 8 * sum(v)
-// A non-finite amax makes the scale NaN so that the affected outputs are NaN, as an f32 path would give.
-__device__ __forceinline__ void stage_chunk_x16(Smem<2>& sm, int c, const float (&xe)[8], bool active) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(xe[e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    float scale = amax > 0.0f ? __fdiv_rn(amax, 32767.0f) : 1.0f;
-    if (!(amax <= 3.0e38f)) scale = __int_as_float(0x7FC00000);
-    const float inv = __fdiv_rn(1.0f, scale);
-    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;
-    int sum = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        int q = __float2int_rn(__fmul_rn(xe[e], inv));
-        q = max(-32767, min(32767, q));
-        sum += q;
-        const uint32_t lo8 = static_cast<uint32_t>(q) & 0xFFu;
-        const uint32_t hi8 = static_cast<uint32_t>(q >> 8) & 0xFFu;
-        if (e < 4) { l0 |= lo8 << (8 * e); h0 |= hi8 << (8 * e); }
-        else { l1 |= lo8 << (8 * (e - 4)); h1 |= hi8 << (8 * (e - 4)); }
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (active) {
-        store_chunk_planes<2>(sm, c, 0, l0, l1);
-        store_chunk_planes<2>(sm, c, 1, h0, h1);
-        if ((c & 3) == 0) {
-            sm.xs[c >> 2] = scale;
-            sm.bias[c >> 2] = 8 * sum;
-        }
-    }
-}
-
-__device__ __forceinline__ void load8(const uint16_t* p, int c, uint16_t (&h)[8]) {
-    const uint4 raw = reinterpret_cast<const uint4*>(p)[c];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        h[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
-        h[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
-    }
-}
-
-// Zero the padding blocks [nb, nbp) so that idle lanes contribute exactly 0.
-template <int PLANES> __device__ __forceinline__ void zero_padding(const GemvParams& p, Smem<PLANES>& sm) {
-    for (int b = p.nb + threadIdx.x; b < sm.nbp; b += blockDim.x) {
-#pragma unroll
-        for (int q = 0; q < PLANES * 2; q++) sm.plane[q * sm.nbp + b] = make_uint4(0, 0, 0, 0);
-        sm.xs[b] = 0.0f;
-        sm.bias[b] = 0;
-    }
-}
-
-// Stage the activations.  PRO = 0: the caller's vector (int8 codes for W4A8, 16-bit values for W4A16).
-// PRO = 1: RMSNorm of the caller's 16-bit vector first, in the library's fixed order (256 threads; thread t
-// adds x^2 over the 8-element chunks t, t+256, ... ; xor butterfly per warp; warp sums added in ascending
-// order; r = 1/sqrt(sum/n + eps); o = round16((x*r)*w)), then quantised exactly as the separate kernels do.
-template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_activations(const GemvParams& p,
-                                                                                           Smem<PLANES>& sm) {
-    zero_padding<PLANES>(p, sm);
-    if constexpr (PLANES == 1 && PRO == 0) {
-        stage_q8(p, sm);
-        return;
-    } else {
-        const uint16_t* x = static_cast<const uint16_t*>(p.x16);
-        const int chunks = p.K >> 3;
-        float r = 1.0f;
-        if constexpr (PRO == 1) {
-            __shared__ float warp_part[kGemvThreads / 32];
-            float acc = 0.0f;
-            for (int c = threadIdx.x; c < chunks; c += kGemvThreads) {
-                uint16_t h[8];
-                load8(x, c, h);
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float v = Act16<XDT>::to_f32(h[e]);
-                    acc = __fmaf_rn(v, v, acc);
-                }
+        for (int c = 0; c < C; c++) {
+            const int b = (cg * C + c) * kWarp + lane;
+            if (b < p.nb) {
+                t.w[c][r] = ld_stream_u4(nib + (rb + b) * 16);
+                t.s[c][r] = ld_stream_f32(sc + rb + b);
+            } else {
+                t.w[c][r] = make_uint4(0, 0, 0, 0);
+                t.s[c][r] = 0.0f;
             }
-            acc = warp_sum(acc);
-            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
-            __syncthreads();
-            float total = warp_part[0];
-#pragma unroll
-            for (int w = 1; w < kGemvThreads / 32; w++) total = __fadd_rn(total, warp_part[w]);
-            r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.K)), p.eps)));
-        }
-        const int iters = (chunks + kGemvThreads - 1) / kGemvThreads;
-        for (int it = 0; it < iters; it++) {
-            const int c = it * kGemvThreads + threadIdx.x;
-            const bool active = c < chunks;
-            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (active) {
-                uint16_t h[8];
-                load8(x, c, h);
-                if constexpr (PRO == 1) {
-                    uint16_t hw[8];
-                    load8(static_cast<const uint16_t*>(p.norm_w), c, hw);
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        const float o = __fmul_rn(__fmul_rn(Act16<XDT>::to_f32(h[e]), r), Act16<XDT>::to_f32(hw[e]));
-                        v[e] = Act16<XDT>::to_f32(Act16<XDT>::from_f32(o));
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) v[e] = Act16<XDT>::to_f32(h[e]);
-                }
-                if constexpr (PLANES == 2) {
-                    if (p.awq != nullptr) {
-#pragma unroll
-                        for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
-                    }
-                }
-            }
-            if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);
-            else stage_chunk_x16(sm, c, v, active);
         }
     }
 }
 
-template <int PLANES, int XDT, int ODT, bool IDOT, int PRO>
+template <int PLANES, int XDT, int ODT, bool IDOT, int PRO, int R, int C>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int W = blockDim.x >> 5;
+    constexpr int W = kGemvThreads / 32;
     const int S = p.S;
+    const int CG = (S + C - 1) / C;  // column groups per row
     Smem<PLANES> sm(smem_raw, S * kWarp);
 
-    const int tile_begin = static_cast<int>(static_cast<long long>(p.tiles) * blockIdx.x / gridDim.x);
-    const int tile_end = static_cast<int>(static_cast<long long>(p.tiles) * (blockIdx.x + 1) / gridDim.x);
-    const int chunk_tiles_max = max(1, kPartFloats / (kRows * S));
-    const int dt = W / S, ds = W - dt * S;  // task stride W decomposed into (tiles, column sets)
+    const int tiles = (p.n_total + R - 1) / R;
+    const int tile_begin = static_cast<int>(static_cast<long long>(tiles) * blockIdx.x / gridDim.x);
+    const int tile_end = static_cast<int>(static_cast<long long>(tiles) * (blockIdx.x + 1) / gridDim.x);
+    const int chunk_tiles_max = max(1, kPartFloats / (R * CG));
 
     // Weights do not depend on the producer kernel: start streaming them before waiting for it.
-    WTile cur, nxt;
-    int t = warp / S, s = warp - (warp / S) * S;  // position inside the current chunk
+    WItem<R, C> it;
     int chunk0 = tile_begin;
     int chunk_tiles = min(chunk_tiles_max, tile_end - chunk0);
-    if (chunk_tiles > 0 && t < chunk_tiles) load_wtile(p, chunk0 + t, s, lane, cur);
+    int q = warp;  // item index inside the chunk: tile q / CG, column group q % CG
+    if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
 
     pdl_wait();
     stage_activations<PLANES, XDT, PRO>(p, sm);
@@ -371,53 +93,55 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     pdl_launch_dependents();
 
     while (chunk_tiles > 0) {
-        while (t < chunk_tiles) {
-            // prefetch the warp's next task of this chunk
-            int tn = t + dt, sn = s + ds;
-            if (sn >= S) { sn -= S; tn++; }
-            if (tn < chunk_tiles) load_wtile(p, chunk0 + tn, sn, lane, nxt);
-
-            XTile<PLANES> x;
-            const int bs = s * kWarp + lane;  // < nbp always
+        const int n_items = chunk_tiles * CG;
+        while (q < n_items) {
+            const int tl = q / CG, cg = q - tl * CG;
+            float a[R];
 #pragma unroll
-            for (int pl = 0; pl < PLANES; pl++) {
-                x.lo[pl] = sm.plane[(pl * 2 + 0) * sm.nbp + bs];
-                x.hi[pl] = sm.plane[(pl * 2 + 1) * sm.nbp + bs];
-            }
-            x.xs = sm.xs[bs];
-            x.bias = sm.bias[bs];
-
-            float a[kRows];
+            for (int c = 0; c < C; c++) {
+                const int bs = min((cg * C + c), S - 1) * kWarp + lane;  // < nbp; idle column sets carry zero weights
+                XTile<PLANES> x;
 #pragma unroll
-            for (int r = 0; r < kRows; r++) {
-                const int I = block_dot<PLANES>(cur.w[r], x);
-                if constexpr (IDOT) {
-                    const int grow = cur.row0 + r;
-                    if (grow < p.n_total && cur.b < p.nb) p.idot[static_cast<long long>(grow) * p.nb + cur.b] = I;
-                    a[r] = 0.0f;
-                } else {
-                    a[r] = __fmul_rn(__fmul_rn(cur.s[r], x.xs), static_cast<float>(I));
+                for (int pl = 0; pl < PLANES; pl++) {
+                    x.lo[pl] = sm.plane[(pl * 2 + 0) * sm.nbp + bs];
+                    x.hi[pl] = sm.plane[(pl * 2 + 1) * sm.nbp + bs];
+                }
+                x.xs = sm.xs[bs];
+                x.bias = sm.bias[bs];
+                const bool live = (cg * C + c) < S;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int I = block_dot<PLANES>(it.w[c][r], x);
+                    if constexpr (IDOT) {
+                        const int grow = it.row0 + r;
+                        const int b = (cg * C + c) * kWarp + lane;
+                        if (live && grow < p.n_total && b < p.nb) p.idot[static_cast<long long>(grow) * p.nb + b] = I;
+                        a[r] = 0.0f;
+                    } else {
+                        // per lane the C column sets of the group are added in ascending order, first term exact
+                        const float v = live ? __fmul_rn(__fmul_rn(it.s[c][r], x.xs), static_cast<float>(I)) : 0.0f;
+                        a[r] = (c == 0) ? v : __fadd_rn(a[r], v);
+                    }
                 }
             }
+            // issue the next item's loads before reducing this one
+            const int qn = q + W;
+            if (qn < n_items) load_item<R, C>(p, chunk0 + qn / CG, qn % CG, lane, it);
             if constexpr (!IDOT) {
-                warp_sum_multi<kRows>(a, lane);
-                if (multi_row_writer<kRows>(lane)) {
-                    sm.part[(t * kRows + multi_row_of<kRows>(lane)) * S + s] = a[0];
-                }
+                warp_sum_multi<R>(a, lane);
+                if (multi_row_writer<R>(lane)) sm.part[(tl * R + multi_row_of<R>(lane)) * CG + cg] = a[0];
             }
-            cur = nxt;
-            t = tn;
-            s = sn;
+            q = qn;
         }
         __syncthreads();
         if constexpr (!IDOT) {
-            // add the column-set partials of every row of the chunk in ascending order, then store
-            const int rows = chunk_tiles * kRows;
-            for (int i = threadIdx.x; i < rows; i += blockDim.x) {
-                const int grow = chunk0 * kRows + i;
+            // add the column-group partials of every row of the chunk in ascending order, then store
+            const int rows = chunk_tiles * R;
+            for (int i = threadIdx.x; i < rows; i += kGemvThreads) {
+                const int grow = chunk0 * R + i;
                 if (grow >= p.n_total) continue;
-                float y = sm.part[i * S];
-                for (int c = 1; c < S; c++) y += sm.part[i * S + c];
+                float y = sm.part[i * CG];
+                for (int c = 1; c < CG; c++) y = __fadd_rn(y, sm.part[i * CG + c]);
                 void* out;
                 const void* res;
                 int lrow;
@@ -438,9 +162,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
         chunk0 += chunk_tiles;
         chunk_tiles = min(chunk_tiles_max, tile_end - chunk0);
         __syncthreads();
-        t = warp / S;
-        s = warp - t * S;
-        if (chunk_tiles > 0 && t < chunk_tiles) load_wtile(p, chunk0 + t, s, lane, cur);
+        q = warp;
+        if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
     }
 }
 
@@ -458,6 +181,7 @@ __global__ void gemv_w4_unaligned_kernel(const GemvParams p) {
     void* out = grow < p.row_end[0] ? p.out[0] : (grow < p.row_end[1] ? p.out[1] : p.out[2]);
     const void* res = grow < p.row_end[0] ? p.res[0] : (grow < p.row_end[1] ? p.res[1] : p.res[2]);
     float y = 0.0f;
+    float a = 0.0f;
     for (int s = 0; s < p.S; s++) {
         const int b = s * kWarp + lane;
         float v = 0.0f;
@@ -496,8 +220,13 @@ __global__ void gemv_w4_unaligned_kernel(const GemvParams p) {
             }
             v = __fmul_rn(__fmul_rn(sc[static_cast<long long>(lrow) * p.nb + b], xs), static_cast<float>(I));
         }
-        v = warp_sum(v);
-        y = (s == 0) ? v : y + v;
+        // same order as the main kernel: per lane the column sets of a group of four in ascending order,
+        // xor butterfly over the lanes, then the groups in ascending order
+        a = ((s & 3) == 0) ? v : __fadd_rn(a, v);
+        if ((s & 3) == 3 || s == p.S - 1) {
+            const float part = warp_sum(a);
+            y = (s < 4) ? part : __fadd_rn(y, part);
+        }
     }
     if (lane == 0) {
         if (res != nullptr) {
@@ -513,7 +242,7 @@ __global__ void gemv_w4_unaligned_kernel(const GemvParams p) {
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-template <typename Kern> static int launch_gemv(Kern kern, const GemvParams& p, int planes, cudaStream_t stream) {
+template <typename Kern> static int launch_gemv(Kern kern, const GemvParams& p, int planes, int rows_per_item, cudaStream_t stream) {
     const size_t smem = gemv_smem_bytes(planes, p.S);
     if (smem > static_cast<size_t>(kMaxGemvSmem)) return set_status(NVE_ERR_TOO_LARGE);
     if (smem > 48 * 1024) {
@@ -521,7 +250,8 @@ template <typename Kern> static int launch_gemv(Kern kern, const GemvParams& p, 
         if (st != NVE_OK) return st;
     }
     int grid = 2 * sm_count();
-    if (grid > p.tiles) grid = p.tiles;
+    const int tiles = (p.n_total + rows_per_item - 1) / rows_per_item;
+    if (grid > tiles) grid = tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kGemvThreads);
@@ -548,7 +278,12 @@ static bool all_aligned(const GemvParams& p, int num_mats, int planes, int pro) 
 }
 
 template <int PLANES, int XDT, int ODT, int PRO> static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
-    if (all_aligned(p, num_mats, PLANES, PRO)) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO>, p, PLANES, st);
+    if (all_aligned(p, num_mats, PLANES, PRO)) {
+        // 8 blocks per lane and item: 2 rows x 4 column sets, or more rows when a row has fewer column sets
+        if (p.S >= 3) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 2, 4>, p, PLANES, 2, st);
+        if (p.S == 2) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 4, 2>, p, PLANES, 4, st);
+        return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 8, 1>, p, PLANES, 8, st);
+    }
     if constexpr (PRO != 0) {
         return set_status(NVE_ERR_BAD_ALIGNMENT);  // the fused prologue needs 16-byte aligned vectors
     } else {
@@ -576,8 +311,8 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
         if (m < num_mats) {
             if (mats[m].N <= 0) return NVE_ERR_BAD_SHAPE;
             if (!mats[m].nibbles || !mats[m].scales || !mats[m].out) return NVE_ERR_BAD_POINTER;
-            // a 4-row tile must not straddle two matrices
-            if (num_mats > 1 && m + 1 < num_mats && (mats[m].N % kRows) != 0) return NVE_ERR_BAD_SHAPE;
+            // a row tile (up to 8 rows) must not straddle two matrices
+            if (num_mats > 1 && m + 1 < num_mats && (mats[m].N % 8) != 0) return NVE_ERR_BAD_SHAPE;
             total += mats[m].N;
             p.nib[m] = mats[m].nibbles; p.sc[m] = mats[m].scales; p.out[m] = mats[m].out; p.res[m] = mats[m].residual;
         } else {
@@ -590,7 +325,6 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.K = K;
     p.nb = K / kBlockK;
     p.S = (p.nb + kWarp - 1) / kWarp;
-    p.tiles = (p.n_total + kRows - 1) / kRows;
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.awq = nullptr; p.idot = nullptr;
     p.norm_w = nullptr; p.eps = 0.0f;
     return NVE_OK;
@@ -636,7 +370,7 @@ extern "C" int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int3
     p.xq = xq;
     p.xs = nullptr;
     p.idot = I;
-    return launch_gemv(gemv_w4_kernel<1, NVE_DT_F16, NVE_DT_F32, true, 0>, p, 1, static_cast<cudaStream_t>(stream));
+    return launch_gemv(gemv_w4_kernel<1, NVE_DT_F16, NVE_DT_F32, true, 0, 2, 4>, p, 1, 2, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_rmsnorm_matvec_w4a8_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
@@ -696,7 +430,7 @@ extern "C" void nve_qkv_matvec_w4a16(const uint16_t* x, const uint8_t* q_nibbles
                                {v_nibbles, v_scales, v_out, nullptr, Nv}};
     // One launch when the three matrices share the activation multiplier and tile cleanly; otherwise three.
     const bool same_awq = (q_awq == k_awq) && (k_awq == v_awq);
-    if (same_awq && Nq > 0 && Nk > 0 && Nv > 0 && (Nq % kRows) == 0 && (Nk % kRows) == 0) {
+    if (same_awq && Nq > 0 && Nk > 0 && Nv > 0 && (Nq % 8) == 0 && (Nk % 8) == 0) {
         nve_b200_matvec_w4a16_multi(x, NVE_DT_F16, q_awq, m, 3, K, NVE_DT_F16, stream);
         return;
     }

@@ -610,8 +610,10 @@ void orc_w4a8_matvec_mt(const int8_t* xq, const float* xs, const uint8_t* nibble
 /* Restatement of the CUDA library's own f32 summation order (bit-level checks) */
 /* ------------------------------------------------------------------------- */
 
-/* The library adds the 32 lane values of one (row, 32-block column set) with a xor butterfly
- * (pairs l^16, then ^8, ^4, ^2, ^1) and then adds the column-set partials in ascending order. */
+/* The library's summation order for one row: a column set is 32 consecutive blocks, lane l owns block l of
+ * it; per lane the column sets of a group of four are added in ascending order (first term exact); the 32
+ * lane values of a group are added with a xor butterfly (pairs l^16, then ^8, ^4, ^2, ^1); the groups are
+ * added in ascending order. */
 static float lane_tree32(const float* v) {
     float a[32];
     memcpy(a, v, sizeof(a));
@@ -620,29 +622,52 @@ static float lane_tree32(const float* v) {
     return a[0];
 }
 
-/* W4A8 GEMV with the library's order: v = (wsc*xs) * (float)I per block (two roundings), lane tree per
- * column set, ascending sum over column sets.  The integer part is cuda/nve_kernels.cu:817-862. */
+/* blockval(ctx, b) returns the f32 value of block b of the current row. */
+typedef float (*orc_blockval_fn)(void* ctx, long b);
+
+static float b200_row_sum(orc_blockval_fn fn, void* ctx, long nb) {
+    long S = (nb + 31) / 32;
+    float tot = 0.0f;
+    for (long g0 = 0; g0 < S; g0 += 4) {
+        float lane[32];
+        for (int l = 0; l < 32; l++) {
+            float a = 0.0f;
+            for (long s = g0; s < g0 + 4 && s < S; s++) {
+                long b = s * 32 + l;
+                float v = b < nb ? fn(ctx, b) : 0.0f;
+                a = (s == g0) ? v : a + v;
+            }
+            lane[l] = a;
+        }
+        float part = lane_tree32(lane);
+        tot = (g0 == 0) ? part : tot + part;
+    }
+    return tot;
+}
+
+typedef struct {
+    const int8_t* xq;
+    const float* xs;
+    const uint8_t* nibbles;
+    const float* wsc;
+    long n, nb;
+} b200_w4a8_ctx;
+
+static float b200_w4a8_block(void* p, long b) {
+    b200_w4a8_ctx* c = (b200_w4a8_ctx*)p;
+    int32_t I = 0;
+    for (int e = 0; e < Q4_BLOCK; e++) I += gpu_q(c->nibbles, c->n, c->nb, b, e) * (int32_t)c->xq[b * Q4_BLOCK + e];
+    return (c->wsc[c->n * c->nb + b] * c->xs[b]) * (float)I;
+}
+
+/* W4A8 GEMV with the library's order: v = (wsc*xs) * (float)I per block (two roundings), summed as above.
+ * The integer part is cuda/nve_kernels.cu:817-862. */
 void orc_w4a8_matvec_b200(const int8_t* xq, const float* xs, const uint8_t* nibbles, const float* wsc, long N, long K,
                           float* y) {
-    long nb = K / Q4_BLOCK;
-    long S = (nb + 31) / 32;
+    b200_w4a8_ctx c = {xq, xs, nibbles, wsc, 0, K / Q4_BLOCK};
     for (long n = 0; n < N; n++) {
-        float tot = 0.0f;
-        for (long s = 0; s < S; s++) {
-            float v[32];
-            for (int l = 0; l < 32; l++) {
-                long b = s * 32 + l;
-                v[l] = 0.0f;
-                if (b < nb) {
-                    int32_t I = 0;
-                    for (int e = 0; e < Q4_BLOCK; e++) I += gpu_q(nibbles, n, nb, b, e) * (int32_t)xq[b * Q4_BLOCK + e];
-                    v[l] = (wsc[n * nb + b] * xs[b]) * (float)I;
-                }
-            }
-            float part = lane_tree32(v);
-            tot = (s == 0) ? part : tot + part;
-        }
-        y[n] = tot;
+        c.n = n;
+        y[n] = b200_row_sum(b200_w4a8_block, &c, c.nb);
     }
 }
 
@@ -669,32 +694,33 @@ void orc_x16_fixedpoint(const uint16_t* x16, long K, int is_bf16, const float* a
     }
 }
 
+typedef struct {
+    const int32_t* v16;
+    const float* xs;
+    const uint8_t* nibbles;
+    const float* wsc;
+    long n, nb;
+} b200_w4a16_ctx;
+
+static float b200_w4a16_block(void* p, long b) {
+    b200_w4a16_ctx* c = (b200_w4a16_ctx*)p;
+    int64_t I = 0;
+    for (int e = 0; e < Q4_BLOCK; e++) I += (int64_t)gpu_q(c->nibbles, c->n, c->nb, b, e) * c->v16[b * Q4_BLOCK + e];
+    return (c->wsc[c->n * c->nb + b] * c->xs[b]) * (float)(int32_t)I;
+}
+
 /* W4A16 GEMV as the library computes it: integer dot of (q-8) with the fixed-point codes, then the same
  * scaling and summation order as orc_w4a8_matvec_b200. */
 void orc_w4a16_matvec_b200(const uint16_t* x16, int is_bf16, const float* awq, const uint8_t* nibbles,
                            const float* wsc, long N, long K, float* y) {
     long nb = K / Q4_BLOCK;
-    long S = (nb + 31) / 32;
     int32_t* v16 = (int32_t*)malloc(sizeof(int32_t) * (size_t)K);
     float* xs = (float*)malloc(sizeof(float) * (size_t)nb);
     orc_x16_fixedpoint(x16, K, is_bf16, awq, v16, xs);
+    b200_w4a16_ctx c = {v16, xs, nibbles, wsc, 0, nb};
     for (long n = 0; n < N; n++) {
-        float tot = 0.0f;
-        for (long s = 0; s < S; s++) {
-            float v[32];
-            for (int l = 0; l < 32; l++) {
-                long b = s * 32 + l;
-                v[l] = 0.0f;
-                if (b < nb) {
-                    int64_t I = 0;
-                    for (int e = 0; e < Q4_BLOCK; e++) I += (int64_t)gpu_q(nibbles, n, nb, b, e) * v16[b * Q4_BLOCK + e];
-                    v[l] = (wsc[n * nb + b] * xs[b]) * (float)(int32_t)I;
-                }
-            }
-            float part = lane_tree32(v);
-            tot = (s == 0) ? part : tot + part;
-        }
-        y[n] = tot;
+        c.n = n;
+        y[n] = b200_row_sum(b200_w4a16_block, &c, nb);
     }
     free(v16);
     free(xs);
