@@ -146,3 +146,72 @@ def decode_bytes_per_token(shape: ModelShape, context: int) -> int:
     """Algorithmic HBM bytes of one decoded token: every packed weight once, the 16-bit K/V prefix once."""
     kv = 2 * shape.num_kv_heads * context * shape.head_dim * 2
     return shape.num_layers * (layer_weight_bytes(shape) + kv)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Command-line driver for one GEMV group (the analogue of the reference's cuda/bench_main.cu): used for
+# per-shape timing and as the small, bounded workload for profiler captures.
+#
+#   python -m nve_b200.bench_random --model 8b --group gateup --route w4a8 --layers 4 --reps 3 [--time]
+# ----------------------------------------------------------------------------------------------------------
+def gemv_groups(shape: ModelShape) -> Dict[str, Tuple[List[int], int]]:
+    """The four GEMV launches of a decode layer: row counts of the matrices that share one launch, and K."""
+    qd, kvd = shape.num_heads * shape.head_dim, shape.num_kv_heads * shape.head_dim
+    return {"qkv": ([qd, kvd, kvd], shape.hidden), "o": ([shape.hidden], qd),
+            "gateup": ([shape.ffn, shape.ffn], shape.hidden), "down": ([shape.hidden], shape.ffn)}
+
+
+def _main() -> None:
+    import argparse
+
+    ap = argparse.ArgumentParser(description="run one GEMV group of the synthetic decode stack")
+    ap.add_argument("--model", default="8b", choices=sorted(SHAPES))
+    ap.add_argument("--group", default="gateup", choices=["qkv", "o", "gateup", "down"])
+    ap.add_argument("--route", default="w4a8", choices=["w4a8", "w4a16"])
+    ap.add_argument("--layers", type=int, default=4, help="distinct weight sets to rotate over (keep > L2 in total)")
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
+    a = ap.parse_args()
+    from .decode_graph import CapturedSequence
+
+    ck.set_pdl(bool(a.pdl))
+    ns, k = gemv_groups(SHAPES[a.model])[a.group]
+    ws = [[make_w4(n, k, 1, 100 * li + j) for j, n in enumerate(ns)] for li in range(a.layers)]
+    x = ck.fill_normal(k, 1, 999, dtype=torch.float16)
+    xq, xs = ck.quantize_f16_q8(x)
+    outs = [torch.empty((1, n), dtype=torch.float16, device="cuda") for n in ns]
+    nbytes = sum(w4_bytes(n, k) for n in ns)
+
+    def launches(_a=None, _b=None):
+        for li in range(a.layers):
+            trip = [w.triple() for w in ws[li]]
+            if a.route == "w4a8":
+                ck.matvec_w4a8_multi(xq, xs, trip, k, outs=outs)
+            else:
+                ck.matvec_w4a16_multi(x, None, trip, k, outs=outs)
+
+    torch.cuda.synchronize()
+    if not a.time:
+        for _ in range(a.reps):
+            launches()
+        torch.cuda.synchronize()
+        print(f"{a.model} {a.group} {a.route}: {a.reps * a.layers} launches of {nbytes / 1e6:.1f} MB")
+        return
+    seq = CapturedSequence(launches)
+    for _ in range(3):
+        seq.replay(0, 1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.reps):
+        seq.replay(0, 1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a.reps * a.layers)
+    seq.destroy()
+    print(f"{a.model} {a.group} {a.route} pdl={a.pdl}: {us:.2f} us/launch, {nbytes / us / 1e3:.1f} GB/s ({nbytes / 1e6:.1f} MB)")
+
+
+if __name__ == "__main__":
+    _main()
