@@ -258,6 +258,25 @@ NVE_API int nve_b200_fill_normal(float* out, long long n, unsigned long long see
 NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long seed, unsigned long long stream_id,
                             unsigned long long first, float scale, int dtype, nve_stream_t stream);
 
+/* ---- tensor parallel (no counterpart in the reference, which is single-GPU) -------------------------------
+ * One process per GPU.  nve_b200_tp_create allocates this rank's symmetric buffer (partial sums for up to
+ * max_rows output rows, per-CTA launch counters) and returns its 64-byte CUDA IPC handle; after the handles of
+ * all ranks have been exchanged on the host, nve_b200_tp_connect(handles[world][64], rank order) maps the
+ * peers.  The *_allreduce GEMVs then compute out = [residual +] sum over ranks of (W_shard . x_shard) for a
+ * K-sharded (row-parallel) projection in ONE kernel: each CTA publishes its rows, waits (bounded) for the same
+ * CTA of every peer and adds the partials in rank order with plain peer loads, so every rank holds
+ * bit-identical results.  All ranks must issue the same sequence of *_allreduce calls with the same N.
+ * nve_b200_tp_error returns 0, or 1 + the rank whose flag a bounded wait gave up on. */
+NVE_API int nve_b200_tp_create(int rank, int world, int max_rows, void* handle_out);
+NVE_API int nve_b200_tp_connect(const void* handles);
+NVE_API int nve_b200_tp_world(void);
+NVE_API int nve_b200_tp_error(int reset);
+NVE_API int nve_b200_tp_destroy(void);
+NVE_API int nve_b200_matvec_w4a8_allreduce(const int8_t* xq, const float* xq_scales, const nve_b200_w4_matrix* mat,
+                                           int K, int out_dtype, nve_stream_t stream);
+NVE_API int nve_b200_matvec_w4a16_allreduce(const void* x, int x_dtype, const float* awq,
+                                            const nve_b200_w4_matrix* mat, int K, int out_dtype, nve_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

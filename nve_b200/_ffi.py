@@ -103,6 +103,13 @@ SIGNATURES = {
     "nve_b200_dequant_w4a16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "nve_b200_q4_quantize": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "nve_b200_q4_repack_blocks": (_I, [_P, _P, _P, _I, _I, _P]),
+    "nve_b200_tp_create": (_I, [_I, _I, _I, _P]),
+    "nve_b200_tp_connect": (_I, [_P]),
+    "nve_b200_tp_world": (_I, []),
+    "nve_b200_tp_error": (_I, [_I]),
+    "nve_b200_tp_destroy": (_I, []),
+    "nve_b200_matvec_w4a8_allreduce": (_I, [_P, _P, C.POINTER(W4Matrix), _I, _I, _P]),
+    "nve_b200_matvec_w4a16_allreduce": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _P]),
     "nve_b200_fill_normal": (_I, [_P, _LL, _ULL, _ULL, _ULL, _F, _P]),
     "nve_b200_fill_normal_16": (_I, [_P, _LL, _ULL, _ULL, _ULL, _F, _I, _P]),
 }

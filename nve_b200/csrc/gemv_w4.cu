@@ -33,6 +33,8 @@
 
 namespace nve {
 
+constexpr unsigned kTpSpinLimit = 1u << 21;  // bounded wait for a peer's flag (polls, each at least ~1 us)
+
 // One warp item: R rows x C consecutive column sets (R * C = 8 blocks per lane), all 16 loads in flight at once.
 template <int R, int C> struct WItem {
     uint4 w[C][R];
@@ -89,8 +91,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
 
     pdl_wait();
     stage_activations<PLANES, XDT, PRO>(p, sm);
+    // tensor parallel: this launch's sequence number is this CTA's own counter + 1; partial sums go to the
+    // buffer half selected by its parity (a peer can be at most one all-reduce ahead)
+    __shared__ unsigned tp_epoch_s;
+    if (p.tp.world > 1 && threadIdx.x == 0) tp_epoch_s = p.tp.flag[p.tp.rank][blockIdx.x] + 1u;
     __syncthreads();
     pdl_launch_dependents();
+    const unsigned tp_epoch = p.tp.world > 1 ? tp_epoch_s : 0u;
+    float* tp_mine = p.tp.world > 1 ? p.tp.buf[p.tp.rank] + static_cast<size_t>(tp_epoch & 1u) * p.tp.rows_cap : nullptr;
 
     while (chunk_tiles > 0) {
         const int n_items = chunk_tiles * CG;
@@ -142,6 +150,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 if (grow >= p.n_total) continue;
                 float y = sm.part[i * CG];
                 for (int c = 1; c < CG; c++) y = __fadd_rn(y, sm.part[i * CG + c]);
+                if (tp_mine != nullptr) {  // this rank's partial sum; reduced over the ranks after the last chunk
+                    tp_mine[grow] = y;
+                    continue;
+                }
                 void* out;
                 const void* res;
                 int lrow;
@@ -164,6 +176,47 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
         __syncthreads();
         q = warp;
         if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
+    }
+
+    if constexpr (!IDOT) {
+        if (p.tp.world > 1) {
+            // ---- fused all-reduce over peer memory: publish this CTA's rows, wait for the same CTA of every
+            // peer (same shapes and grid on all ranks => same row range), add the partials in rank order.
+            // Every rank adds in the same order, so the replicated result is bit-identical everywhere.
+            if (threadIdx.x == 0) {
+                __threadfence_system();
+                st_release_sys(p.tp.flag[p.tp.rank] + blockIdx.x, tp_epoch);
+            }
+            if (threadIdx.x < p.tp.world && static_cast<int>(threadIdx.x) != p.tp.rank) {
+                const unsigned* f = p.tp.flag[threadIdx.x] + blockIdx.x;
+                bool ok = false;
+                for (unsigned spin = 0; spin < kTpSpinLimit; spin++) {
+                    // counters only grow; the signed difference tolerates wrap-around
+                    if (static_cast<int>(ld_acquire_sys(f) - tp_epoch) >= 0) { ok = true; break; }
+                    __nanosleep(64);
+                }
+                if (!ok) atomicExch(p.tp.err, 1 + static_cast<int>(threadIdx.x));  // bounded wait expired: report, do not hang
+            }
+            __syncthreads();
+            const int row_lo = tile_begin * R;
+            const int row_hi = min(tile_end * R, p.n_total);
+            const size_t slot = static_cast<size_t>(tp_epoch & 1u) * p.tp.rows_cap;
+            for (int grow = row_lo + threadIdx.x; grow < row_hi; grow += kGemvThreads) {
+                float y = 0.0f;
+                for (int r = 0; r < p.tp.world; r++) {
+                    const float v = ld_relaxed_sys_f32(p.tp.buf[r] + slot + grow);
+                    y = (r == 0) ? v : __fadd_rn(y, v);
+                }
+                const void* res = p.res[0];
+                if (res != nullptr) {
+                    float yr = y;
+                    if constexpr (ODT == NVE_DT_F16) yr = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(y));
+                    if constexpr (ODT == NVE_DT_BF16) yr = Act16<NVE_DT_BF16>::to_f32(Act16<NVE_DT_BF16>::from_f32(y));
+                    y = __fadd_rn(load_out<ODT>(res, grow), yr);
+                }
+                store_out<ODT>(p.out[0], grow, y);
+            }
+        }
     }
 }
 
@@ -327,6 +380,8 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.S = (p.nb + kWarp - 1) / kWarp;
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.awq = nullptr; p.idot = nullptr;
     p.norm_w = nullptr; p.eps = 0.0f;
+    p.tp.world = 0; p.tp.rank = 0; p.tp.rows_cap = 0; p.tp.err = nullptr;
+    for (int r = 0; r < kTpMaxWorld; r++) { p.tp.buf[r] = nullptr; p.tp.flag[r] = nullptr; }
     return NVE_OK;
 }
 
@@ -403,6 +458,47 @@ extern "C" int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* no
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (act_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 1>(p, num_mats, out_dtype, cs);
     if (act_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 1>(p, num_mats, out_dtype, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+// ---- tensor-parallel GEMVs: y = all-reduce over the ranks of (W_shard . x_shard), optional residual ----------
+static int attach_tp(GemvParams& p) {
+    const TpDev& t = tp_device_ctx();
+    if (t.world < 2) return NVE_ERR_BAD_POINTER;  // no connected tensor-parallel context
+    if (p.n_total > t.rows_cap) return NVE_ERR_TOO_LARGE;
+    if (2 * sm_count() > kTpMaxCtas) return NVE_ERR_TOO_LARGE;
+    p.tp = t;
+    return NVE_OK;
+}
+
+extern "C" int nve_b200_matvec_w4a8_allreduce(const int8_t* xq, const float* xq_scales, const nve_b200_w4_matrix* mat,
+                                              int K, int out_dtype, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mat, 1, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!xq || !xq_scales) return set_status(NVE_ERR_BAD_POINTER);
+    p.xq = xq;
+    p.xs = xq_scales;
+    if (!all_aligned(p, 1, 1, 0)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    st = attach_tp(p);
+    if (st != NVE_OK) return set_status(st);
+    return dispatch_out<1, NVE_DT_F16, 0>(p, 1, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nve_b200_matvec_w4a16_allreduce(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mat,
+                                               int K, int out_dtype, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mat, 1, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!x) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = x;
+    p.awq = awq;
+    if (!all_aligned(p, 1, 2, 0)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    st = attach_tp(p);
+    if (st != NVE_OK) return set_status(st);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (x_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 0>(p, 1, out_dtype, cs);
+    if (x_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 0>(p, 1, out_dtype, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
 }
 

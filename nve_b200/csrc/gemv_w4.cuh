@@ -9,6 +9,19 @@ constexpr int kGemvThreads = 256;  // 8 warps
 constexpr int kPartFloats = 4096;  // shared-memory floats for column-set partial sums
 constexpr int kMaxGemvSmem = 200 * 1024;  // dynamic shared memory a GEMV CTA may ask for
 
+// Tensor-parallel context as the kernels see it: every rank's partial-sum buffer and flag array, mapped into
+// this process (own memory for `rank`, CUDA-IPC peer mappings for the others).  world <= 1 disables it.
+constexpr int kTpMaxWorld = 8;
+constexpr int kTpMaxCtas = 1024;
+struct TpDev {
+    int world;
+    int rank;
+    int rows_cap;                 // rows per parity slot of a partial buffer
+    float* buf[kTpMaxWorld];      // [2][rows_cap] f32 partial sums of rank r
+    unsigned* flag[kTpMaxWorld];  // [kTpMaxCtas] launch counters of rank r, one per CTA index
+    int* err;                     // local error word (0 = ok)
+};
+
 struct GemvParams {
     const uint8_t* nib[3];
     const float* sc[3];
@@ -26,6 +39,7 @@ struct GemvParams {
     const void* norm_w; // RMSNorm weight of the fused prologue (16-bit, same type as x16)
     float eps;
     int32_t* idot;      // debug: per-block integer dots [n_total, nb]
+    TpDev tp;           // all-reduce of the (single) output over the tensor-parallel ranks
 };
 
 template <int PLANES> struct XTile {
@@ -297,5 +311,8 @@ template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_ac
     }
 }
 
+
+// Device view of the process's tensor-parallel context (tp.cu); world == 0 when none is connected.
+const TpDev& tp_device_ctx();
 
 }  // namespace nve

@@ -448,6 +448,34 @@ def attn_decode_fused(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, 
                                                  num_kv_heads, head_dim, max_seq_len, float(scale), stream()))
 
 
+def matvec_w4a8_allreduce(xq: Tensor, xq_scales: Tensor, weights: Sequence, k: int, out_dtype=torch.float16,
+                          outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """Row-parallel W4A8 GEMV of one matrix with the all-reduce over the tensor-parallel ranks fused in."""
+    if len(weights) != 1:
+        raise ValueError("the fused all-reduce takes one matrix")
+    if outs is None:
+        outs = [torch.empty((1, weights[0][2]), dtype=out_dtype, device=xq.device)]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_matvec_w4a8_allreduce",
+               _lib().nve_b200_matvec_w4a8_allreduce(_ptr(xq, _Q8, "xq"), _ptr(xq_scales, torch.float32), arr, k,
+                                                     _TORCH_DT[out_dtype], stream()))
+    return list(outs)
+
+
+def matvec_w4a16_allreduce(x: Tensor, awq: Optional[Tensor], weights: Sequence, k: int, out_dtype=torch.float16,
+                           outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """Row-parallel W4A16 GEMV of one matrix with the all-reduce over the tensor-parallel ranks fused in."""
+    if len(weights) != 1:
+        raise ValueError("the fused all-reduce takes one matrix")
+    if outs is None:
+        outs = [torch.empty((1, weights[0][2]), dtype=out_dtype, device=x.device)]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_matvec_w4a16_allreduce",
+               _lib().nve_b200_matvec_w4a16_allreduce(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
+                                                      _ptr(awq, torch.float32), arr, k, _TORCH_DT[out_dtype], stream()))
+    return list(outs)
+
+
 def w4a8_idot(xq: Tensor, nibbles: Tensor, n: int, k: int) -> Tensor:
     """Exact per-block integer dots I[n, k/32] (int32)."""
     out = torch.empty((n, k // 32), dtype=torch.int32, device=xq.device)

@@ -43,8 +43,10 @@ class _LayerScratch:
 class StaticDecodeGraph:
     """One captured decode step over all layers of a GpuInferenceState."""
 
-    def __init__(self, state: GpuInferenceState, hidden_size: int, ffn_size: int, importance: Sequence[float]):
+    def __init__(self, state: GpuInferenceState, hidden_size: int, ffn_size: int, importance: Sequence[float],
+                 allreduce: bool = False):
         self.state = state
+        self.allreduce = allreduce  # tensor parallel: `state` holds this rank's shards (ffn_size is the local FFN width)
         self.hidden_size = hidden_size
         self.ffn_size = ffn_size
         self.importance = list(importance)
@@ -80,7 +82,7 @@ class StaticDecodeGraph:
 
         st = self.state
         _layer_forward_fused(self.hidden_buf, st.layer_weights[li], st, li, d_pos, d_seqlen, self.routes[li],
-                             out=self.hidden_buf, scratch=self.s)
+                             out=self.hidden_buf, scratch=self.s, allreduce=self.allreduce)
 
     def capture(self) -> None:
         """src/decode_graph.rs:138-370."""

@@ -224,10 +224,13 @@ def _fused_attention_supported(state: "GpuInferenceState") -> bool:
 
 
 def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInferenceState, layer_idx: int, d_pos: int,
-                         d_seqlen: int, use_w4a8: bool, out: Optional[Tensor] = None, scratch=None) -> Tensor:
+                         d_seqlen: int, use_w4a8: bool, out: Optional[Tensor] = None, scratch=None,
+                         allreduce: bool = False) -> Tensor:
     """Six launches per layer: [RMSNorm + q/k/v GEMV], [RoPE + KV write + attention (+ quantise)], [o_proj GEMV +
     residual], [RMSNorm + gate/up GEMV], [SiLU*up (+ quantise)], [down GEMV + residual].  `scratch` supplies
-    pre-allocated buffers (graph capture); `out` receives the new hidden state (may alias `hidden`)."""
+    pre-allocated buffers (graph capture); `out` receives the new hidden state (may alias `hidden`).  With
+    `allreduce` the weights are this rank's tensor-parallel shards and the two row-parallel GEMVs sum their output
+    over the ranks inside the kernel."""
     nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
     dev, f16 = hidden.device, torch.float16
     hidden_size = hidden.numel()
@@ -252,21 +255,22 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
         ck.rmsnorm_matvec_w4a8_multi(hidden, w.input_norm, eps, qkv_w, w.q_proj.k, outs=qkv_o)
         ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv,
                              hd, max_seq, scale, out_q=xq_a, out_scales=xs_a)
-        ck.matvec_w4a8_multi(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        gemv8 = ck.matvec_w4a8_allreduce if allreduce else ck.matvec_w4a8_multi
+        gemv8(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
         ck.rmsnorm_matvec_w4a8_multi(h1, w.post_attn_norm, eps, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
                                      outs=[gate, up])
         ck.silu_mul_quantize_q8(gate, up, xq=xq_f, scales=xs_f)
-        ck.matvec_w4a8_multi(xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
+        gemv8(xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
     else:
         ck.rmsnorm_matvec_w4a16_multi(hidden, w.input_norm, eps, w.q_proj.awq_scales, qkv_w, w.q_proj.k, outs=qkv_o)
         ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv,
                              hd, max_seq, scale)
-        ck.matvec_w4a16_multi(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        gemv16 = ck.matvec_w4a16_allreduce if allreduce else ck.matvec_w4a16_multi
+        gemv16(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
         ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
                                       [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
         ck.silu_mul_inplace(gate, up)
-        ck.matvec_w4a16_multi(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1],
-                              residuals=[h1])
+        gemv16(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
     return h1
 
 
