@@ -263,9 +263,9 @@ NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long s
  * max_rows output rows, per-CTA launch counters) and returns its 64-byte CUDA IPC handle; after the handles of
  * all ranks have been exchanged on the host, nve_b200_tp_connect(handles[world][64], rank order) maps the
  * peers.  The *_allreduce GEMVs then compute out = [residual +] sum over ranks of (W_shard . x_shard) for a
- * K-sharded (row-parallel) projection in ONE kernel: each CTA publishes its rows, waits (bounded) for the same
- * CTA of every peer and adds the partials in rank order with plain peer loads, so every rank holds
- * bit-identical results.  All ranks must issue the same sequence of *_allreduce calls with the same N.
+ * K-sharded (row-parallel) projection in ONE kernel: each CTA pushes its partial rows as {value, epoch} slots
+ * into every rank's buffer with plain 8-byte peer stores, then polls (bounded) its own buffer until the slots
+ * of its rows carry the current epoch and adds them in rank order, so every rank holds bit-identical results.  All ranks must issue the same sequence of *_allreduce calls with the same N.
  * nve_b200_tp_error returns 0, or 1 + the rank whose flag a bounded wait gave up on. */
 NVE_API int nve_b200_tp_create(int rank, int world, int max_rows, void* handle_out);
 NVE_API int nve_b200_tp_connect(const void* handles);

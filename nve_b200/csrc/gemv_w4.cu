@@ -33,7 +33,7 @@
 
 namespace nve {
 
-constexpr unsigned kTpSpinLimit = 1u << 21;  // bounded wait for a peer's flag (polls, each at least ~1 us)
+constexpr unsigned kTpSpinLimit = 1u << 22;  // bounded wait for a peer's slot (local polls of >= 32 ns each)
 
 // One warp item: R rows x C consecutive column sets (R * C = 8 blocks per lane), all 16 loads in flight at once.
 template <int R, int C> struct WItem {
@@ -91,14 +91,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
 
     pdl_wait();
     stage_activations<PLANES, XDT, PRO>(p, sm);
-    // tensor parallel: this launch's sequence number is this CTA's own counter + 1; partial sums go to the
-    // buffer half selected by its parity (a peer can be at most one all-reduce ahead)
+    // tensor parallel: this launch's epoch is this CTA's own launch counter + 1; slots of the parity it selects
+    // are used (a peer can be at most one all-reduce ahead, so two parities never collide)
     __shared__ unsigned tp_epoch_s;
-    if (p.tp.world > 1 && threadIdx.x == 0) tp_epoch_s = p.tp.flag[p.tp.rank][blockIdx.x] + 1u;
+    if (p.tp.world > 1 && threadIdx.x == 0) tp_epoch_s = p.tp.counter[blockIdx.x] + 1u;
     __syncthreads();
     pdl_launch_dependents();
-    const unsigned tp_epoch = p.tp.world > 1 ? tp_epoch_s : 0u;
-    float* tp_mine = p.tp.world > 1 ? p.tp.buf[p.tp.rank] + static_cast<size_t>(tp_epoch & 1u) * p.tp.rows_cap : nullptr;
+    const bool tp_on = p.tp.world > 1;
+    const unsigned tp_epoch = tp_on ? tp_epoch_s : 0u;
+    // offset of the plane [parity][source = this rank] inside any rank's buffer
+    const size_t tp_plane = (static_cast<size_t>(tp_epoch & 1u) * p.tp.world + p.tp.rank) * p.tp.rows_cap;
 
     while (chunk_tiles > 0) {
         const int n_items = chunk_tiles * CG;
@@ -150,8 +152,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 if (grow >= p.n_total) continue;
                 float y = sm.part[i * CG];
                 for (int c = 1; c < CG; c++) y = __fadd_rn(y, sm.part[i * CG + c]);
-                if (tp_mine != nullptr) {  // this rank's partial sum; reduced over the ranks after the last chunk
-                    tp_mine[grow] = y;
+                if (tp_on) {  // push this rank's partial sum {value, epoch} to every rank; reduced after the last chunk
+                    for (int r = 0; r < p.tp.world; r++)
+                        st_relaxed_sys_v2(p.tp.ll[r] + tp_plane + grow, __float_as_uint(y), tp_epoch);
                     continue;
                 }
                 void* out;
@@ -180,32 +183,25 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
 
     if constexpr (!IDOT) {
         if (p.tp.world > 1) {
-            // ---- fused all-reduce over peer memory: publish this CTA's rows, wait for the same CTA of every
-            // peer (same shapes and grid on all ranks => same row range), add the partials in rank order.
+            // ---- fused all-reduce: every rank has pushed (or is pushing) its partial rows into this rank's buffer;
+            // poll the local slots of this CTA's rows until they carry this epoch and add them in rank order.
             // Every rank adds in the same order, so the replicated result is bit-identical everywhere.
-            if (threadIdx.x == 0) {
-                __threadfence_system();
-                st_release_sys(p.tp.flag[p.tp.rank] + blockIdx.x, tp_epoch);
-            }
-            if (threadIdx.x < p.tp.world && static_cast<int>(threadIdx.x) != p.tp.rank) {
-                const unsigned* f = p.tp.flag[threadIdx.x] + blockIdx.x;
-                bool ok = false;
-                for (unsigned spin = 0; spin < kTpSpinLimit; spin++) {
-                    // counters only grow; the signed difference tolerates wrap-around
-                    if (static_cast<int>(ld_acquire_sys(f) - tp_epoch) >= 0) { ok = true; break; }
-                    __nanosleep(64);
-                }
-                if (!ok) atomicExch(p.tp.err, 1 + static_cast<int>(threadIdx.x));  // bounded wait expired: report, do not hang
-            }
-            __syncthreads();
+            if (threadIdx.x == 0) p.tp.counter[blockIdx.x] = tp_epoch;
             const int row_lo = tile_begin * R;
             const int row_hi = min(tile_end * R, p.n_total);
-            const size_t slot = static_cast<size_t>(tp_epoch & 1u) * p.tp.rows_cap;
+            const uint2* mine = p.tp.ll[p.tp.rank] + static_cast<size_t>(tp_epoch & 1u) * p.tp.world * p.tp.rows_cap;
             for (int grow = row_lo + threadIdx.x; grow < row_hi; grow += kGemvThreads) {
                 float y = 0.0f;
                 for (int r = 0; r < p.tp.world; r++) {
-                    const float v = ld_relaxed_sys_f32(p.tp.buf[r] + slot + grow);
-                    y = (r == 0) ? v : __fadd_rn(y, v);
+                    const uint2* slot = mine + static_cast<size_t>(r) * p.tp.rows_cap + grow;
+                    uint2 v = ld_relaxed_sys_v2(slot);
+                    for (unsigned spin = 0; v.y != tp_epoch && spin < kTpSpinLimit; spin++) {
+                        __nanosleep(32);
+                        v = ld_relaxed_sys_v2(slot);
+                    }
+                    if (v.y != tp_epoch) atomicExch(p.tp.err, 1 + r);  // bounded wait expired: report, do not hang
+                    const float part = __uint_as_float(v.x);
+                    y = (r == 0) ? part : __fadd_rn(y, part);
                 }
                 const void* res = p.res[0];
                 if (res != nullptr) {
@@ -381,7 +377,8 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.awq = nullptr; p.idot = nullptr;
     p.norm_w = nullptr; p.eps = 0.0f;
     p.tp.world = 0; p.tp.rank = 0; p.tp.rows_cap = 0; p.tp.err = nullptr;
-    for (int r = 0; r < kTpMaxWorld; r++) { p.tp.buf[r] = nullptr; p.tp.flag[r] = nullptr; }
+    p.tp.counter = nullptr;
+    for (int r = 0; r < kTpMaxWorld; r++) p.tp.ll[r] = nullptr;
     return NVE_OK;
 }
 

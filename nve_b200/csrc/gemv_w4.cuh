@@ -9,16 +9,19 @@ constexpr int kGemvThreads = 256;  // 8 warps
 constexpr int kPartFloats = 4096;  // shared-memory floats for column-set partial sums
 constexpr int kMaxGemvSmem = 200 * 1024;  // dynamic shared memory a GEMV CTA may ask for
 
-// Tensor-parallel context as the kernels see it: every rank's partial-sum buffer and flag array, mapped into
-// this process (own memory for `rank`, CUDA-IPC peer mappings for the others).  world <= 1 disables it.
+// Tensor-parallel context as the kernels see it.  Every rank owns a "low-latency" buffer of 8-byte slots
+// {f32 partial sum, u32 epoch}, indexed [parity][source rank][row]; a rank PUSHES its partial rows into the
+// buffers of all ranks (its own included) with single 8-byte stores and then polls only its own, local buffer
+// until the slots carry the current epoch.  Data and flag travel in one store, so no fence and no round trip
+// is needed.  world <= 1 disables it.
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpMaxCtas = 1024;
 struct TpDev {
     int world;
     int rank;
-    int rows_cap;                 // rows per parity slot of a partial buffer
-    float* buf[kTpMaxWorld];      // [2][rows_cap] f32 partial sums of rank r
-    unsigned* flag[kTpMaxWorld];  // [kTpMaxCtas] launch counters of rank r, one per CTA index
+    int rows_cap;                 // rows per [parity][source] plane
+    uint2* ll[kTpMaxWorld];       // rank r's buffer (own memory for `rank`, CUDA-IPC peer mappings otherwise)
+    unsigned* counter;            // local [kTpMaxCtas]: all-reduce launches seen by each CTA index
     int* err;                     // local error word (0 = ok)
 };
 

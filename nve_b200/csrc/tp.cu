@@ -1,13 +1,14 @@
-// Tensor-parallel context: one symmetric buffer per rank (partial sums + per-CTA launch counters), exported
-// with CUDA IPC and mapped by every peer, so that the row-parallel GEMVs (o_proj, down_proj) can all-reduce
-// their output inside the kernel with plain peer loads over NVLink / NVSwitch (gemv_w4.cu).
+// Tensor-parallel context: one symmetric buffer per rank ({partial sum, epoch} slots + per-CTA launch counters),
+// exported with CUDA IPC and mapped by every peer, so that the row-parallel GEMVs (o_proj, down_proj) can
+// all-reduce their output inside the kernel: partial rows are pushed to every rank with plain 8-byte peer
+// stores over NVLink / NVSwitch and each rank polls only its own memory (gemv_w4.cu).
 //
 // The reference project has no multi-GPU path; this file has no counterpart there.
 //
 // Protocol (host side, once):  every rank calls nve_b200_tp_create -> exchanges the 64-byte handles through any
 // host channel (the Python side uses torch.distributed) -> every rank calls nve_b200_tp_connect with all
 // handles in rank order.  No multicast / multimem objects are created: peers are reached with ordinary
-// loads, and every device-side wait is bounded (an expired wait sets the error word read by
+// stores, and every device-side wait is bounded (an expired wait sets the error word read by
 // nve_b200_tp_error).
 #include <string.h>
 
@@ -25,14 +26,13 @@ struct TpHost {
 };
 TpHost g_tp;
 
-constexpr size_t kFlagBytes = kTpMaxCtas * sizeof(unsigned);
-constexpr size_t kErrOffset = kFlagBytes;
-constexpr size_t kBufOffset = kFlagBytes + 256;
+// allocation: [counters kTpMaxCtas u32][error word, padded to 256 B][slots: 2 parities x world x rows_cap x 8 B]
+constexpr size_t kCounterBytes = kTpMaxCtas * sizeof(unsigned);
+constexpr size_t kErrOffset = kCounterBytes;
+constexpr size_t kBufOffset = kCounterBytes + 256;
 
 void fill_rank(TpDev& d, int r, void* base) {
-    unsigned char* b = static_cast<unsigned char*>(base);
-    d.flag[r] = reinterpret_cast<unsigned*>(b);
-    d.buf[r] = reinterpret_cast<float*>(b + kBufOffset);
+    d.ll[r] = reinterpret_cast<uint2*>(static_cast<unsigned char*>(base) + kBufOffset);
 }
 }  // namespace
 
@@ -49,7 +49,7 @@ extern "C" int nve_b200_tp_create(int rank, int world, int max_rows, void* handl
     if (world < 2 || world > kTpMaxWorld || rank < 0 || rank >= world || max_rows <= 0 || handle_out == nullptr)
         return set_status(NVE_ERR_BAD_SHAPE);
     if (g_tp.local != nullptr) return set_status(NVE_ERR_BAD_SHAPE);  // one context per process
-    const size_t bytes = kBufOffset + 2 * static_cast<size_t>(max_rows) * sizeof(float);
+    const size_t bytes = kBufOffset + 2 * static_cast<size_t>(world) * max_rows * sizeof(uint2);
     void* base = nullptr;
     cudaError_t e = cudaMalloc(&base, bytes);
     if (e == cudaSuccess) e = cudaMemset(base, 0, bytes);
@@ -69,6 +69,7 @@ extern "C" int nve_b200_tp_create(int rank, int world, int max_rows, void* handl
     g_tp.dev.rank = rank;
     g_tp.dev.rows_cap = max_rows;
     g_tp.dev.err = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + kErrOffset);
+    g_tp.dev.counter = reinterpret_cast<unsigned*>(base);
     fill_rank(g_tp.dev, rank, base);
     return set_status(NVE_OK);
 }

@@ -36,7 +36,9 @@ def _timed(fn, iters: int) -> float:
 
 
 def run(args, seed: int, model: str, context: int, workload: str) -> None:
-    from bench import ClockSampler  # the launcher script is on sys.path
+    import __main__ as bench_main  # bench.py, the launcher script
+
+    ClockSampler = bench_main.ClockSampler
 
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -131,7 +133,7 @@ def run(args, seed: int, model: str, context: int, workload: str) -> None:
         dims = proj_dims(shape)
         weight_bytes = shape.num_layers * sum(w4_bytes(n, k) for n, k in dims.values())
         per_gpu_bytes = weight_bytes / world
-        peaks_path = os.path.join(os.path.dirname(os.path.abspath(sys.modules["bench"].__file__)), "MEASURED_PEAKS.json")
+        peaks_path = os.path.join(os.path.dirname(os.path.abspath(bench_main.__file__)), "MEASURED_PEAKS.json")
         if os.path.exists(peaks_path):
             peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
         else:
@@ -144,7 +146,7 @@ def run(args, seed: int, model: str, context: int, workload: str) -> None:
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": workload, "model_shape": model, "context": context, "batch": 1,
                        "activations": "f16", "kv_cache": "f16", "parallelism": f"tp{world}",
-                       "collective": "all-reduce fused into the o_proj / down_proj GEMV kernels over CUDA-IPC peer loads",
+                       "collective": "all-reduce fused into the o_proj / down_proj GEMV kernels: 8-byte {value, epoch} peer stores over NVLink, local polling",
                        "l2_policy": "inputs larger than L2 per GPU only up to tp4: "
                                     f"{weight_bytes / world / 1e9:.2f} GB of weights streamed per GPU per step",
                        "launches_per_step": launches_per_step, "programmatic_dependent_launch": pdl,
@@ -162,7 +164,7 @@ def run(args, seed: int, model: str, context: int, workload: str) -> None:
                          "traffic": None},
             "cpu_baseline": None,
         }
-        print(json.dumps(line), flush=True)
+        bench_main.emit(line)
     dist.barrier()
     ctx.destroy()
     dist.destroy_process_group()
