@@ -258,6 +258,19 @@ NVE_API int nve_b200_fill_normal(float* out, long long n, unsigned long long see
 NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long seed, unsigned long long stream_id,
                             unsigned long long first, float scale, int dtype, nve_stream_t stream);
 
+/* Batched W4A16 GEMM for decode batches 1 < M <= 64 on the tcgen05 tensor cores: Y[M,N] = X[M,K] . W^T with the
+ * packed weights dequantised in shared memory (replaces nve_dequant_w4a16 + dense GEMM, src/gpu_layer.rs:220-239).
+ * X and Y are row-major; x_dtype f16 or bf16, y_dtype = x_dtype or f32; K % 64 == 0.  Weights are rounded to f16 as
+ * (q-8)*scale like the reference's dequantisation; bf16 activations are converted to f16 (exact up to +-65504,
+ * saturating beyond); accumulation is f32 in tensor memory.
+ * `scratch` (may be NULL) holds f32 split-K partials, which let small N fill all SMs; its size comes from
+ * nve_b200_gemm_w4a16_scratch_bytes.  nve_b200_gemm_error returns the code latched by an expired bounded wait. */
+NVE_API size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K);
+NVE_API int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
+                                int y_dtype, int M, int N, int K, void* scratch, size_t scratch_bytes,
+                                nve_stream_t stream);
+NVE_API int nve_b200_gemm_error(int reset);
+
 /* ---- tensor parallel (no counterpart in the reference, which is single-GPU) -------------------------------
  * One process per GPU.  nve_b200_tp_create allocates this rank's symmetric buffer (partial sums for up to
  * max_rows output rows, per-CTA launch counters) and returns its 64-byte CUDA IPC handle; after the handles of

@@ -476,6 +476,29 @@ def matvec_w4a16_allreduce(x: Tensor, awq: Optional[Tensor], weights: Sequence, 
     return list(outs)
 
 
+def gemm_w4a16_scratch_bytes(m: int, n: int, k: int) -> int:
+    return int(_lib().nve_b200_gemm_w4a16_scratch_bytes(m, n, k))
+
+
+def gemm_w4a16(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out_dtype=None, out: Optional[Tensor] = None,
+               scratch: Optional[Tensor] = None) -> Tensor:
+    """Batched W4A16 GEMM on the tensor cores: x [M, K] (f16/bf16), M <= 64 -> [M, n].  `scratch` (uint8/float
+    tensor of gemm_w4a16_scratch_bytes) enables split-K for small n."""
+    m = x.shape[0]
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device) if out is None else out
+    sb = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _ffi.check("nve_b200_gemm_w4a16",
+               _lib().nve_b200_gemm_w4a16(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x), _ptr(nibbles, torch.uint8),
+                                          _ptr(scales, torch.float32), _ptr(out, out_dtype, "out"), _TORCH_DT[out_dtype], m, n, k,
+                                          _ptr(scratch), sb, stream()))
+    return out
+
+
+def gemm_error(reset: bool = False) -> int:
+    return int(_lib().nve_b200_gemm_error(int(reset)))
+
+
 def w4a8_idot(xq: Tensor, nibbles: Tensor, n: int, k: int) -> Tensor:
     """Exact per-block integer dots I[n, k/32] (int32)."""
     out = torch.empty((n, k // 32), dtype=torch.int32, device=xq.device)

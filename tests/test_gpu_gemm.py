@@ -1,0 +1,78 @@
+"""GPU parity: the tcgen05 batched W4A16 GEMM against the reference's CPU semantics (q4_linear: one f32 GEMV per
+row of X, src/quantize.rs:1057-1075) on the same 16-bit-rounded activations."""
+import numpy as np
+import pytest
+
+from helpers import TOL, dev, rel_rms_err
+from oracle import np_oracle as npo
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(orc, M, N, K, seed, bf):
+    W = orc.fill_normal(N * K, seed, 1, scale=0.02).reshape(N, K)
+    nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+    X16 = orc.to_act16(orc.fill_normal(M * K, seed, 2), bf).reshape(M, K)
+    Wq = npo.unpack_gpu(nib).astype(np.float64) * np.repeat(sc.astype(np.float64), 32, axis=1)
+    ref = orc.from_act16(X16, bf).astype(np.float64) @ Wq.T
+    return nib, sc, X16, ref
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 128, 64), (16, 128, 512), (1, 256, 1024), (8, 384, 2048), (32, 1024, 4096),
+                                    (64, 512, 4096), (33, 200, 1024), (64, 4096, 4096), (16, 2048, 14336)])
+@pytest.mark.parametrize("bf", [False, True])
+def test_gemm_w4a16_tensor_core(cuda, orc, M, N, K, bf):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    dt = torch.bfloat16 if bf else torch.float16
+    nib, sc, X16, ref = _case(orc, M, N, K, 700 + M + N, bf)
+    dx, dn, ds = dev(X16, dt), dev(nib), dev(sc)
+    y32 = ck.gemm_w4a16(dx, dn, ds, N, K, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert ck.gemm_error() == 0
+    # weights and scales are rounded to the activation type (as the reference dequantises to f16): ~2^-11 (f16)
+    # or ~2^-8 (bf16) relative per weight; the f16 path stays far inside the stated tolerance, bf16 inside it
+    assert rel_rms_err(y32.cpu().numpy(), ref) < 3e-3
+    # the 16-bit output is the f32 accumulator rounded once (for bf16 that rounding alone is ~8e-3 of the RMS at
+    # 4 sigma, so the tolerance is judged on the f32 output and the 16-bit output is checked as its rounding)
+    y16 = ck.gemm_w4a16(dx, dn, ds, N, K)
+    assert torch.equal(y16, y32.to(dt))
+    if not bf:
+        assert rel_rms_err(y16.float().cpu().numpy(), ref) < TOL
+    # split-K through caller-provided scratch gives the same result within f32 reassociation
+    nbytes = ck.gemm_w4a16_scratch_bytes(M, N, K)
+    if nbytes:
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        ys = ck.gemm_w4a16(dx, dn, ds, N, K, out_dtype=torch.float32, scratch=scratch)
+        assert rel_rms_err(ys.cpu().numpy(), ref) < 3e-3
+        assert ck.gemm_error() == 0
+
+
+def test_gemm_matches_gemv_rows(cuda, orc):
+    """Row m of the batched result equals the batch-1 W4A16 GEMV of row m within tolerance (different arithmetic:
+    f16 weights on tensor cores vs the integer path)."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    M, N, K = 16, 1024, 4096
+    nib, sc, X16, ref = _case(orc, M, N, K, 801, False)
+    dx, dn, ds = dev(X16, torch.float16), dev(nib), dev(sc)
+    Y = ck.gemm_w4a16(dx, dn, ds, N, K, out_dtype=torch.float32).cpu().numpy()
+    for m in (0, 7, 15):
+        y = ck.matvec_w4a16_multi(dx[m].contiguous(), None, [(dn, ds, N)], K, out_dtype=torch.float32)[0].cpu().numpy().reshape(-1)
+        assert rel_rms_err(Y[m], y) < 3e-3
+
+
+def test_gemm_rejects_bad_arguments(cuda):
+    from nve_b200 import _ffi
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    x = torch.zeros((65, 64), dtype=torch.float16, device="cuda")
+    nib = torch.zeros((128, 32), dtype=torch.uint8, device="cuda")
+    sc = torch.zeros((128, 2), dtype=torch.float32, device="cuda")
+    with pytest.raises(_ffi.NveKernelError):
+        ck.gemm_w4a16(x, nib, sc, 128, 64)  # M > 64
+    with pytest.raises(_ffi.NveKernelError):
+        ck.gemm_w4a16(x[:8, :32].contiguous(), nib, sc, 128, 32)  # K % 64 != 0
