@@ -271,6 +271,20 @@ NVE_API int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbl
                                 nve_stream_t stream);
 NVE_API int nve_b200_gemm_error(int reset);
 
+/* Allocation-free form of nve_b200_gemm_w4a16.  No counterpart in the reference: it exists for callers that have
+ * no workspace to pass and may not allocate one -- the reference's batch > 1 call site (GpuWeight::matmul_x,
+ * src/gpu_layer.rs:220-239) only receives activations and weights and can run under CUDA-graph capture, where
+ * cudaMalloc is illegal; a latency-critical serving thread is in the same position.  The split-K partial sums go
+ * to a fixed 4 MiB array inside the library image (held on every GPU that loads the library until the process
+ * exits) instead of a caller buffer.  Same arguments and results as nve_b200_gemm_w4a16 otherwise.
+ *   - A shape whose partial sums (nve_b200_gemm_w4a16_scratch_bytes) exceed 4 MiB is refused: NVE_ERR_TOO_LARGE.
+ *   - The first call on each device resolves the array's device address and caches it; make that call before
+ *     any stream capture begins.
+ *   - All calls share the array and it keeps the previous call's contents (nothing in it needs to start at
+ *     zero); two of these GEMMs running concurrently on one GPU race on it -- keep them on one stream. */
+NVE_API int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
+                                        int y_dtype, int M, int N, int K, nve_stream_t stream);
+
 /* ---- tensor parallel (no counterpart in the reference, which is single-GPU) -------------------------------
  * One process per GPU.  nve_b200_tp_create allocates this rank's symmetric buffer (partial sums for up to
  * max_rows output rows, per-CTA launch counters) and returns its 64-byte CUDA IPC handle; after the handles of

@@ -106,6 +106,7 @@ SIGNATURES = {
     "nve_b200_gemm_w4a16_scratch_bytes": (_S, [_I, _I, _I]),
     "nve_b200_gemm_w4a16": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _S, _P]),
     "nve_b200_gemm_error": (_I, [_I]),
+    "nve_b200_gemm_w4a16_noalloc": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P]),
     "nve_b200_tp_create": (_I, [_I, _I, _I, _P]),
     "nve_b200_tp_connect": (_I, [_P]),
     "nve_b200_tp_world": (_I, []),

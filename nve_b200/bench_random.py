@@ -172,6 +172,7 @@ def _main() -> None:
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
+    ap.add_argument("--batch", type=int, default=1, help="> 1: the tcgen05 batched W4A16 GEMM with this many rows of X")
     a = ap.parse_args()
     from .decode_graph import CapturedSequence
 
@@ -183,8 +184,19 @@ def _main() -> None:
     outs = [torch.empty((1, n), dtype=torch.float16, device="cuda") for n in ns]
     nbytes = sum(w4_bytes(n, k) for n in ns)
 
+    xb = yb = scratch = None
+    if a.batch > 1:
+        xb = ck.fill_normal(a.batch * k, 1, 998, dtype=torch.float16).view(a.batch, k)
+        yb = [torch.empty((a.batch, n), dtype=torch.float16, device="cuda") for n in ns]
+        nbytes_s = max(ck.gemm_w4a16_scratch_bytes(a.batch, n, k) for n in ns)
+        scratch = torch.empty(max(nbytes_s, 16), dtype=torch.uint8, device="cuda")
+
     def launches(_a=None, _b=None):
         for li in range(a.layers):
+            if a.batch > 1:  # one GEMM per matrix of the group
+                for w, y in zip(ws[li], yb):
+                    ck.gemm_w4a16(xb, w.nibbles, w.scales, w.n, k, out=y, scratch=scratch)
+                continue
             trip = [w.triple() for w in ws[li]]
             if a.route == "w4a8":
                 ck.matvec_w4a8_multi(xq, xs, trip, k, outs=outs)
@@ -210,7 +222,9 @@ def _main() -> None:
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (a.reps * a.layers)
     seq.destroy()
-    print(f"{a.model} {a.group} {a.route} pdl={a.pdl}: {us:.2f} us/launch, {nbytes / us / 1e3:.1f} GB/s ({nbytes / 1e6:.1f} MB)")
+    flops = 2.0 * a.batch * sum(ns) * k
+    print(f"{a.model} {a.group} {a.route} batch={a.batch} pdl={a.pdl}: {us:.2f} us/group, {nbytes / us / 1e3:.1f} GB/s "
+          f"({nbytes / 1e6:.1f} MB), {flops / us / 1e6:.1f} TFLOP/s")
 
 
 if __name__ == "__main__":

@@ -27,6 +27,8 @@
 // permutation of K applied to both operands.
 // Every mbarrier wait is bounded; an expired wait latches an error code (nve_b200_gemm_error) and the CTA
 // leaves through the normal path, freeing its TMEM columns.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace nve {
@@ -477,4 +479,81 @@ extern "C" int nve_b200_gemm_error(int reset) {
         cudaMemcpyToSymbol(g_gemm_device_error, &zero, sizeof(int));
     }
     return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the batched GEMM.
+//
+// Who needs it: the reference's batch > 1 call site (GpuWeight::matmul_x) receives only the activations and the
+// weight tensors -- it has no workspace to hand down -- and it can run while a CUDA graph is being recorded,
+// where cudaMalloc is illegal; a serving thread that must not touch the allocator is in the same position.
+// For those callers the split-K partial sums live in a fixed array inside the library image instead of a
+// caller-provided buffer.
+//
+// Cost and limits: the array is kStaticScratchFloats * 4 bytes (4 MiB) of device memory on every GPU that loads
+// the library, until the process exits.  A call whose split-K partials (nve_b200_gemm_w4a16_scratch_bytes) exceed
+// it is rejected with NVE_ERR_TOO_LARGE.  All calls share the one array: two such GEMMs that overlap on the same
+// GPU (different streams) race on it; issue them on one stream.  The array keeps whatever the previous call
+// left in it; nothing in it has to start at zero, because every partial a call reads was written by that same
+// call's first kernel.
+//
+// The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+// current) and caches it; make that first call before starting any stream capture.
+// ---------------------------------------------------------------------------------------------------------
+namespace nve {
+
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(1) << 20;  // 1 Mi floats = 4 MiB
+static __device__ __align__(256) float g_gemm_static_scratch[kStaticScratchFloats];
+
+// Device address of g_gemm_static_scratch on the current device.  In host code the symbol itself is only a
+// stand-in and must never be passed to a kernel; the address comes from the runtime, once per device.
+static int static_scratch_address(float** out) {
+    static std::mutex mu;
+    static float* cached[64] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_cuda_status(e);
+    if (dev < 0 || dev >= 64) return set_status(NVE_ERR_BAD_SHAPE);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gemm_static_scratch);
+        if (e != cudaSuccess) return set_cuda_status(e);
+        if (ptr == nullptr) return set_status(NVE_ERR_BAD_POINTER);
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return NVE_OK;
+}
+
+}  // namespace nve
+
+extern "C" int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
+                                           int y_dtype, int M, int N, int K, nve_stream_t stream) {
+    if (!X || !nibbles || !scales || !Y) return set_status(NVE_ERR_BAD_POINTER);
+    if (M < 1 || M > 64 || N < 1 || K < kKBlock || (K % kKBlock) != 0) return set_status(NVE_ERR_BAD_SHAPE);
+    if (x_dtype != NVE_DT_F16 && x_dtype != NVE_DT_BF16) return set_status(NVE_ERR_BAD_DTYPE);
+    if (y_dtype != x_dtype && y_dtype != NVE_DT_F32) return set_status(NVE_ERR_BAD_DTYPE);
+    if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 4)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    const int ks = choose_ksplit(N, K, true);
+    const size_t need = ks > 1 ? static_cast<size_t>(ks) * M * N : 0;  // floats
+    if (need > kStaticScratchFloats) return set_status(NVE_ERR_TOO_LARGE);
+    float* scratch = nullptr;
+    int st = static_scratch_address(&scratch);
+    if (st != NVE_OK) return st;
+    GemmParams p;
+    p.X = static_cast<const uint16_t*>(X);
+    p.nib = nibbles;
+    p.sc = scales;
+    p.Y = Y;
+    p.M = M; p.N = N; p.K = K;
+    p.nb = K / 32;
+    p.kblocks = K / kKBlock;
+    p.ksplit = ks;
+    p.partial = scratch;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (x_dtype == NVE_DT_F16) {
+        return y_dtype == NVE_DT_F32 ? gemm_mb<false, NVE_DT_F32>(p, cs) : gemm_mb<false, NVE_DT_F16>(p, cs);
+    }
+    return y_dtype == NVE_DT_F32 ? gemm_mb<true, NVE_DT_F32>(p, cs) : gemm_mb<true, NVE_DT_BF16>(p, cs);
 }

@@ -495,6 +495,17 @@ def gemm_w4a16(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out_d
     return out
 
 
+def gemm_w4a16_noalloc(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out: Tensor) -> Tensor:
+    """Batched W4A16 GEMM for callers that cannot allocate: the caller passes input and output tensors only, the
+    split-K workspace is a fixed 4 MiB array inside the library (shapes needing more raise NVE_ERR_TOO_LARGE).
+    Calls share that array: keep them on one stream.  Make the first call on a device outside stream capture."""
+    _ffi.check("nve_b200_gemm_w4a16_noalloc",
+               _lib().nve_b200_gemm_w4a16_noalloc(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
+                                                  _ptr(nibbles, torch.uint8), _ptr(scales, torch.float32), _ptr(out, None, "out"),
+                                                  _dt(out), x.shape[0], n, k, stream()))
+    return out
+
+
 def gemm_error(reset: bool = False) -> int:
     return int(_lib().nve_b200_gemm_error(int(reset)))
 
