@@ -3,30 +3,36 @@
 // Replaces the reference's batch > 1 path, which materialises the whole weight matrix as f16 in HBM
 // (cuda/nve_kernels.cu:397-433, nve_dequant_w4a16) and then runs a dense GEMM on it
 // (src/gpu_layer.rs:220-239): 0.625 + 2 + 2 = 4.6 bytes of HBM traffic per weight instead of 0.625.
-// Here the packed weights are read once, dequantised to 16-bit in shared memory and consumed by tcgen05.mma
-// with the accumulators in tensor memory.
+// Here the packed weights are read once, dequantised to f16 in registers, written straight into tensor memory
+// and consumed from there by tcgen05.mma (A operand in TMEM), with the accumulators in tensor memory as well.
 //
-// Mapping: the 128 weight rows of a tile are the MMA M dimension, the batch is the MMA N dimension
-// (16 / 32 / 64), K advances 64 elements (one 128-byte swizzle row) per pipeline stage, 16 per instruction.
-//   D[128 x MB] (TMEM, f32) += A[128 x 64] (dequantised f16 weights, K-major, SWIZZLE_128B)
-//                            * B[MB x 64]  (f16 activations,         K-major, SWIZZLE_128B)
+// Mapping: the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), the batch is the MMA N dimension
+// (16 / 32 / 64), K advances 64 elements per pipeline stage, 16 per instruction.
+//   D[128 x MB] (TMEM, f32) += A[128 x 64] (dequantised f16 weights, TMEM: lane = row, 2 elements per column)
+//                            * B[MB x 64]  (f16 activations, shared memory, K-major, SWIZZLE_128B)
+// TMEM columns: four accumulator sets of MB columns, then 12 (MB = 64: 8) operand stages of 32 columns.  Eight to
+// twelve stages (two or three super-blocks of four K blocks) are what decouples the dequantisers from the MMA round trip (arrive -> issue -> commit -> wake-up,
+// about a microsecond): with four stages that round trip was paid once per super-block and bounded the kernel.
 // Weights are always dequantised to f16, the type the reference dequantises to; bf16 activations are converted
 // to f16 while the tile is staged (bf16 weights would cost 2^-8 per weight and leave no tolerance margin).
-// Roles in a CTA of 288 threads:
-//   warps 0-7  producers: cp.async ring of raw nibbles + scales (8 stages deep, each thread copies and later
-//              reads only its own 16 + 4 bytes, so no barrier is needed on that ring); dequantise
-//              (q-8)*scale with the f16/bf16 "magic number" trick (3 instructions per 2 weights) and store
-//              128-bit chunks into the swizzled operand stage; load and store the activation tile;
-//              fence.proxy.async; arrive on the stage's "full" mbarrier.
-//   warp 8     allocates TMEM, issues tcgen05.mma (one elected lane), tcgen05.commit -> "empty" mbarrier of
-//              the stage, and after the last K block -> the accumulator barrier.
+// Roles in a CTA of 384 threads:
+//   warps 0-7  producers: cp.async ring of raw nibbles + scales in super-stages of 256 weights per row (coalesced
+//              along K: a warp-wide copy touches 4 cache lines), one producer barrier per super-stage.  Two groups
+//              of four warps (thread = weight row = TMEM lane); per super-block group g dequantises K blocks 2g and
+//              2g+1 in one burst: (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the
+//              multiply), tcgen05.st into the stage's columns, activation tile into shared memory,
+//              tcgen05.wait::st + fence.proxy.async, one arrival per warp on each stage's "full" mbarrier.
+//   warps 8-11 issue tcgen05.mma (one lane each): warp 8+w takes K block w of every super-block into accumulator
+//              set w, tcgen05.commit -> "empty" mbarrier of the stage, and after its last K block -> the
+//              accumulator barrier.  Issuing costs a thread ~70 cycles per MMA and ~150 per commit whatever the
+//              shape, which is why four warps share it.  Warp 8 also allocates and frees the TMEM columns.
 //   warps 0-3  epilogue: tcgen05.ld (32 lanes x MB columns per warp), convert, store Y (or f32 split-K
 //              partials to scratch, reduced in fixed order by a second small kernel).
 // Inside a 64-wide K block both operands use the same fixed permutation of K inside every 8-element chunk
 // ([0,2,1,3,4,6,5,7]), which is what the cheapest nibble extraction produces; a GEMM is invariant to a
 // permutation of K applied to both operands.
-// Every mbarrier wait is bounded; an expired wait latches an error code (nve_b200_gemm_error) and the CTA
-// leaves through the normal path, freeing its TMEM columns.
+// Every mbarrier wait is bounded in time; an expired wait latches an error code (nve_b200_gemm_error) and the
+// CTA leaves through the normal path, freeing its TMEM columns.
 #include <mutex>
 
 #include "common.cuh"
@@ -35,13 +41,31 @@ namespace nve {
 
 constexpr int kTileN = 128;      // weight rows per CTA = MMA M
 constexpr int kKBlock = 64;      // K elements per pipeline stage (128 bytes of 16-bit)
-constexpr int kRawStages = 8;    // cp.async ring depth (raw nibbles + scales)
-constexpr int kOpStages = 4;     // dequantised operand stages
+constexpr int kSuper = 4;        // K blocks per raw super-stage: 256 elements = 128 contiguous nibble bytes per row
+constexpr int kRawStages = 4;    // cp.async ring depth in super-stages (two are in flight ahead of the dequantisers)
+constexpr int kStageCols = kKBlock / 2;     // TMEM columns of one A stage: two f16 per 32-bit column
+constexpr int kTmemCols = 512;   // the whole tensor memory of the SM
+constexpr int kMmaWarps = kSuper; // one per K block of a super-block, each with its own accumulator set
+// Issuing is what bounds this kernel, not the tensor pipe: with N <= 64 an MMA is a few cycles of work, but a
+// thread needs about 70 cycles per tcgen05.mma and 150 per tcgen05.commit (measured with clock64 around each),
+// whatever the instruction's shape.  Four warps therefore issue in parallel, warp w taking K block w of every
+// super-block into its own accumulator set; the epilogue sums the sets in ascending order.
+__host__ __device__ constexpr int acc_sets(int) { return kMmaWarps; }
+// super-blocks of operand stages in flight: what is left of the 512 columns, in units of 4 stages x 32 columns
+__host__ __device__ constexpr int op_slots(int mb) { return (kTmemCols - acc_sets(mb) * mb) / (kSuper * kStageCols); }
+constexpr int kMaxOpStages = 12;
 constexpr int kProducerThreads = 256;
-constexpr int kGemmThreads = kProducerThreads + 32;
-constexpr unsigned kGemmSpinLimit = 1u << 24;
+constexpr int kProducerWarps = kProducerThreads / 32;
+constexpr int kGemmThreads = kProducerThreads + 32 * kMmaWarps;
+constexpr unsigned long long kGemmWaitLimitNs = 50ull * 1000 * 1000;  // a legitimate wait lasts microseconds
 
 __device__ int g_gemm_device_error = 0;
+#ifdef NVE_GEMM_TRACE
+__device__ long long g_trace[3][64][8];
+#define TRACE(w, i, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 64) g_trace[w][i][k] = clock64(); } while (0)
+#else
+#define TRACE(w, i, k) do {} while (0)
+#endif
 
 struct GemmParams {
     const uint16_t* X;     // [M, K] 16-bit
@@ -63,23 +87,37 @@ __device__ __forceinline__ void mb_init(uint64_t* bar, unsigned count) {
 __device__ __forceinline__ void mb_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(bar)) : "memory");
 }
+__device__ __forceinline__ bool mb_try(uint32_t addr, unsigned parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded by wall time (the hardware may suspend a try_wait for a while, so an iteration count bounds nothing):
+// false after kGemmWaitLimitNs without the phase completing.
 __device__ __forceinline__ bool mb_wait(uint64_t* bar, unsigned parity) {
     const uint32_t addr = s_addr(bar);
-    for (unsigned spin = 0; spin < kGemmSpinLimit; spin++) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
+    for (int spin = 0; spin < 64; spin++)
+        if (mb_try(addr, parity)) return true;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    do {
+        for (int spin = 0; spin < 16; spin++)
+            if (mb_try(addr, parity)) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    } while (t - t0 < kGemmWaitLimitNs);
     return false;
 }
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(s_addr(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s_addr(dst)), "l"(src) : "memory");
@@ -106,12 +144,21 @@ __host__ __device__ constexpr uint32_t make_idesc(int mb, bool bf16) {
            (static_cast<uint32_t>(kTileN >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// A operand read from tensor memory (128 lanes x 8 columns = 16 f16 per row), B through a shared-memory descriptor.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive TMEM columns of this thread's lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -123,35 +170,35 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int c) {
     return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
 }
 
-// (q - 8) * scale for the two nibbles selected by `pair` = 0x000N000N-masked word, as packed 16-bit floats.
-template <bool BF16> __device__ __forceinline__ uint32_t dequant_pair(uint32_t masked, uint32_t scale2) {
-    if constexpr (BF16) {
-        // 0x4300 = 128.0 in bf16, one ulp = 1: 128 + q is exact; minus 136 gives q - 8 exactly
-        masked |= 0x43004300u;
-        __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&masked);
-        const uint32_t c136 = 0x43084308u;
-        v = __hsub2(v, *reinterpret_cast<const __nv_bfloat162*>(&c136));
-        v = __hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&scale2));
-        return *reinterpret_cast<uint32_t*>(&v);
-    } else {
-        // 0x6400 = 1024.0 in f16, one ulp = 1: 1024 + q is exact; minus 1032 gives q - 8 exactly
-        masked |= 0x64006400u;
-        __half2 v = *reinterpret_cast<const __half2*>(&masked);
-        const uint32_t c1032 = 0x64086408u;
-        v = __hsub2(v, *reinterpret_cast<const __half2*>(&c1032));
-        v = __hmul2(v, *reinterpret_cast<const __half2*>(&scale2));
-        return *reinterpret_cast<uint32_t*>(&v);
-    }
+// Dequantisation of two nibbles: 0x6400 is 1024.0 in f16 with one ulp = 1, so 1024 + q is exact once the nibble is
+// OR-ed into the low mantissa bits; subtracting 1032 gives q - 8 exactly, and one multiply by the f16 scale rounds
+// once.  (A single-FMA form needs 1.5 * scale to be exact, which costs two bits of scale precision -- measured at
+// 9e-3 of the output RMS, too close to the tolerance -- so it is not used.)
+struct DequantScale {
+    uint32_t mul2;  // half2(s, s)
+};
+__device__ __forceinline__ DequantScale make_dequant_scale(float scale) {
+    const __half2 m = __float2half2_rn(scale);
+    DequantScale d;
+    d.mul2 = *reinterpret_cast<const uint32_t*>(&m);
+    return d;
+}
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, const DequantScale& d) {
+    const uint32_t bits = (shifted & 0x000F000Fu) | 0x64006400u;
+    const uint32_t c1032 = 0x64086408u;
+    __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), *reinterpret_cast<const __half2*>(&c1032));
+    v = __hmul2(v, *reinterpret_cast<const __half2*>(&d.mul2));
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // One raw word (4 bytes = elements j..j+3 in the low nibbles, j+16..j+19 in the high nibbles) -> two low pairs
 // (e_j, e_j+2), (e_j+1, e_j+3) and two high pairs in the same pattern.
-template <bool BF16> __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t scale2, uint32_t& lo0, uint32_t& lo1,
-                                                                  uint32_t& hi0, uint32_t& hi1) {
-    lo0 = dequant_pair<BF16>(w & 0x000F000Fu, scale2);
-    lo1 = dequant_pair<BF16>((w >> 8) & 0x000F000Fu, scale2);
-    hi0 = dequant_pair<BF16>((w >> 4) & 0x000F000Fu, scale2);
-    hi1 = dequant_pair<BF16>((w >> 12) & 0x000F000Fu, scale2);
+__device__ __forceinline__ void dequant_word(uint32_t w, const DequantScale& d, uint32_t& lo0, uint32_t& lo1, uint32_t& hi0,
+                                             uint32_t& hi1) {
+    lo0 = dequant_pair(w, d);        // nibbles at bits 0-3 / 16-19
+    lo1 = dequant_pair(w >> 8, d);   // bits 8-11 / 24-27
+    hi0 = dequant_pair(w >> 4, d);   // bits 4-7 / 20-23
+    hi1 = dequant_pair(w >> 12, d);  // bits 12-15 / 28-31
 }
 
 // bf16 pair -> f16 pair.  Exact for 6.1e-5 <= |x| <= 65504 (every bf16 significand fits f16); larger magnitudes
@@ -177,16 +224,19 @@ __device__ __forceinline__ uint4 permute_chunk(uint4 x) {
 template <int MB, bool BF16, int ODT>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const GemmParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // layout: A stages | B stages | raw nibbles | raw scales | barriers
-    constexpr int kABytes = kTileN * 128;
+    // layout: B stages | raw nibbles | raw scales | barriers
     constexpr int kBBytes = MB * 128;
+    constexpr int kAccSets = acc_sets(MB);
+    constexpr int kAccCols = kAccSets * MB;     // TMEM columns [0, kAccCols): accumulators, then the operand stages
+    constexpr int kSlots = op_slots(MB);
+    constexpr int kOpStages = kSlots * kSuper;  // dequantised operand stages (A in TMEM, B in shared memory)
+    static_assert(kAccCols + kOpStages * kStageCols <= kTmemCols && kSlots >= 2 && kOpStages <= kMaxOpStages, "TMEM budget");
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* sA = smem;
-    unsigned char* sB = sA + kOpStages * kABytes;
-    unsigned char* sRawN = sB + kOpStages * kBBytes;            // [kRawStages][128 rows][32 B]
-    float* sRawS = reinterpret_cast<float*>(sRawN + kRawStages * kTileN * 32);  // [kRawStages][128][2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kRawStages * kTileN * 2);
-    uint64_t* full = bars;                  // [kOpStages], 256 arrivals
+    unsigned char* sB = smem;
+    unsigned char* sRawN = sB + kOpStages * kBBytes;            // [kRawStages][128 rows][128 B], 16-byte chunks XOR-swizzled
+    float* sRawS = reinterpret_cast<float*>(sRawN + kRawStages * kTileN * 128);  // [kRawStages][128 rows][8 scales]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kRawStages * kTileN * 8);
+    uint64_t* full = bars;                  // [kOpStages], one arrival per warp of the owning group
     uint64_t* empty = bars + kOpStages;     // [kOpStages], 1 arrival (tcgen05.commit)
     uint64_t* accum = bars + 2 * kOpStages; // 1 arrival
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kOpStages + 1);
@@ -199,18 +249,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     const int kb_begin = static_cast<int>(static_cast<long long>(p.kblocks) * split / p.ksplit);
     const int kb_end = static_cast<int>(static_cast<long long>(p.kblocks) * (split + 1) / p.ksplit);
     const int nkb = kb_end - kb_begin;
-    constexpr int kTmemCols = MB < 32 ? 32 : MB;
 
     if (tid == 0) {
         for (int i = 0; i < kOpStages; i++) {
-            mb_init(&full[i], kProducerThreads);
+            mb_init(&full[i], kProducerWarps / 2);  // the four warps of the group that owns the stage
             mb_init(&empty[i], 1);
         }
-        mb_init(accum, 1);
+        mb_init(accum, min(kMmaWarps, nkb));  // one tcgen05.commit per issuing warp that has work
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {  // TMEM allocation is warp-wide
+    if (warp == kProducerWarps) {  // TMEM allocation is warp-wide
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -220,26 +269,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp < 8) {
+    if (warp < kProducerWarps) {
         // ------------------------------------------------------------------ producers
-        const int r = tid & (kTileN - 1);  // weight row inside the tile
-        const int h = tid >> 7;            // which 32-wide quantisation block of the K block
-        const int grow = min(n0 + r, p.N - 1);
-        const uint8_t* nib_row = p.nib + static_cast<long long>(grow) * (p.K / 2);
-        const float* sc_row = p.sc + static_cast<long long>(grow) * p.nb;
-        auto issue_raw = [&](int i) {
-            if (i < nkb) {
-                const int kb = kb_begin + i;
-                const int st = i % kRawStages;
-                cp_async_16(sRawN + (static_cast<size_t>(st) * kTileN + r) * 32 + h * 16, nib_row + kb * 32 + h * 16);
-                cp_async_4(sRawS + (static_cast<size_t>(st) * kTileN + r) * 2 + h, sc_row + kb * 2 + h);
+        // Raw loading is coalesced along K: 8 lanes copy the 128 contiguous nibble bytes (256 weights) of one row,
+        // so a warp-wide cp.async touches 4 cache lines instead of 32.  16-byte chunks are XOR-swizzled by the row
+        // so that the later per-row reads are bank-conflict free.
+        const int nsb = (nkb + kSuper - 1) / kSuper;
+        auto issue_raw = [&](int sb) {
+            if (sb < nsb) {
+                const int st = sb % kRawStages;
+                const int kb0 = kb_begin + sb * kSuper;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {  // 128 rows x 8 chunks of 16 bytes
+                    const int id = tid + kProducerThreads * j;
+                    const int rr = id >> 3, c = id & 7;
+                    if (sb * kSuper + (c >> 1) < nkb) {
+                        const int grow = min(n0 + rr, p.N - 1);
+                        cp_async_16(sRawN + static_cast<size_t>(st) * (kTileN * 128) + rr * 128 + ((c ^ (rr & 7)) << 4),
+                                    p.nib + static_cast<long long>(grow) * (p.K / 2) + kb0 * 32 + c * 16);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++) {  // 128 rows x 4 K blocks x 2 scales
+                    const int id = tid + kProducerThreads * j;
+                    const int rr = id >> 2, kbi = id & 3;
+                    if (sb * kSuper + kbi < nkb) {
+                        const int grow = min(n0 + rr, p.N - 1);
+                        cp_async_8(sRawS + static_cast<size_t>(st) * (kTileN * 8) + rr * 8 + kbi * 2,
+                                   p.sc + static_cast<long long>(grow) * p.nb + (kb0 + kbi) * 2);
+                    }
+                }
             }
             cp_async_commit();
         };
-        for (int i = 0; i < kRawStages - 1; i++) issue_raw(i);
+        issue_raw(0);
+        issue_raw(1);
 
-        // activation chunks owned by this thread: chunk id = j * 8 + c, ids tid and tid + 256 (MB * 8 <= 512)
-        constexpr int kXChunks = MB * 8;
+        // Two groups of four warps; in every super-block group g dequantises K blocks 2g and 2g+1 in one burst:
+        // both waits first, then all loads, arithmetic and stores, one round of fences, two arrivals.
+        static_assert(kSuper == 4, "a group owns two K blocks of a super-block");
+        const int r = tid & (kTileN - 1);  // weight row inside the tile = TMEM lane
+        const int g = tid >> 7;            // group
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kAccCols;
+        constexpr int kXChunks = MB * 8;   // 16-byte activation chunks per K block: chunk id = row * 8 + c
+        constexpr int kXPer = (kXChunks + kTileN - 1) / kTileN;  // chunks per thread per K block
         auto load_x = [&](int i, int id) -> uint4 {
             uint4 v = make_uint4(0, 0, 0, 0);
             const int j = id >> 3, c = id & 7;
@@ -253,47 +326,109 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             return v;
         };
         pdl_wait();  // activations come from the previous kernel; weights do not
-        uint4 x0 = load_x(0, tid), x1 = load_x(0, tid + 256);
+        // Activation chunks are fetched one super-block ahead: an L2 round trip is longer than a K block takes.
+        uint4 xr[2][kXPer];
+#pragma unroll
+        for (int b2 = 0; b2 < 2; b2++)
+#pragma unroll
+            for (int m = 0; m < kXPer; m++) xr[b2][m] = load_x(2 * g + b2, r + kTileN * m);
 
         bool ok = true;
-        for (int i = 0; i < nkb && ok; i++) {
-            const int so = i % kOpStages;
-            issue_raw(i + kRawStages - 1);
-            cp_async_wait<kRawStages - 1>();  // this thread's copies for K block i have landed
-            if (i >= kOpStages) {
-                ok = mb_wait(&empty[so], static_cast<unsigned>(i / kOpStages - 1) & 1u);
-                if (!ok || *reinterpret_cast<volatile int*>(abort_flag)) {
-                    atomicCAS(&g_gemm_device_error, 0, 1);
-                    atomicExch(abort_flag, 1);
-                    ok = false;
-                    break;
+        for (int sb = 0; sb < nsb; sb++) {
+            // raw slot (sb+2) % 4 was last read for super-block sb-2, which every producer finished before passing
+            // the barrier of super-block sb-1
+            TRACE(g, sb, 0);
+            issue_raw(sb + 2);
+            TRACE(g, sb, 1);
+            cp_async_wait<2>();                               // this thread's copies of super-block sb have landed
+            TRACE(g, sb, 2);
+            asm volatile("bar.sync 2, 256;" ::: "memory");   // ... and everybody else's
+            TRACE(g, sb, 3);
+            uint4 nx[2][kXPer];
+#pragma unroll
+            for (int b2 = 0; b2 < 2; b2++)
+#pragma unroll
+                for (int m = 0; m < kXPer; m++) nx[b2][m] = load_x((sb + 1) * kSuper + 2 * g + b2, r + kTileN * m);
+            const int i0 = sb * kSuper + 2 * g;     // first K block of this group's burst
+            const int nvalid = min(2, nkb - i0);    // K blocks of the burst that exist
+            const int slot = sb % kSlots, use = sb / kSlots;
+            const int so0 = slot * kSuper + 2 * g;  // operand stage of the first K block of the burst
+            // a warp that gave up keeps attending the producer barrier above (the others would wait for it for ever)
+            // and does nothing else
+            if (ok && nvalid > 0) {
+                if (use >= 1) {
+                    // one lane polls for the warp: many threads spinning on one mbarrier word serialise
+                    bool w = true;
+                    if (lane == 0) {
+                        const unsigned par = static_cast<unsigned>(use - 1) & 1u;
+                        w = mb_wait(&empty[so0], par);
+                        if (w && nvalid > 1) w = mb_wait(&empty[so0 + 1], par);
+                    }
+                    w = __shfl_sync(0xffffffffu, w, 0);
+                    if (!w || *reinterpret_cast<volatile int*>(abort_flag)) {
+                        if (lane == 0) {
+                            atomicCAS(&g_gemm_device_error, 0, 1);
+                            atomicExch(abort_flag, 1);
+                        }
+                        ok = false;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                TRACE(g, sb, 4);
+                if (ok) {
+                    const int st = sb % kRawStages;
+                    const unsigned char* rawrow = sRawN + static_cast<size_t>(st) * (kTileN * 128) + r * 128;
+                    const float4 sc4 = *reinterpret_cast<const float4*>(sRawS + static_cast<size_t>(st) * (kTileN * 8) + r * 8 + 4 * g);
+                    const float scv[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+                    uint4 raw[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++)  // quantisation blocks 4g .. 4g+3 of the super-stage row
+                        raw[q] = *reinterpret_cast<const uint4*>(rawrow + (((4 * g + q) ^ (r & 7)) << 4));
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int b2 = q >> 1, h = q & 1;
+                        if (b2 < nvalid) {
+                            const DequantScale ds = make_dequant_scale(scv[q]);
+                            // v[0..3] = elements 0-7, v[4..7] = 8-15, v[8..11] = 16-23, v[12..15] = 24-31 of the
+                            // block, each group of four in the order (e0,e2)(e1,e3)
+                            uint32_t v[16];
+                            dequant_word(raw[q].x, ds, v[0], v[1], v[8], v[9]);
+                            dequant_word(raw[q].y, ds, v[2], v[3], v[10], v[11]);
+                            dequant_word(raw[q].z, ds, v[4], v[5], v[12], v[13]);
+                            dequant_word(raw[q].w, ds, v[6], v[7], v[14], v[15]);
+                            tmem_st16(tmem_lane + (so0 + b2) * kStageCols + 16 * h, v);
+                        }
+                    }
+                    // ---- activation tiles (same K permutation inside every chunk)
+#pragma unroll
+                    for (int b2 = 0; b2 < 2; b2++) {
+                        if (b2 < nvalid) {
+                            unsigned char* b_stage = sB + (so0 + b2) * kBBytes;
+#pragma unroll
+                            for (int m = 0; m < kXPer; m++) {
+                                const int id = r + kTileN * m;
+                                if (id < kXChunks)
+                                    *reinterpret_cast<uint4*>(b_stage + sw128_off(id >> 3, id & 7)) = permute_chunk(xr[b2][m]);
+                            }
+                        }
+                    }
+                    TRACE(g, sb, 5);
+                    // TMEM stores complete; shared-memory stores visible to the tensor core (async proxy); signal
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {  // one arrival per warp
+                        mb_arrive(&full[so0]);
+                        if (nvalid > 1) mb_arrive(&full[so0 + 1]);
+                    }
+                    TRACE(g, sb, 6);
                 }
             }
-            // ---- dequantise this thread's 32 weights -> 4 chunks of the operand row
-            const int st = i % kRawStages;
-            const uint4 raw = *reinterpret_cast<const uint4*>(sRawN + (static_cast<size_t>(st) * kTileN + r) * 32 + h * 16);
-            const float scale = sRawS[(static_cast<size_t>(st) * kTileN + r) * 2 + h];
-            const __half2 s2 = __float2half2_rn(scale);
-            const uint32_t scale2 = *reinterpret_cast<const uint32_t*>(&s2);
-            uint4 c0, c1, c2, c3;  // chunks 4h .. 4h+3 of the row
-            dequant_word<false>(raw.x, scale2, c0.x, c0.y, c2.x, c2.y);
-            dequant_word<false>(raw.y, scale2, c0.z, c0.w, c2.z, c2.w);
-            dequant_word<false>(raw.z, scale2, c1.x, c1.y, c3.x, c3.y);
-            dequant_word<false>(raw.w, scale2, c1.z, c1.w, c3.z, c3.w);
-            unsigned char* a_stage = sA + so * kABytes;
-            *reinterpret_cast<uint4*>(a_stage + sw128_off(r, 4 * h + 0)) = c0;
-            *reinterpret_cast<uint4*>(a_stage + sw128_off(r, 4 * h + 1)) = c1;
-            *reinterpret_cast<uint4*>(a_stage + sw128_off(r, 4 * h + 2)) = c2;
-            *reinterpret_cast<uint4*>(a_stage + sw128_off(r, 4 * h + 3)) = c3;
-            // ---- activation tile (same K permutation inside every chunk)
-            unsigned char* b_stage = sB + so * kBBytes;
-            if (tid < kXChunks) *reinterpret_cast<uint4*>(b_stage + sw128_off(tid >> 3, tid & 7)) = permute_chunk(x0);
-            if (tid + 256 < kXChunks) *reinterpret_cast<uint4*>(b_stage + sw128_off((tid + 256) >> 3, tid & 7)) = permute_chunk(x1);
-            x0 = load_x(i + 1, tid);
-            x1 = load_x(i + 1, tid + 256);
-            // make the generic-proxy stores visible to the tensor core (async proxy), then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mb_arrive(&full[so]);
+#pragma unroll
+            for (int b2 = 0; b2 < 2; b2++)
+#pragma unroll
+                for (int m = 0; m < kXPer; m++) xr[b2][m] = nx[b2][m];
         }
         cp_async_wait<0>();
         pdl_launch_dependents();
@@ -311,20 +446,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                 const int n = n0 + warp * 32 + lane;  // this thread's output feature
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 #pragma unroll
+                const int used = min(kAccSets, nkb);  // accumulator sets that received an MMA
                 for (int cb = 0; cb < MB; cb += 8) {
-                    uint32_t v[8];
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                                 : "r"(taddr + cb));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    float y[8];
+                    for (int a = 0; a < used; a++) {
+                        uint32_t v[8];
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                                     : "r"(taddr + a * MB + cb));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 8; j++) y[j] = a == 0 ? __uint_as_float(v[j]) : __fadd_rn(y[j], __uint_as_float(v[j]));
+                    }
                     if (n < p.N) {
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int m = cb + j;
                             if (m < p.M) {
-                                const float y = __uint_as_float(v[j]);
-                                if (p.ksplit > 1) p.partial[(static_cast<long long>(split) * p.M + m) * p.N + n] = y;
-                                else store_out<ODT>(p.Y, static_cast<long long>(m) * p.N + n, y);
+                                if (p.ksplit > 1) p.partial[(static_cast<long long>(split) * p.M + m) * p.N + n] = y[j];
+                                else store_out<ODT>(p.Y, static_cast<long long>(m) * p.N + n, y[j]);
                             }
                         }
                     }
@@ -333,46 +473,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
     } else {
-        // ------------------------------------------------------------------ MMA issuer (warp 8)
+        // ------------------------------------------------------------------ MMA issuers (last four warps)
+        // One lane per warp runs the loop: waits, fences, MMAs and commits are all single-thread operations.
         constexpr uint32_t idesc = make_idesc(MB, false);  // both operands are f16 (bf16 activations are converted)
-        bool ok = true;
-        for (int i = 0; i < nkb && ok; i++) {
-            const int so = i % kOpStages;
-            bool w = true;
-            if (lane == 0) w = mb_wait(&full[so], static_cast<unsigned>(i / kOpStages) & 1u);
-            w = __shfl_sync(0xffffffffu, w, 0);
-            if (!w || *reinterpret_cast<volatile int*>(abort_flag)) {
-                if (lane == 0) {
+        const int w = warp - kProducerWarps;               // K block of the super-block and accumulator set
+        if (lane == 0) {
+            bool issued = false;
+            for (int sb = 0; sb * kSuper + w < nkb; sb++) {
+                const int so = (sb % kSlots) * kSuper + w;
+                const bool ready = mb_wait(&full[so], static_cast<unsigned>(sb / kSlots) & 1u);
+                if (!ready || *reinterpret_cast<volatile int*>(abort_flag)) {
                     atomicCAS(&g_gemm_device_error, 0, 2);
                     atomicExch(abort_flag, 1);
+                    break;
                 }
-                ok = false;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (lane == 0) {
-                const uint64_t adesc = make_desc_k_sw128(s_addr(sA + so * kABytes));
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_tmem = tmem_base + kAccCols + so * kStageCols;
                 const uint64_t bdesc = make_desc_k_sw128(s_addr(sB + so * kBBytes));
 #pragma unroll
                 for (int kk = 0; kk < kKBlock / 16; kk++) {
-                    // 16 elements = 32 bytes further along K inside the swizzle row: +2 in 16-byte units
-                    umma_f16(tmem_base, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                    // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
+                    umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(&empty[so]);                 // stage reusable once these MMAs have read it
-                if (i == nkb - 1) umma_commit(accum);    // accumulator complete
+                umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
+                issued = true;
             }
-            __syncwarp();
+            // this warp's accumulator set is complete (on an abandoned run the epilogue is not waiting any more)
+            if (issued) umma_commit(accum);
         }
+        __syncwarp();
     }
 
     // ---- teardown: all tensor-memory traffic is finished or abandoned; free the columns
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kProducerWarps) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
+#ifdef NVE_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int nve_dbg_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8);
+}
+#endif
 // Sum the split-K partials in ascending split order and convert.
 template <int ODT> __global__ void gemm_splitk_reduce_kernel(const float* partial, void* Y, int ksplit, long long mn) {
     pdl_wait();
@@ -384,8 +528,12 @@ template <int ODT> __global__ void gemm_splitk_reduce_kernel(const float* partia
 }
 
 static size_t gemm_smem_bytes(int mb) {
-    return 1024 + static_cast<size_t>(kOpStages) * (kTileN * 128 + mb * 128) + static_cast<size_t>(kRawStages) * kTileN * (32 + 8) +
-           (2 * kOpStages + 1) * 8 + 16;
+    const size_t need = 1024 + static_cast<size_t>(op_slots(mb) * kSuper) * (mb * 128) + static_cast<size_t>(kRawStages) * kTileN * (128 + 32) +
+                        (2 * kMaxOpStages + 1) * 8 + 16;
+    // A CTA allocates all 512 TMEM columns, so a second CTA on the same SM would only sit in tcgen05.alloc until the
+    // first one ends: ask for more than half of the SM's shared memory to keep it off the SM instead.
+    const size_t half_sm = 120 * 1024;
+    return need > half_sm ? need : half_sm;
 }
 
 static int choose_ksplit(int N, int K, bool have_scratch) {
