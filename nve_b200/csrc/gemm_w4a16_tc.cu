@@ -11,21 +11,21 @@
 //   D[128 x MB] (TMEM, f32) += A[128 x 64] (dequantised f16 weights, TMEM: lane = row, 2 elements per column)
 //                            * B[MB x 64]  (f16 activations, shared memory, K-major, SWIZZLE_128B)
 // TMEM columns: four accumulator sets of MB columns, then 12 (MB = 64: 8) operand stages of 32 columns.  Eight to
-// twelve stages (two or three super-blocks of four K blocks) are what decouples the dequantisers from the MMA round trip (arrive -> issue -> commit -> wake-up,
-// about a microsecond): with four stages that round trip was paid once per super-block and bounded the kernel.
+// twelve stages (two or three super-blocks of four K blocks) decouple the dequantisers from the MMA round trip
+// (arrive -> issue -> commit -> wake-up, about a microsecond).
 // Weights are always dequantised to f16, the type the reference dequantises to; bf16 activations are converted
 // to f16 while the tile is staged (bf16 weights would cost 2^-8 per weight and leave no tolerance margin).
-// Roles in a CTA of 384 threads:
-//   warps 0-7  producers: cp.async ring of raw nibbles + scales in super-stages of 256 weights per row (coalesced
-//              along K: a warp-wide copy touches 4 cache lines), one producer barrier per super-stage.  Two groups
-//              of four warps (thread = weight row = TMEM lane); per super-block group g dequantises K blocks 2g and
-//              2g+1 in one burst: (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the
-//              multiply), tcgen05.st into the stage's columns, activation tile into shared memory,
-//              tcgen05.wait::st + fence.proxy.async, one arrival per warp on each stage's "full" mbarrier.
-//   warps 8-11 issue tcgen05.mma (one lane each): warp 8+w takes K block w of every super-block into accumulator
+// Roles in a CTA of 640 threads:
+//   warps 0-15 producers: cp.async ring of raw nibbles + scales in super-stages of 256 weights per row (coalesced
+//              along K: a warp-wide copy touches 4 cache lines), one producer barrier per super-stage.  Four groups
+//              of four warps (thread = weight row = TMEM lane); per super-block group g dequantises K block g:
+//              (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the multiply), tcgen05.st
+//              into the stage's columns, activation tile into shared memory, tcgen05.wait::st + fence.proxy.async,
+//              one arrival per warp on the stage's "full" mbarrier.
+//   warps 16-19 issue tcgen05.mma (one lane each): warp 16+w takes K block w of every super-block into accumulator
 //              set w, tcgen05.commit -> "empty" mbarrier of the stage, and after its last K block -> the
 //              accumulator barrier.  Issuing costs a thread ~70 cycles per MMA and ~150 per commit whatever the
-//              shape, which is why four warps share it.  Warp 8 also allocates and frees the TMEM columns.
+//              shape, which is why four warps share it.  Warp 16 also allocates and frees the TMEM columns.
 //   warps 0-3  epilogue: tcgen05.ld (32 lanes x MB columns per warp), convert, store Y (or f32 split-K
 //              partials to scratch, reduced in fixed order by a second small kernel).
 // Inside a 64-wide K block both operands use the same fixed permutation of K inside every 8-element chunk
@@ -54,14 +54,16 @@ __host__ __device__ constexpr int acc_sets(int) { return kMmaWarps; }
 // super-blocks of operand stages in flight: what is left of the 512 columns, in units of 4 stages x 32 columns
 __host__ __device__ constexpr int op_slots(int mb) { return (kTmemCols - acc_sets(mb) * mb) / (kSuper * kStageCols); }
 constexpr int kMaxOpStages = 12;
-constexpr int kProducerThreads = 256;
+constexpr int kGroups = 4;         // producer groups of four warps (thread = weight row = TMEM lane)
+constexpr int kBurst = kSuper / kGroups;  // K blocks a group dequantises per super-block
+constexpr int kProducerThreads = 128 * kGroups;
 constexpr int kProducerWarps = kProducerThreads / 32;
 constexpr int kGemmThreads = kProducerThreads + 32 * kMmaWarps;
 constexpr unsigned long long kGemmWaitLimitNs = 50ull * 1000 * 1000;  // a legitimate wait lasts microseconds
 
 __device__ int g_gemm_device_error = 0;
 #ifdef NVE_GEMM_TRACE
-__device__ long long g_trace[3][64][8];
+__device__ long long g_trace[5][64][8];
 #define TRACE(w, i, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 64) g_trace[w][i][k] = clock64(); } while (0)
 #else
 #define TRACE(w, i, k) do {} while (0)
@@ -91,7 +93,7 @@ __device__ __forceinline__ bool mb_try(uint32_t addr, unsigned parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(addr), "r"(parity)
@@ -115,6 +117,12 @@ __device__ __forceinline__ bool mb_wait(uint64_t* bar, unsigned parity) {
 }
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16s(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8s(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(s_addr(dst)), "l"(src) : "memory");
@@ -170,10 +178,11 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int c) {
     return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
 }
 
-// Dequantisation of two nibbles: 0x6400 is 1024.0 in f16 with one ulp = 1, so 1024 + q is exact once the nibble is
-// OR-ed into the low mantissa bits; subtracting 1032 gives q - 8 exactly, and one multiply by the f16 scale rounds
-// once.  (A single-FMA form needs 1.5 * scale to be exact, which costs two bits of scale precision -- measured at
-// 9e-3 of the output RMS, too close to the tolerance -- so it is not used.)
+// Dequantisation of two nibbles.  0x6400 is 1024.0 in f16 with one ulp = 1, so OR-ing a nibble into mantissa bits
+// 0-3 gives 1024 + q exactly; 0x5400 is 64.0 with one ulp = 1/16, so a nibble left in place at bits 4-7 gives
+// 64 + q exactly (no shift needed).  Subtracting 1032 (72) gives q - 8 exactly, and one multiply by the f16 scale
+// rounds once.  (A single-FMA form needs 1.5 * scale to be exact, which costs two bits of scale precision --
+// measured at 9e-3 of the output RMS, too close to the tolerance -- so it is not used.)
 struct DequantScale {
     uint32_t mul2;  // half2(s, s)
 };
@@ -183,10 +192,10 @@ __device__ __forceinline__ DequantScale make_dequant_scale(float scale) {
     d.mul2 = *reinterpret_cast<const uint32_t*>(&m);
     return d;
 }
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, const DequantScale& d) {
-    const uint32_t bits = (shifted & 0x000F000Fu) | 0x64006400u;
-    const uint32_t c1032 = 0x64086408u;
-    __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), *reinterpret_cast<const __half2*>(&c1032));
+template <bool HIGH> __device__ __forceinline__ uint32_t dequant_pair(uint32_t w, const DequantScale& d) {
+    const uint32_t bits = HIGH ? ((w & 0x00F000F0u) | 0x54005400u) : ((w & 0x000F000Fu) | 0x64006400u);
+    const uint32_t off = HIGH ? 0x54805480u /* 72 */ : 0x64086408u /* 1032 */;
+    __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), *reinterpret_cast<const __half2*>(&off));
     v = __hmul2(v, *reinterpret_cast<const __half2*>(&d.mul2));
     return *reinterpret_cast<const uint32_t*>(&v);
 }
@@ -195,10 +204,11 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, const Dequant
 // (e_j, e_j+2), (e_j+1, e_j+3) and two high pairs in the same pattern.
 __device__ __forceinline__ void dequant_word(uint32_t w, const DequantScale& d, uint32_t& lo0, uint32_t& lo1, uint32_t& hi0,
                                              uint32_t& hi1) {
-    lo0 = dequant_pair(w, d);        // nibbles at bits 0-3 / 16-19
-    lo1 = dequant_pair(w >> 8, d);   // bits 8-11 / 24-27
-    hi0 = dequant_pair(w >> 4, d);   // bits 4-7 / 20-23
-    hi1 = dequant_pair(w >> 12, d);  // bits 12-15 / 28-31
+    const uint32_t t = w >> 8;
+    lo0 = dequant_pair<false>(w, d);  // nibbles at bits 0-3 / 16-19
+    hi0 = dequant_pair<true>(w, d);   // bits 4-7 / 20-23
+    lo1 = dequant_pair<false>(t, d);  // bits 8-11 / 24-27
+    hi1 = dequant_pair<true>(t, d);   // bits 12-15 / 28-31
 }
 
 // bf16 pair -> f16 pair.  Exact for 6.1e-5 <= |x| <= 65504 (every bf16 significand fits f16); larger magnitudes
@@ -252,7 +262,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
     if (tid == 0) {
         for (int i = 0; i < kOpStages; i++) {
-            mb_init(&full[i], kProducerWarps / 2);  // the four warps of the group that owns the stage
+            mb_init(&full[i], 4);  // the four warps of the group that owns the stage
             mb_init(&empty[i], 1);
         }
         mb_init(accum, min(kMmaWarps, nkb));  // one tcgen05.commit per issuing warp that has work
@@ -273,51 +283,81 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         // ------------------------------------------------------------------ producers
         // Raw loading is coalesced along K: 8 lanes copy the 128 contiguous nibble bytes (256 weights) of one row,
         // so a warp-wide cp.async touches 4 cache lines instead of 32.  16-byte chunks are XOR-swizzled by the row
-        // so that the later per-row reads are bank-conflict free.
+        // so that the later per-row reads are bank-conflict free.  All addresses are set up once; the loop only
+        // advances them (the kernel is bound by instruction issue, so loop overhead counts).
         const int nsb = (nkb + kSuper - 1) / kSuper;
-        auto issue_raw = [&](int sb) {
-            if (sb < nsb) {
-                const int st = sb % kRawStages;
-                const int kb0 = kb_begin + sb * kSuper;
+        constexpr int kNibPer = 1024 / kProducerThreads;  // 128 rows x 8 chunks of 16 bytes
+        constexpr int kScPer = 512 / kProducerThreads;    // 128 rows x 4 K blocks x 2 scales
+        constexpr uint32_t kRawNStage = kTileN * 128, kRawSStage = kTileN * 8 * 4;
+        const uint8_t* gn[kNibPer];
+        uint32_t sn[kNibPer];
+        int kn[kNibPer];  // K block of the super-block that the chunk belongs to
 #pragma unroll
-                for (int j = 0; j < 4; j++) {  // 128 rows x 8 chunks of 16 bytes
-                    const int id = tid + kProducerThreads * j;
-                    const int rr = id >> 3, c = id & 7;
-                    if (sb * kSuper + (c >> 1) < nkb) {
-                        const int grow = min(n0 + rr, p.N - 1);
-                        cp_async_16(sRawN + static_cast<size_t>(st) * (kTileN * 128) + rr * 128 + ((c ^ (rr & 7)) << 4),
-                                    p.nib + static_cast<long long>(grow) * (p.K / 2) + kb0 * 32 + c * 16);
-                    }
+        for (int j = 0; j < kNibPer; j++) {
+            const int id = tid + kProducerThreads * j;
+            const int rr = id >> 3, c = id & 7;
+            const int grow = min(n0 + rr, p.N - 1);
+            gn[j] = p.nib + static_cast<long long>(grow) * (p.K / 2) + kb_begin * 32 + c * 16;
+            sn[j] = s_addr(sRawN) + rr * 128 + ((c ^ (rr & 7)) << 4);
+            kn[j] = c >> 1;
+        }
+        const float* gs[kScPer];
+        uint32_t ss[kScPer];
+        int ks[kScPer];
+#pragma unroll
+        for (int j = 0; j < kScPer; j++) {
+            const int id = tid + kProducerThreads * j;
+            const int rr = id >> 2, kbi = id & 3;
+            const int grow = min(n0 + rr, p.N - 1);
+            gs[j] = p.sc + static_cast<long long>(grow) * p.nb + (kb_begin + kbi) * 2;
+            ss[j] = s_addr(sRawS) + (rr * 8 + kbi * 2) * 4;
+            ks[j] = kbi;
+        }
+        int issue_left = nkb;  // K blocks from the next super-block to issue onwards
+        uint32_t issue_n = 0, issue_s = 0;  // byte offsets of the raw stage to fill
+        auto issue_raw = [&]() {
+            if (issue_left > 0) {
+#pragma unroll
+                for (int j = 0; j < kNibPer; j++) {
+                    if (kn[j] < issue_left) cp_async_16s(sn[j] + issue_n, gn[j]);
+                    gn[j] += kSuper * 32;
                 }
 #pragma unroll
-                for (int j = 0; j < 2; j++) {  // 128 rows x 4 K blocks x 2 scales
-                    const int id = tid + kProducerThreads * j;
-                    const int rr = id >> 2, kbi = id & 3;
-                    if (sb * kSuper + kbi < nkb) {
-                        const int grow = min(n0 + rr, p.N - 1);
-                        cp_async_8(sRawS + static_cast<size_t>(st) * (kTileN * 8) + rr * 8 + kbi * 2,
-                                   p.sc + static_cast<long long>(grow) * p.nb + (kb0 + kbi) * 2);
-                    }
+                for (int j = 0; j < kScPer; j++) {
+                    if (ks[j] < issue_left) cp_async_8s(ss[j] + issue_s, gs[j]);
+                    gs[j] += kSuper * 2;
                 }
+                issue_left -= kSuper;
+                issue_n = issue_n == (kRawStages - 1) * kRawNStage ? 0 : issue_n + kRawNStage;
+                issue_s = issue_s == (kRawStages - 1) * kRawSStage ? 0 : issue_s + kRawSStage;
             }
             cp_async_commit();
         };
-        issue_raw(0);
-        issue_raw(1);
+        issue_raw();
+        issue_raw();
 
-        // Two groups of four warps; in every super-block group g dequantises K blocks 2g and 2g+1 in one burst:
-        // both waits first, then all loads, arithmetic and stores, one round of fences, two arrivals.
-        static_assert(kSuper == 4, "a group owns two K blocks of a super-block");
+        // Groups of four warps; in every super-block group g dequantises K blocks kBurst*g .. kBurst*(g+1)-1 in one
+        // go: the waits first, then all loads, arithmetic and stores, one round of fences, one arrival per stage.
         const int r = tid & (kTileN - 1);  // weight row inside the tile = TMEM lane
         const int g = tid >> 7;            // group
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kAccCols;
         constexpr int kXChunks = MB * 8;   // 16-byte activation chunks per K block: chunk id = row * 8 + c
         constexpr int kXPer = (kXChunks + kTileN - 1) / kTileN;  // chunks per thread per K block
-        auto load_x = [&](int i, int id) -> uint4 {
-            uint4 v = make_uint4(0, 0, 0, 0);
+        const uint16_t* xp[kXPer];  // this thread's chunk of K block kBurst*g of the current super-block (or null)
+        uint32_t xs[kXPer];         // its place inside an activation stage
+#pragma unroll
+        for (int m = 0; m < kXPer; m++) {
+            const int id = r + kTileN * m;
             const int j = id >> 3, c = id & 7;
-            if (i < nkb && id < kXChunks && j < p.M) {
-                v = *reinterpret_cast<const uint4*>(p.X + static_cast<long long>(j) * p.K + (kb_begin + i) * kKBlock + c * 8);
+            xp[m] = (id < kXChunks && j < p.M) ? p.X + static_cast<long long>(j) * p.K + (kb_begin + kBurst * g) * kKBlock + c * 8
+                                               : nullptr;
+            xs[m] = s_addr(sB) + sw128_off(id >> 3, id & 7);
+        }
+        // chunk m of K block b2 of the burst; `left` = K blocks that exist from the burst's first one onwards
+        auto load_x = [&](int m, int b2, int left) -> uint4 {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (xp[m] != nullptr && b2 < left) {
+                v = *reinterpret_cast<const uint4*>(xp[m] + b2 * kKBlock);
                 if constexpr (BF16) {
                     v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
                     v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
@@ -327,45 +367,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         };
         pdl_wait();  // activations come from the previous kernel; weights do not
         // Activation chunks are fetched one super-block ahead: an L2 round trip is longer than a K block takes.
-        uint4 xr[2][kXPer];
+        uint4 xr[kBurst][kXPer];
+        int left = nkb - kBurst * g;  // K blocks that exist from this group's burst of the current super-block onwards
 #pragma unroll
-        for (int b2 = 0; b2 < 2; b2++)
+        for (int b2 = 0; b2 < kBurst; b2++)
 #pragma unroll
-            for (int m = 0; m < kXPer; m++) xr[b2][m] = load_x(2 * g + b2, r + kTileN * m);
+            for (int m = 0; m < kXPer; m++) xr[b2][m] = load_x(m, b2, left);
+
+        // read offsets of this group's quantisation blocks inside a raw row / scale row
+        uint32_t roff[2 * kBurst];
+#pragma unroll
+        for (int q = 0; q < 2 * kBurst; q++) roff[q] = r * 128 + (((2 * kBurst * g + q) ^ (r & 7)) << 4);
+        const uint32_t soff = (r * 8 + 2 * kBurst * g) * 4;
 
         bool ok = true;
+        int slot = 0;            // super-block slot of the operand ring
+        bool first_use = true;   // no wait while the ring is filled for the first time
+        unsigned par = 1;        // parity of the previous use of the slot
+        uint32_t raw_n = 0, raw_s = 0;  // byte offsets of the raw stage to read
         for (int sb = 0; sb < nsb; sb++) {
-            // raw slot (sb+2) % 4 was last read for super-block sb-2, which every producer finished before passing
-            // the barrier of super-block sb-1
+            // the raw stage filled here was last read two super-blocks ago, which every producer finished before
+            // passing the barrier of the previous super-block
             TRACE(g, sb, 0);
-            issue_raw(sb + 2);
+            issue_raw();
             TRACE(g, sb, 1);
             cp_async_wait<2>();                               // this thread's copies of super-block sb have landed
             TRACE(g, sb, 2);
-            asm volatile("bar.sync 2, 256;" ::: "memory");   // ... and everybody else's
+            asm volatile("bar.sync 2, %0;" ::"n"(kProducerThreads) : "memory");  // ... and everybody else's
             TRACE(g, sb, 3);
-            uint4 nx[2][kXPer];
+            uint4 nx[kBurst][kXPer];
 #pragma unroll
-            for (int b2 = 0; b2 < 2; b2++)
+            for (int m = 0; m < kXPer; m++)
+                if (xp[m] != nullptr) xp[m] += kSuper * kKBlock;
 #pragma unroll
-                for (int m = 0; m < kXPer; m++) nx[b2][m] = load_x((sb + 1) * kSuper + 2 * g + b2, r + kTileN * m);
-            const int i0 = sb * kSuper + 2 * g;     // first K block of this group's burst
-            const int nvalid = min(2, nkb - i0);    // K blocks of the burst that exist
-            const int slot = sb % kSlots, use = sb / kSlots;
-            const int so0 = slot * kSuper + 2 * g;  // operand stage of the first K block of the burst
+            for (int b2 = 0; b2 < kBurst; b2++)
+#pragma unroll
+                for (int m = 0; m < kXPer; m++) nx[b2][m] = load_x(m, b2, left - kSuper);
+            const int nvalid = min(kBurst, left);      // K blocks of the burst that exist
+            const int so0 = slot * kSuper + kBurst * g;  // operand stage of the first K block of the burst
             // a warp that gave up keeps attending the producer barrier above (the others would wait for it for ever)
             // and does nothing else
             if (ok && nvalid > 0) {
-                if (use >= 1) {
+                if (!first_use) {
                     // one lane polls for the warp: many threads spinning on one mbarrier word serialise
                     bool w = true;
-                    if (lane == 0) {
-                        const unsigned par = static_cast<unsigned>(use - 1) & 1u;
-                        w = mb_wait(&empty[so0], par);
-                        if (w && nvalid > 1) w = mb_wait(&empty[so0 + 1], par);
-                    }
+                    if (lane == 0)
+                        for (int b2 = 0; b2 < nvalid && w; b2++) w = mb_wait(&empty[so0 + b2], par);
                     w = __shfl_sync(0xffffffffu, w, 0);
-                    if (!w || *reinterpret_cast<volatile int*>(abort_flag)) {
+                    if (!w) {
                         if (lane == 0) {
                             atomicCAS(&g_gemm_device_error, 0, 1);
                             atomicExch(abort_flag, 1);
@@ -376,16 +425,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                 }
                 TRACE(g, sb, 4);
                 if (ok) {
-                    const int st = sb % kRawStages;
-                    const unsigned char* rawrow = sRawN + static_cast<size_t>(st) * (kTileN * 128) + r * 128;
-                    const float4 sc4 = *reinterpret_cast<const float4*>(sRawS + static_cast<size_t>(st) * (kTileN * 8) + r * 8 + 4 * g);
-                    const float scv[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-                    uint4 raw[4];
+                    float scv[2 * kBurst];
+                    uint4 raw[2 * kBurst];
 #pragma unroll
-                    for (int q = 0; q < 4; q++)  // quantisation blocks 4g .. 4g+3 of the super-stage row
-                        raw[q] = *reinterpret_cast<const uint4*>(rawrow + (((4 * g + q) ^ (r & 7)) << 4));
+                    for (int q = 0; q < 2 * kBurst; q += 2) {
+                        const float2 s2 = *reinterpret_cast<const float2*>(reinterpret_cast<const unsigned char*>(sRawS) + raw_s + soff + q * 4);
+                        scv[q] = s2.x;
+                        scv[q + 1] = s2.y;
+                    }
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
+                    for (int q = 0; q < 2 * kBurst; q++)  // this group's quantisation blocks of the super-stage row
+                        raw[q] = *reinterpret_cast<const uint4*>(sRawN + raw_n + roff[q]);
+#pragma unroll
+                    for (int q = 0; q < 2 * kBurst; q++) {
                         const int b2 = q >> 1, h = q & 1;
                         if (b2 < nvalid) {
                             const DequantScale ds = make_dequant_scale(scv[q]);
@@ -401,14 +453,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     }
                     // ---- activation tiles (same K permutation inside every chunk)
 #pragma unroll
-                    for (int b2 = 0; b2 < 2; b2++) {
+                    for (int b2 = 0; b2 < kBurst; b2++) {
                         if (b2 < nvalid) {
-                            unsigned char* b_stage = sB + (so0 + b2) * kBBytes;
 #pragma unroll
                             for (int m = 0; m < kXPer; m++) {
-                                const int id = r + kTileN * m;
-                                if (id < kXChunks)
-                                    *reinterpret_cast<uint4*>(b_stage + sw128_off(id >> 3, id & 7)) = permute_chunk(xr[b2][m]);
+                                if (r + kTileN * m < kXChunks) {
+                                    const uint4 v = permute_chunk(xr[b2][m]);
+                                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(xs[m] + (so0 + b2) * kBBytes), "r"(v.x),
+                                                 "r"(v.y), "r"(v.z), "r"(v.w)
+                                                 : "memory");
+                                }
                             }
                         }
                     }
@@ -419,16 +473,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {  // one arrival per warp
-                        mb_arrive(&full[so0]);
-                        if (nvalid > 1) mb_arrive(&full[so0 + 1]);
+                        for (int b2 = 0; b2 < nvalid; b2++) mb_arrive(&full[so0 + b2]);
                     }
                     TRACE(g, sb, 6);
                 }
             }
 #pragma unroll
-            for (int b2 = 0; b2 < 2; b2++)
+            for (int b2 = 0; b2 < kBurst; b2++)
 #pragma unroll
                 for (int m = 0; m < kXPer; m++) xr[b2][m] = nx[b2][m];
+            left -= kSuper;
+            raw_n = raw_n == (kRawStages - 1) * kRawNStage ? 0 : raw_n + kRawNStage;
+            raw_s = raw_s == (kRawStages - 1) * kRawSStage ? 0 : raw_s + kRawSStage;
+            if (++slot == kSlots) {
+                slot = 0;
+                first_use = false;
+                par ^= 1u;
+            }
         }
         cp_async_wait<0>();
         pdl_launch_dependents();
@@ -445,8 +506,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             if (done) {
                 const int n = n0 + warp * 32 + lane;  // this thread's output feature
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-#pragma unroll
                 const int used = min(kAccSets, nkb);  // accumulator sets that received an MMA
+#pragma unroll
                 for (int cb = 0; cb < MB; cb += 8) {
                     float y[8];
                     for (int a = 0; a < used; a++) {
@@ -481,7 +542,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             bool issued = false;
             for (int sb = 0; sb * kSuper + w < nkb; sb++) {
                 const int so = (sb % kSlots) * kSuper + w;
+                if (w == 0) TRACE(4, sb, 0);
                 const bool ready = mb_wait(&full[so], static_cast<unsigned>(sb / kSlots) & 1u);
+                if (w == 0) TRACE(4, sb, 1);
                 if (!ready || *reinterpret_cast<volatile int*>(abort_flag)) {
                     atomicCAS(&g_gemm_device_error, 0, 2);
                     atomicExch(abort_flag, 1);
@@ -495,7 +558,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
                     umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
                 }
+                if (w == 0) TRACE(4, sb, 2);
                 umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
+                if (w == 0) TRACE(4, sb, 3);
                 issued = true;
             }
             // this warp's accumulator set is complete (on an abandoned run the epilogue is not waiting any more)
@@ -514,7 +579,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
 #ifdef NVE_GEMM_TRACE
 extern "C" __attribute__((visibility("default"))) int nve_dbg_trace(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8);
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 5 * 64 * 8);
 }
 #endif
 // Sum the split-K partials in ascending split order and convert.
