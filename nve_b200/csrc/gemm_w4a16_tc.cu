@@ -89,28 +89,27 @@ __device__ __forceinline__ void mb_init(uint64_t* bar, unsigned count) {
 __device__ __forceinline__ void mb_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(bar)) : "memory");
 }
+// One try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or the hint
+// (nanoseconds) runs out, so a waiting warp does not burn issue slots that the dequantising warps need.
 __device__ __forceinline__ bool mb_try(uint32_t addr, unsigned parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(20000u)
         : "memory");
     return done != 0;
 }
-// Bounded by wall time (the hardware may suspend a try_wait for a while, so an iteration count bounds nothing):
-// false after kGemmWaitLimitNs without the phase completing.
+// Bounded by wall time: false after kGemmWaitLimitNs without the phase completing.
 __device__ __forceinline__ bool mb_wait(uint64_t* bar, unsigned parity) {
     const uint32_t addr = s_addr(bar);
-    for (int spin = 0; spin < 64; spin++)
-        if (mb_try(addr, parity)) return true;
+    if (mb_try(addr, parity)) return true;
     unsigned long long t0, t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     do {
-        for (int spin = 0; spin < 16; spin++)
-            if (mb_try(addr, parity)) return true;
+        if (mb_try(addr, parity)) return true;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     } while (t - t0 < kGemmWaitLimitNs);
     return false;
@@ -192,9 +191,26 @@ __device__ __forceinline__ DequantScale make_dequant_scale(float scale) {
     d.mul2 = *reinterpret_cast<const uint32_t*>(&m);
     return d;
 }
-template <bool HIGH> __device__ __forceinline__ uint32_t dequant_pair(uint32_t w, const DequantScale& d) {
-    const uint32_t bits = HIGH ? ((w & 0x00F000F0u) | 0x54005400u) : ((w & 0x000F000Fu) | 0x64006400u);
-    const uint32_t off = HIGH ? 0x54805480u /* 72 */ : 0x64086408u /* 1032 */;
+// Masks, magic numbers and offsets live in registers that the optimiser cannot see through: with literal
+// constants the compiler emitted two LOP3 per pair (one immediate per instruction); (w & mask) | magic is a
+// single LOP3 when all three operands are registers.
+struct DequantConsts {
+    uint32_t mask_lo, magic_lo, off_lo, mask_hi, magic_hi, off_hi;
+};
+__device__ __forceinline__ DequantConsts make_dequant_consts() {
+    DequantConsts c;
+    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(c.mask_lo));
+    asm volatile("mov.b32 %0, 0x64006400;" : "=r"(c.magic_lo));
+    asm volatile("mov.b32 %0, 0x64086408;" : "=r"(c.off_lo));   // 1032
+    asm volatile("mov.b32 %0, 0x00F000F0;" : "=r"(c.mask_hi));
+    asm volatile("mov.b32 %0, 0x54005400;" : "=r"(c.magic_hi));
+    asm volatile("mov.b32 %0, 0x54805480;" : "=r"(c.off_hi));   // 72
+    return c;
+}
+template <bool HIGH> __device__ __forceinline__ uint32_t dequant_pair(uint32_t w, const DequantScale& d, const DequantConsts& c) {
+    uint32_t bits;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(w), "r"(HIGH ? c.mask_hi : c.mask_lo), "r"(HIGH ? c.magic_hi : c.magic_lo));
+    const uint32_t off = HIGH ? c.off_hi : c.off_lo;
     __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), *reinterpret_cast<const __half2*>(&off));
     v = __hmul2(v, *reinterpret_cast<const __half2*>(&d.mul2));
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -202,13 +218,13 @@ template <bool HIGH> __device__ __forceinline__ uint32_t dequant_pair(uint32_t w
 
 // One raw word (4 bytes = elements j..j+3 in the low nibbles, j+16..j+19 in the high nibbles) -> two low pairs
 // (e_j, e_j+2), (e_j+1, e_j+3) and two high pairs in the same pattern.
-__device__ __forceinline__ void dequant_word(uint32_t w, const DequantScale& d, uint32_t& lo0, uint32_t& lo1, uint32_t& hi0,
-                                             uint32_t& hi1) {
+__device__ __forceinline__ void dequant_word(uint32_t w, const DequantScale& d, const DequantConsts& c, uint32_t& lo0,
+                                             uint32_t& lo1, uint32_t& hi0, uint32_t& hi1) {
     const uint32_t t = w >> 8;
-    lo0 = dequant_pair<false>(w, d);  // nibbles at bits 0-3 / 16-19
-    hi0 = dequant_pair<true>(w, d);   // bits 4-7 / 20-23
-    lo1 = dequant_pair<false>(t, d);  // bits 8-11 / 24-27
-    hi1 = dequant_pair<true>(t, d);   // bits 12-15 / 28-31
+    lo0 = dequant_pair<false>(w, d, c);  // nibbles at bits 0-3 / 16-19
+    hi0 = dequant_pair<true>(w, d, c);   // bits 4-7 / 20-23
+    lo1 = dequant_pair<false>(t, d, c);  // bits 8-11 / 24-27
+    hi1 = dequant_pair<true>(t, d, c);   // bits 12-15 / 28-31
 }
 
 // bf16 pair -> f16 pair.  Exact for 6.1e-5 <= |x| <= 65504 (every bf16 significand fits f16); larger magnitudes
@@ -380,6 +396,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         for (int q = 0; q < 2 * kBurst; q++) roff[q] = r * 128 + (((2 * kBurst * g + q) ^ (r & 7)) << 4);
         const uint32_t soff = (r * 8 + 2 * kBurst * g) * 4;
 
+        const DequantConsts dc = make_dequant_consts();
         bool ok = true;
         int slot = 0;            // super-block slot of the operand ring
         bool first_use = true;   // no wait while the ring is filled for the first time
@@ -444,10 +461,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                             // v[0..3] = elements 0-7, v[4..7] = 8-15, v[8..11] = 16-23, v[12..15] = 24-31 of the
                             // block, each group of four in the order (e0,e2)(e1,e3)
                             uint32_t v[16];
-                            dequant_word(raw[q].x, ds, v[0], v[1], v[8], v[9]);
-                            dequant_word(raw[q].y, ds, v[2], v[3], v[10], v[11]);
-                            dequant_word(raw[q].z, ds, v[4], v[5], v[12], v[13]);
-                            dequant_word(raw[q].w, ds, v[6], v[7], v[14], v[15]);
+                            dequant_word(raw[q].x, ds, dc, v[0], v[1], v[8], v[9]);
+                            dequant_word(raw[q].y, ds, dc, v[2], v[3], v[10], v[11]);
+                            dequant_word(raw[q].z, ds, dc, v[4], v[5], v[12], v[13]);
+                            dequant_word(raw[q].w, ds, dc, v[6], v[7], v[14], v[15]);
                             tmem_st16(tmem_lane + (so0 + b2) * kStageCols + 16 * h, v);
                         }
                     }
