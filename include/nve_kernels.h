@@ -259,12 +259,16 @@ NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long s
                             unsigned long long first, float scale, int dtype, nve_stream_t stream);
 
 /* Batched W4A16 GEMM for decode batches 1 < M <= 64 on the tcgen05 tensor cores: Y[M,N] = X[M,K] . W^T with the
- * packed weights dequantised in shared memory (replaces nve_dequant_w4a16 + dense GEMM, src/gpu_layer.rs:220-239).
- * X and Y are row-major; x_dtype f16 or bf16, y_dtype = x_dtype or f32; K % 64 == 0.  Weights are rounded to f16 as
- * (q-8)*scale like the reference's dequantisation; bf16 activations are converted to f16 (exact up to +-65504,
- * saturating beyond); accumulation is f32 in tensor memory.
- * `scratch` (may be NULL) holds f32 split-K partials, which let small N fill all SMs; its size comes from
- * nve_b200_gemm_w4a16_scratch_bytes.  nve_b200_gemm_error returns the code latched by an expired bounded wait. */
+ * packed weights dequantised on the fly into tensor memory (replaces nve_dequant_w4a16 + dense GEMM,
+ * src/gpu_layer.rs:220-239).
+ * X and Y are row-major; x_dtype f16 or bf16, y_dtype = x_dtype or f32; K % 64 == 0; X and nibbles 16-byte aligned,
+ * scales 8-byte aligned.  Weights are rounded to f16 as (q-8)*scale like the reference's dequantisation;
+ * accumulation is f32 in tensor memory.
+ * `scratch` (may be NULL for f16 activations) holds, in this order, an f16 copy of bf16 activations (exact up to
+ * +-65504, saturating beyond) and the f32 split-K partials that let small N fill all SMs; its size comes from
+ * nve_b200_gemm_w4a16_scratch_bytes.  bf16 activations without enough scratch for their copy are refused with
+ * NVE_ERR_TOO_LARGE; a scratch too small for split-K only lowers the split.
+ * nve_b200_gemm_error returns the code latched by an expired bounded wait. */
 NVE_API size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K);
 NVE_API int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
                                 int y_dtype, int M, int N, int K, void* scratch, size_t scratch_bytes,
@@ -277,7 +281,8 @@ NVE_API int nve_b200_gemm_error(int reset);
  * cudaMalloc is illegal; a latency-critical serving thread is in the same position.  The split-K partial sums go
  * to a fixed 4 MiB array inside the library image (held on every GPU that loads the library until the process
  * exits) instead of a caller buffer.  Same arguments and results as nve_b200_gemm_w4a16 otherwise.
- *   - A shape whose partial sums (nve_b200_gemm_w4a16_scratch_bytes) exceed 4 MiB is refused: NVE_ERR_TOO_LARGE.
+ *   - A shape whose workspace (split-K partial sums, plus the f16 copy of bf16 activations) exceeds 4 MiB is
+ *     refused: NVE_ERR_TOO_LARGE.
  *   - The first call on each device resolves the array's device address and caches it; make that call before
  *     any stream capture begins.
  *   - All calls share the array and it keeps the previous call's contents (nothing in it needs to start at

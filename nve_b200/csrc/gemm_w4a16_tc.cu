@@ -33,6 +33,8 @@
 // permutation of K applied to both operands.
 // Every mbarrier wait is bounded in time; an expired wait latches an error code (nve_b200_gemm_error) and the
 // CTA leaves through the normal path, freeing its TMEM columns.
+#include <cuda.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -42,7 +44,7 @@ namespace nve {
 constexpr int kTileN = 128;      // weight rows per CTA = MMA M
 constexpr int kKBlock = 64;      // K elements per pipeline stage (128 bytes of 16-bit)
 constexpr int kSuper = 4;        // K blocks per raw super-stage: 256 elements = 128 contiguous nibble bytes per row
-constexpr int kRawStages = 4;    // cp.async ring depth in super-stages (two are in flight ahead of the dequantisers)
+constexpr int kRawStages = 3;    // cp.async ring depth per team, in super-stages
 constexpr int kStageCols = kKBlock / 2;     // TMEM columns of one A stage: two f16 per 32-bit column
 constexpr int kTmemCols = 512;   // the whole tensor memory of the SM
 constexpr int kMmaWarps = kSuper; // one per K block of a super-block, each with its own accumulator set
@@ -54,9 +56,11 @@ __host__ __device__ constexpr int acc_sets(int) { return kMmaWarps; }
 // super-blocks of operand stages in flight: what is left of the 512 columns, in units of 4 stages x 32 columns
 __host__ __device__ constexpr int op_slots(int mb) { return (kTmemCols - acc_sets(mb) * mb) / (kSuper * kStageCols); }
 constexpr int kMaxOpStages = 12;
-constexpr int kGroups = 4;         // producer groups of four warps (thread = weight row = TMEM lane)
+constexpr int kTeams = 2;          // producer teams; team t takes super-blocks t, t+2, ... on its own barrier and raw ring
+constexpr int kGroups = 2;         // groups of four warps per team (thread = weight row = TMEM lane)
 constexpr int kBurst = kSuper / kGroups;  // K blocks a group dequantises per super-block
-constexpr int kProducerThreads = 128 * kGroups;
+constexpr int kTeamThreads = 128 * kGroups;
+constexpr int kProducerThreads = kTeamThreads * kTeams;
 constexpr int kProducerWarps = kProducerThreads / 32;
 constexpr int kGemmThreads = kProducerThreads + 32 * kMmaWarps;
 constexpr unsigned long long kGemmWaitLimitNs = 50ull * 1000 * 1000;  // a legitimate wait lasts microseconds
@@ -91,6 +95,16 @@ __device__ __forceinline__ void mb_arrive(uint64_t* bar) {
 }
 // One try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or the hint
 // (nanoseconds) runs out, so a waiting warp does not burn issue slots that the dequantising warps need.
+__device__ __forceinline__ void mb_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(bar)), "r"(bytes) : "memory");
+}
+// One TMA tile load (no multicast): box at element coordinates (x, y) of the tensor map -> shared memory, bytes
+// counted on the mbarrier.  x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(mbar)
+                 : "memory");
+}
 __device__ __forceinline__ bool mb_try(uint32_t addr, unsigned parity) {
     uint32_t done;
     asm volatile(
@@ -146,8 +160,8 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_byte_addr) {
 }
 
 // Instruction descriptor for kind::f16: D = f32, A and B = f16 (0) or bf16 (1), both K-major, M = 128, N = MB.
-__host__ __device__ constexpr uint32_t make_idesc(int mb, bool bf16) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(mb >> 3) << 17) |
+__host__ __device__ constexpr uint32_t make_idesc(int mb, bool a_bf16, bool b_bf16) {
+    return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(mb >> 3) << 17) |
            (static_cast<uint32_t>(kTileN >> 4) << 24);
 }
 
@@ -216,39 +230,21 @@ template <bool HIGH> __device__ __forceinline__ uint32_t dequant_pair(uint32_t w
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// One raw word (4 bytes = elements j..j+3 in the low nibbles, j+16..j+19 in the high nibbles) -> two low pairs
-// (e_j, e_j+2), (e_j+1, e_j+3) and two high pairs in the same pattern.
+// One raw word (4 bytes = elements j..j+3 in the low nibbles, j+16..j+19 in the high nibbles) -> pairs in natural
+// order: lo0 = (e_j, e_j+1), lo1 = (e_j+2, e_j+3), hi0 = (e_j+16, e_j+17), hi1 = (e_j+18, e_j+19).  One byte
+// permute per word ([b0,b2,b1,b3]) puts the two elements of every pair 16 bits apart, where a half2 wants them.
 __device__ __forceinline__ void dequant_word(uint32_t w, const DequantScale& d, const DequantConsts& c, uint32_t& lo0,
                                              uint32_t& lo1, uint32_t& hi0, uint32_t& hi1) {
-    const uint32_t t = w >> 8;
-    lo0 = dequant_pair<false>(w, d, c);  // nibbles at bits 0-3 / 16-19
-    hi0 = dequant_pair<true>(w, d, c);   // bits 4-7 / 20-23
-    lo1 = dequant_pair<false>(t, d, c);  // bits 8-11 / 24-27
-    hi1 = dequant_pair<true>(t, d, c);   // bits 12-15 / 28-31
+    const uint32_t u = __byte_perm(w, 0, 0x3120);
+    const uint32_t t = u >> 8;
+    lo0 = dequant_pair<false>(u, d, c);  // b0 low nibble, b1 low nibble
+    hi0 = dequant_pair<true>(u, d, c);   // b0 high, b1 high
+    lo1 = dequant_pair<false>(t, d, c);  // b2 low, b3 low
+    hi1 = dequant_pair<true>(t, d, c);   // b2 high, b3 high
 }
 
-// bf16 pair -> f16 pair.  Exact for 6.1e-5 <= |x| <= 65504 (every bf16 significand fits f16); larger magnitudes
-// saturate to +-65504, smaller ones round into the f16 subnormal range.
-__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
-    float lo = __uint_as_float(v << 16), hi = __uint_as_float(v & 0xFFFF0000u);
-    lo = fminf(fmaxf(lo, -65504.0f), 65504.0f);
-    hi = fminf(fmaxf(hi, -65504.0f), 65504.0f);
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// Apply the chunk permutation [0,2,1,3,4,6,5,7] to 8 consecutive 16-bit activations.
-__device__ __forceinline__ uint4 permute_chunk(uint4 x) {
-    uint4 r;
-    r.x = __byte_perm(x.x, x.y, 0x5410);  // (x0, x2)
-    r.y = __byte_perm(x.x, x.y, 0x7632);  // (x1, x3)
-    r.z = __byte_perm(x.z, x.w, 0x5410);  // (x4, x6)
-    r.w = __byte_perm(x.z, x.w, 0x7632);  // (x5, x7)
-    return r;
-}
-
-template <int MB, bool BF16, int ODT>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const GemmParams p) {
+template <int MB, int ODT>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // layout: B stages | raw nibbles | raw scales | barriers
     constexpr int kBBytes = MB * 128;
@@ -259,9 +255,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     static_assert(kAccCols + kOpStages * kStageCols <= kTmemCols && kSlots >= 2 && kOpStages <= kMaxOpStages, "TMEM budget");
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sB = smem;
-    unsigned char* sRawN = sB + kOpStages * kBBytes;            // [kRawStages][128 rows][128 B], 16-byte chunks XOR-swizzled
-    float* sRawS = reinterpret_cast<float*>(sRawN + kRawStages * kTileN * 128);  // [kRawStages][128 rows][8 scales]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kRawStages * kTileN * 8);
+    unsigned char* sRawN = sB + kOpStages * kBBytes;            // [kTeams][kRawStages][128 rows][128 B], 16-byte chunks XOR-swizzled
+    float* sRawS = reinterpret_cast<float*>(sRawN + kTeams * kRawStages * kTileN * 128);  // [kTeams][kRawStages][128 rows][8 scales]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kTeams * kRawStages * kTileN * 8);
     uint64_t* full = bars;                  // [kOpStages], one arrival per warp of the owning group
     uint64_t* empty = bars + kOpStages;     // [kOpStages], 1 arrival (tcgen05.commit)
     uint64_t* accum = bars + 2 * kOpStages; // 1 arrival
@@ -278,7 +274,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
     if (tid == 0) {
         for (int i = 0; i < kOpStages; i++) {
-            mb_init(&full[i], 4);  // the four warps of the group that owns the stage
+            mb_init(&full[i], 5);  // the four warps of the group that owns the stage + the TMA issuer's expect_tx
             mb_init(&empty[i], 1);
         }
         mb_init(accum, min(kMmaWarps, nkb));  // one tcgen05.commit per issuing warp that has work
@@ -302,19 +298,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         // so that the later per-row reads are bank-conflict free.  All addresses are set up once; the loop only
         // advances them (the kernel is bound by instruction issue, so loop overhead counts).
         const int nsb = (nkb + kSuper - 1) / kSuper;
-        constexpr int kNibPer = 1024 / kProducerThreads;  // 128 rows x 8 chunks of 16 bytes
-        constexpr int kScPer = 512 / kProducerThreads;    // 128 rows x 4 K blocks x 2 scales
+        // The chain of one super-block (copy wait -> barrier -> ring wait -> load -> convert -> store -> fences ->
+        // arrive) is over a thousand cycles of mostly latency; two teams run it out of phase on alternate
+        // super-blocks, each with its own named barrier and raw ring.
+        const int team = tid / kTeamThreads;
+        const int tt = tid - team * kTeamThreads;        // thread inside the team
+        const int nsb_team = (nsb - team + kTeams - 1) / kTeams;  // super-blocks team, team + kTeams, ...
+        constexpr int kNibPer = 1024 / kTeamThreads;  // 128 rows x 8 chunks of 16 bytes
+        constexpr int kScPer = 512 / kTeamThreads;    // 128 rows x 4 K blocks x 2 scales
         constexpr uint32_t kRawNStage = kTileN * 128, kRawSStage = kTileN * 8 * 4;
+        const unsigned char* teamRawN = sRawN + team * (kRawStages * kRawNStage);
+        const unsigned char* teamRawS = reinterpret_cast<const unsigned char*>(sRawS) + team * (kRawStages * kRawSStage);
         const uint8_t* gn[kNibPer];
         uint32_t sn[kNibPer];
         int kn[kNibPer];  // K block of the super-block that the chunk belongs to
 #pragma unroll
         for (int j = 0; j < kNibPer; j++) {
-            const int id = tid + kProducerThreads * j;
+            const int id = tt + kTeamThreads * j;
             const int rr = id >> 3, c = id & 7;
             const int grow = min(n0 + rr, p.N - 1);
-            gn[j] = p.nib + static_cast<long long>(grow) * (p.K / 2) + kb_begin * 32 + c * 16;
-            sn[j] = s_addr(sRawN) + rr * 128 + ((c ^ (rr & 7)) << 4);
+            gn[j] = p.nib + static_cast<long long>(grow) * (p.K / 2) + (kb_begin + team * kSuper) * 32 + c * 16;
+            sn[j] = s_addr(teamRawN) + rr * 128 + ((c ^ (rr & 7)) << 4);
             kn[j] = c >> 1;
         }
         const float* gs[kScPer];
@@ -322,28 +326,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         int ks[kScPer];
 #pragma unroll
         for (int j = 0; j < kScPer; j++) {
-            const int id = tid + kProducerThreads * j;
+            const int id = tt + kTeamThreads * j;
             const int rr = id >> 2, kbi = id & 3;
             const int grow = min(n0 + rr, p.N - 1);
-            gs[j] = p.sc + static_cast<long long>(grow) * p.nb + (kb_begin + kbi) * 2;
-            ss[j] = s_addr(sRawS) + (rr * 8 + kbi * 2) * 4;
+            gs[j] = p.sc + static_cast<long long>(grow) * p.nb + (kb_begin + team * kSuper + kbi) * 2;
+            ss[j] = s_addr(teamRawS) + (rr * 8 + kbi * 2) * 4;
             ks[j] = kbi;
         }
-        int issue_left = nkb;  // K blocks from the next super-block to issue onwards
-        uint32_t issue_n = 0, issue_s = 0;  // byte offsets of the raw stage to fill
+        int issue_left = nkb - team * kSuper;  // K blocks from the team's next super-block to issue onwards
+        uint32_t issue_n = 0, issue_s = 0;     // byte offsets of the raw stage to fill
         auto issue_raw = [&]() {
             if (issue_left > 0) {
 #pragma unroll
                 for (int j = 0; j < kNibPer; j++) {
                     if (kn[j] < issue_left) cp_async_16s(sn[j] + issue_n, gn[j]);
-                    gn[j] += kSuper * 32;
+                    gn[j] += kTeams * kSuper * 32;
                 }
 #pragma unroll
                 for (int j = 0; j < kScPer; j++) {
                     if (ks[j] < issue_left) cp_async_8s(ss[j] + issue_s, gs[j]);
-                    gs[j] += kSuper * 2;
+                    gs[j] += kTeams * kSuper * 2;
                 }
-                issue_left -= kSuper;
+                issue_left -= kTeams * kSuper;
                 issue_n = issue_n == (kRawStages - 1) * kRawNStage ? 0 : issue_n + kRawNStage;
                 issue_s = issue_s == (kRawStages - 1) * kRawSStage ? 0 : issue_s + kRawSStage;
             }
@@ -354,41 +358,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
         // Groups of four warps; in every super-block group g dequantises K blocks kBurst*g .. kBurst*(g+1)-1 in one
         // go: the waits first, then all loads, arithmetic and stores, one round of fences, one arrival per stage.
+        // The activation tile of a stage is one TMA tile load (SWIZZLE_128B, rows beyond M zero-filled), issued by
+        // one lane of the group as soon as the stage is free; it completes on the stage's "full" barrier.
         const int r = tid & (kTileN - 1);  // weight row inside the tile = TMEM lane
-        const int g = tid >> 7;            // group
+        const int g = tt >> 7;             // group inside the team
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kAccCols;
-        constexpr int kXChunks = MB * 8;   // 16-byte activation chunks per K block: chunk id = row * 8 + c
-        constexpr int kXPer = (kXChunks + kTileN - 1) / kTileN;  // chunks per thread per K block
-        const uint16_t* xp[kXPer];  // this thread's chunk of K block kBurst*g of the current super-block (or null)
-        uint32_t xs[kXPer];         // its place inside an activation stage
-#pragma unroll
-        for (int m = 0; m < kXPer; m++) {
-            const int id = r + kTileN * m;
-            const int j = id >> 3, c = id & 7;
-            xp[m] = (id < kXChunks && j < p.M) ? p.X + static_cast<long long>(j) * p.K + (kb_begin + kBurst * g) * kKBlock + c * 8
-                                               : nullptr;
-            xs[m] = s_addr(sB) + sw128_off(id >> 3, id & 7);
-        }
-        // chunk m of K block b2 of the burst; `left` = K blocks that exist from the burst's first one onwards
-        auto load_x = [&](int m, int b2, int left) -> uint4 {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (xp[m] != nullptr && b2 < left) {
-                v = *reinterpret_cast<const uint4*>(xp[m] + b2 * kKBlock);
-                if constexpr (BF16) {
-                    v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
-                    v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
-                }
-            }
-            return v;
-        };
+        const bool tma_lane = (warp & 3) == 0 && lane == 0;
         pdl_wait();  // activations come from the previous kernel; weights do not
-        // Activation chunks are fetched one super-block ahead: an L2 round trip is longer than a K block takes.
-        uint4 xr[kBurst][kXPer];
-        int left = nkb - kBurst * g;  // K blocks that exist from this group's burst of the current super-block onwards
-#pragma unroll
-        for (int b2 = 0; b2 < kBurst; b2++)
-#pragma unroll
-            for (int m = 0; m < kXPer; m++) xr[b2][m] = load_x(m, b2, left);
+        int left = nkb - team * kSuper - kBurst * g;  // K blocks that exist from this group's burst of the current super-block onwards
+        int kx = (kb_begin + team * kSuper + kBurst * g) * kKBlock;  // K coordinate of that burst
 
         // read offsets of this group's quantisation blocks inside a raw row / scale row
         uint32_t roff[2 * kBurst];
@@ -398,36 +376,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
         const DequantConsts dc = make_dequant_consts();
         bool ok = true;
-        int slot = 0;            // super-block slot of the operand ring
-        bool first_use = true;   // no wait while the ring is filled for the first time
-        unsigned par = 1;        // parity of the previous use of the slot
+        int slot = team % kSlots, use = team / kSlots;  // operand-ring slot of the super-block and how often it was used
         uint32_t raw_n = 0, raw_s = 0;  // byte offsets of the raw stage to read
-        for (int sb = 0; sb < nsb; sb++) {
-            // the raw stage filled here was last read two super-blocks ago, which every producer finished before
-            // passing the barrier of the previous super-block
-            TRACE(g, sb, 0);
+        for (int it = 0; it < nsb_team; it++) {
+            cp_async_wait<1>();                               // this thread's copies of the super-block have landed
+            if (team == 0) asm volatile("bar.sync 2, %0;" ::"n"(kTeamThreads) : "memory");  // ... and the team's
+            else asm volatile("bar.sync 3, %0;" ::"n"(kTeamThreads) : "memory");
+            // every thread of the team has finished the previous super-block, whose raw stage is refilled now
             issue_raw();
-            TRACE(g, sb, 1);
-            cp_async_wait<2>();                               // this thread's copies of super-block sb have landed
-            TRACE(g, sb, 2);
-            asm volatile("bar.sync 2, %0;" ::"n"(kProducerThreads) : "memory");  // ... and everybody else's
-            TRACE(g, sb, 3);
-            uint4 nx[kBurst][kXPer];
-#pragma unroll
-            for (int m = 0; m < kXPer; m++)
-                if (xp[m] != nullptr) xp[m] += kSuper * kKBlock;
-#pragma unroll
-            for (int b2 = 0; b2 < kBurst; b2++)
-#pragma unroll
-                for (int m = 0; m < kXPer; m++) nx[b2][m] = load_x(m, b2, left - kSuper);
             const int nvalid = min(kBurst, left);      // K blocks of the burst that exist
             const int so0 = slot * kSuper + kBurst * g;  // operand stage of the first K block of the burst
             // a warp that gave up keeps attending the producer barrier above (the others would wait for it for ever)
             // and does nothing else
             if (ok && nvalid > 0) {
-                if (!first_use) {
+                if (use > 0) {
                     // one lane polls for the warp: many threads spinning on one mbarrier word serialise
                     bool w = true;
+                    const unsigned par = static_cast<unsigned>(use - 1) & 1u;
                     if (lane == 0)
                         for (int b2 = 0; b2 < nvalid && w; b2++) w = mb_wait(&empty[so0 + b2], par);
                     w = __shfl_sync(0xffffffffu, w, 0);
@@ -440,26 +405,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                TRACE(g, sb, 4);
                 if (ok) {
+                    if (tma_lane) {
+                        for (int b2 = 0; b2 < nvalid; b2++) {
+                            mb_expect_tx(&full[so0 + b2], kBBytes);
+                            tma_load_2d(s_addr(sB + (so0 + b2) * kBBytes), &xmap, kx + b2 * kKBlock, 0, s_addr(&full[so0 + b2]));
+                        }
+                    }
                     float scv[2 * kBurst];
                     uint4 raw[2 * kBurst];
 #pragma unroll
                     for (int q = 0; q < 2 * kBurst; q += 2) {
-                        const float2 s2 = *reinterpret_cast<const float2*>(reinterpret_cast<const unsigned char*>(sRawS) + raw_s + soff + q * 4);
+                        const float2 s2 = *reinterpret_cast<const float2*>(teamRawS + raw_s + soff + q * 4);
                         scv[q] = s2.x;
                         scv[q + 1] = s2.y;
                     }
 #pragma unroll
                     for (int q = 0; q < 2 * kBurst; q++)  // this group's quantisation blocks of the super-stage row
-                        raw[q] = *reinterpret_cast<const uint4*>(sRawN + raw_n + roff[q]);
+                        raw[q] = *reinterpret_cast<const uint4*>(teamRawN + raw_n + roff[q]);
 #pragma unroll
                     for (int q = 0; q < 2 * kBurst; q++) {
                         const int b2 = q >> 1, h = q & 1;
                         if (b2 < nvalid) {
                             const DequantScale ds = make_dequant_scale(scv[q]);
-                            // v[0..3] = elements 0-7, v[4..7] = 8-15, v[8..11] = 16-23, v[12..15] = 24-31 of the
-                            // block, each group of four in the order (e0,e2)(e1,e3)
+                            // v[c] = elements (2c, 2c+1) of the block: TMEM column c of the block's 16 columns
                             uint32_t v[16];
                             dequant_word(raw[q].x, ds, dc, v[0], v[1], v[8], v[9]);
                             dequant_word(raw[q].y, ds, dc, v[2], v[3], v[10], v[11]);
@@ -468,44 +437,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                             tmem_st16(tmem_lane + (so0 + b2) * kStageCols + 16 * h, v);
                         }
                     }
-                    // ---- activation tiles (same K permutation inside every chunk)
-#pragma unroll
-                    for (int b2 = 0; b2 < kBurst; b2++) {
-                        if (b2 < nvalid) {
-#pragma unroll
-                            for (int m = 0; m < kXPer; m++) {
-                                if (r + kTileN * m < kXChunks) {
-                                    const uint4 v = permute_chunk(xr[b2][m]);
-                                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(xs[m] + (so0 + b2) * kBBytes), "r"(v.x),
-                                                 "r"(v.y), "r"(v.z), "r"(v.w)
-                                                 : "memory");
-                                }
-                            }
-                        }
-                    }
-                    TRACE(g, sb, 5);
-                    // TMEM stores complete; shared-memory stores visible to the tensor core (async proxy); signal
+                    // TMEM stores complete and ordered before the arrival
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {  // one arrival per warp
                         for (int b2 = 0; b2 < nvalid; b2++) mb_arrive(&full[so0 + b2]);
                     }
-                    TRACE(g, sb, 6);
                 }
             }
-#pragma unroll
-            for (int b2 = 0; b2 < kBurst; b2++)
-#pragma unroll
-                for (int m = 0; m < kXPer; m++) xr[b2][m] = nx[b2][m];
-            left -= kSuper;
+            left -= kTeams * kSuper;
+            kx += kTeams * kSuper * kKBlock;
             raw_n = raw_n == (kRawStages - 1) * kRawNStage ? 0 : raw_n + kRawNStage;
             raw_s = raw_s == (kRawStages - 1) * kRawSStage ? 0 : raw_s + kRawSStage;
-            if (++slot == kSlots) {
-                slot = 0;
-                first_use = false;
-                par ^= 1u;
+            slot += kTeams;
+            if (slot >= kSlots) {
+                slot -= kSlots;
+                use++;
             }
         }
         cp_async_wait<0>();
@@ -553,7 +501,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     } else {
         // ------------------------------------------------------------------ MMA issuers (last four warps)
         // One lane per warp runs the loop: waits, fences, MMAs and commits are all single-thread operations.
-        constexpr uint32_t idesc = make_idesc(MB, false);  // both operands are f16 (bf16 activations are converted)
+        constexpr uint32_t idesc = make_idesc(MB, false, false);  // both operands f16 (bf16 activations are converted first)
         const int w = warp - kProducerWarps;               // K block of the super-block and accumulator set
         if (lane == 0) {
             bool issued = false;
@@ -610,7 +558,7 @@ template <int ODT> __global__ void gemm_splitk_reduce_kernel(const float* partia
 }
 
 static size_t gemm_smem_bytes(int mb) {
-    const size_t need = 1024 + static_cast<size_t>(op_slots(mb) * kSuper) * (mb * 128) + static_cast<size_t>(kRawStages) * kTileN * (128 + 32) +
+    const size_t need = 1024 + static_cast<size_t>(op_slots(mb) * kSuper) * (mb * 128) + static_cast<size_t>(kTeams * kRawStages) * kTileN * (128 + 32) +
                         (2 * kMaxOpStages + 1) * 8 + 16;
     // A CTA allocates all 512 TMEM columns, so a second CTA on the same SM would only sit in tcgen05.alloc until the
     // first one ends: ask for more than half of the SM's shared memory to keep it off the SM instead.
@@ -629,8 +577,41 @@ static int choose_ksplit(int N, int K, bool have_scratch) {
     return ks;
 }
 
-template <int MB, bool BF16, int ODT> static int launch_gemm(const GemmParams& p, cudaStream_t st) {
-    auto kern = gemm_w4a16_tc_kernel<MB, BF16, ODT>;
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link-time dependency on libcuda).
+// It is a pure host-side encoder: no allocation, no device work, legal during stream capture.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// Tensor map of X [M rows, K columns] (16-bit), box = one K block x MB rows, 128-byte swizzle; rows >= M read zero.
+static int make_x_map(const GemmParams& p, int mb, CUtensorMap* map) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return set_status(NVE_ERR_CUDA);
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.K) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kKBlock), static_cast<cuuint32_t>(mb)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                          const_cast<uint16_t*>(p.X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NVE_OK : set_status(NVE_ERR_CUDA);
+}
+
+template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStream_t st) {
+    auto kern = gemm_w4a16_tc_kernel<MB, ODT>;
+    CUtensorMap xmap;
+    if (int ms = make_x_map(p, MB, &xmap); ms != NVE_OK) return ms;
     const size_t smem = gemm_smem_bytes(MB);
     int s = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(smem));
     if (s != NVE_OK) return s;
@@ -646,7 +627,7 @@ template <int MB, bool BF16, int ODT> static int launch_gemm(const GemmParams& p
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p, xmap);
     count_launch();
     if (e != cudaSuccess) return set_cuda_status(e);
     if (p.ksplit > 1) {
@@ -658,10 +639,63 @@ template <int MB, bool BF16, int ODT> static int launch_gemm(const GemmParams& p
     return set_status(NVE_OK);
 }
 
-template <bool BF16, int ODT> static int gemm_mb(const GemmParams& p, cudaStream_t st) {
-    if (p.M <= 16) return launch_gemm<16, BF16, ODT>(p, st);
-    if (p.M <= 32) return launch_gemm<32, BF16, ODT>(p, st);
-    return launch_gemm<64, BF16, ODT>(p, st);
+template <int ODT> static int gemm_mb(const GemmParams& p, cudaStream_t st) {
+    if (p.M <= 16) return launch_gemm<16, ODT>(p, st);
+    if (p.M <= 32) return launch_gemm<32, ODT>(p, st);
+    return launch_gemm<64, ODT>(p, st);
+}
+
+// bf16 -> f16, eight elements per thread.  Exact for 6.1e-5 <= |x| <= 65504 (every bf16 significand fits f16);
+// larger magnitudes saturate to +-65504, smaller ones round into the f16 subnormal range.
+__global__ void bf16_to_f16_kernel(const uint4* in, uint4* out, long long n8) {
+    pdl_wait();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 v = in[i];
+    auto cvt = [](uint32_t w) {
+        float lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xFFFF0000u);
+        lo = fminf(fmaxf(lo, -65504.0f), 65504.0f);
+        hi = fminf(fmaxf(hi, -65504.0f), 65504.0f);
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    };
+    out[i] = make_uint4(cvt(v.x), cvt(v.y), cvt(v.z), cvt(v.w));
+}
+
+static size_t x16_region_bytes(int M, int K) { return (static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255); }
+
+// Shared by both entry points.  Scratch layout: [f16 copy of bf16 activations (x16_region_bytes)][split-K partials].
+// bf16 activations need the first region; split-K uses what is left.
+static int run_gemm(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y, int y_dtype, int M, int N,
+                    int K, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+    unsigned char* sp = static_cast<unsigned char*>(scratch);
+    GemmParams p;
+    p.X = static_cast<const uint16_t*>(X);
+    if (x_dtype == NVE_DT_BF16) {
+        const size_t xb = x16_region_bytes(M, K);
+        if (sp == nullptr || scratch_bytes < xb) return set_status(NVE_ERR_TOO_LARGE);
+        if (!aligned(sp, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+        const long long n8 = static_cast<long long>(M) * K / 8;
+        bf16_to_f16_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, st>>>(static_cast<const uint4*>(X),
+                                                                                     reinterpret_cast<uint4*>(sp), n8);
+        count_launch();
+        if (int cs = check_launch(); cs != NVE_OK) return cs;
+        p.X = reinterpret_cast<const uint16_t*>(sp);
+        sp += xb;
+        scratch_bytes -= xb;
+    }
+    p.nib = nibbles;
+    p.sc = scales;
+    p.Y = Y;
+    p.M = M; p.N = N; p.K = K;
+    p.nb = K / 32;
+    p.kblocks = K / kKBlock;
+    int ks = choose_ksplit(N, K, sp != nullptr);
+    while (ks > 1 && static_cast<size_t>(ks) * M * N * sizeof(float) > scratch_bytes) ks--;
+    p.ksplit = ks;
+    p.partial = reinterpret_cast<float*>(sp);
+    if (y_dtype == NVE_DT_F32) return gemm_mb<NVE_DT_F32>(p, st);
+    return y_dtype == NVE_DT_F16 ? gemm_mb<NVE_DT_F16>(p, st) : gemm_mb<NVE_DT_BF16>(p, st);
 }
 
 }  // namespace nve
@@ -671,7 +705,7 @@ using namespace nve;
 extern "C" size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0 || (K % kKBlock) != 0) return 0;
     const int ks = choose_ksplit(N, K, true);
-    return ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0;
+    return x16_region_bytes(M, K) + (ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0);
 }
 
 extern "C" int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y, int y_dtype,
@@ -680,24 +714,8 @@ extern "C" int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* ni
     if (M < 1 || M > 64 || N < 1 || K < kKBlock || (K % kKBlock) != 0) return set_status(NVE_ERR_BAD_SHAPE);
     if (x_dtype != NVE_DT_F16 && x_dtype != NVE_DT_BF16) return set_status(NVE_ERR_BAD_DTYPE);
     if (y_dtype != x_dtype && y_dtype != NVE_DT_F32) return set_status(NVE_ERR_BAD_DTYPE);
-    if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 4)) return set_status(NVE_ERR_BAD_ALIGNMENT);
-    GemmParams p;
-    p.X = static_cast<const uint16_t*>(X);
-    p.nib = nibbles;
-    p.sc = scales;
-    p.Y = Y;
-    p.M = M; p.N = N; p.K = K;
-    p.nb = K / 32;
-    p.kblocks = K / kKBlock;
-    int ks = choose_ksplit(N, K, scratch != nullptr);
-    while (ks > 1 && static_cast<size_t>(ks) * M * N * sizeof(float) > scratch_bytes) ks--;
-    p.ksplit = ks;
-    p.partial = static_cast<float*>(scratch);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_dtype == NVE_DT_F16) {
-        return y_dtype == NVE_DT_F32 ? gemm_mb<false, NVE_DT_F32>(p, st) : gemm_mb<false, NVE_DT_F16>(p, st);
-    }
-    return y_dtype == NVE_DT_F32 ? gemm_mb<true, NVE_DT_F32>(p, st) : gemm_mb<true, NVE_DT_BF16>(p, st);
+    if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 8)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    return run_gemm(X, x_dtype, nibbles, scales, Y, y_dtype, M, N, K, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_gemm_error(int reset) {
@@ -764,26 +782,14 @@ extern "C" int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uin
     if (M < 1 || M > 64 || N < 1 || K < kKBlock || (K % kKBlock) != 0) return set_status(NVE_ERR_BAD_SHAPE);
     if (x_dtype != NVE_DT_F16 && x_dtype != NVE_DT_BF16) return set_status(NVE_ERR_BAD_DTYPE);
     if (y_dtype != x_dtype && y_dtype != NVE_DT_F32) return set_status(NVE_ERR_BAD_DTYPE);
-    if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 4)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 8)) return set_status(NVE_ERR_BAD_ALIGNMENT);
     const int ks = choose_ksplit(N, K, true);
-    const size_t need = ks > 1 ? static_cast<size_t>(ks) * M * N : 0;  // floats
-    if (need > kStaticScratchFloats) return set_status(NVE_ERR_TOO_LARGE);
+    const size_t need = (x_dtype == NVE_DT_BF16 ? x16_region_bytes(M, K) : 0) +
+                        (ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0);
+    if (need > kStaticScratchFloats * sizeof(float)) return set_status(NVE_ERR_TOO_LARGE);
     float* scratch = nullptr;
     int st = static_scratch_address(&scratch);
     if (st != NVE_OK) return st;
-    GemmParams p;
-    p.X = static_cast<const uint16_t*>(X);
-    p.nib = nibbles;
-    p.sc = scales;
-    p.Y = Y;
-    p.M = M; p.N = N; p.K = K;
-    p.nb = K / 32;
-    p.kblocks = K / kKBlock;
-    p.ksplit = ks;
-    p.partial = scratch;
-    cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (x_dtype == NVE_DT_F16) {
-        return y_dtype == NVE_DT_F32 ? gemm_mb<false, NVE_DT_F32>(p, cs) : gemm_mb<false, NVE_DT_F16>(p, cs);
-    }
-    return y_dtype == NVE_DT_F32 ? gemm_mb<true, NVE_DT_F32>(p, cs) : gemm_mb<true, NVE_DT_BF16>(p, cs);
+    return run_gemm(X, x_dtype, nibbles, scales, Y, y_dtype, M, N, K, scratch, kStaticScratchFloats * sizeof(float),
+                    static_cast<cudaStream_t>(stream));
 }

@@ -483,10 +483,13 @@ def gemm_w4a16_scratch_bytes(m: int, n: int, k: int) -> int:
 def gemm_w4a16(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out_dtype=None, out: Optional[Tensor] = None,
                scratch: Optional[Tensor] = None) -> Tensor:
     """Batched W4A16 GEMM on the tensor cores: x [M, K] (f16/bf16), M <= 64 -> [M, n].  `scratch` (uint8/float
-    tensor of gemm_w4a16_scratch_bytes) enables split-K for small n."""
+    tensor of gemm_w4a16_scratch_bytes) enables split-K for small n; bf16 activations need it for their f16 copy
+    (allocated here when not given)."""
     m = x.shape[0]
     out_dtype = x.dtype if out_dtype is None else out_dtype
     out = torch.empty((m, n), dtype=out_dtype, device=x.device) if out is None else out
+    if scratch is None and x.dtype == torch.bfloat16:  # the library needs room for an f16 copy of bf16 activations
+        scratch = torch.empty(((m * k * 2 + 255) // 256) * 256, dtype=torch.uint8, device=x.device)
     sb = 0 if scratch is None else scratch.numel() * scratch.element_size()
     _ffi.check("nve_b200_gemm_w4a16",
                _lib().nve_b200_gemm_w4a16(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x), _ptr(nibbles, torch.uint8),
