@@ -9,28 +9,30 @@
 // Mapping: the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), the batch is the MMA N dimension
 // (16 / 32 / 64), K advances 64 elements per pipeline stage, 16 per instruction.
 //   D[128 x MB] (TMEM, f32) += A[128 x 64] (dequantised f16 weights, TMEM: lane = row, 2 elements per column)
-//                            * B[MB x 64]  (f16 activations, shared memory, K-major, SWIZZLE_128B)
+//                            * B[MB x 64]  (f16 activations, shared memory, K-major, SWIZZLE_128B, loaded by TMA)
 // TMEM columns: four accumulator sets of MB columns, then 12 (MB = 64: 8) operand stages of 32 columns.  Eight to
 // twelve stages (two or three super-blocks of four K blocks) decouple the dequantisers from the MMA round trip
 // (arrive -> issue -> commit -> wake-up, about a microsecond).
 // Weights are always dequantised to f16, the type the reference dequantises to; bf16 activations are converted
-// to f16 while the tile is staged (bf16 weights would cost 2^-8 per weight and leave no tolerance margin).
+// to f16 by a small pre-pass into the caller's scratch (bf16 weights would cost 2^-8 per weight and leave no
+// tolerance margin; tcgen05.mma kind::f16 takes both operands in one format).
 // Roles in a CTA of 640 threads:
-//   warps 0-15 producers: cp.async ring of raw nibbles + scales in super-stages of 256 weights per row (coalesced
-//              along K: a warp-wide copy touches 4 cache lines), one producer barrier per super-stage.  Four groups
-//              of four warps (thread = weight row = TMEM lane); per super-block group g dequantises K block g:
-//              (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the multiply), tcgen05.st
-//              into the stage's columns, activation tile into shared memory, tcgen05.wait::st + fence.proxy.async,
-//              one arrival per warp on the stage's "full" mbarrier.
+//   warps 0-15 producers, two teams of eight warps that take alternate super-blocks (256 weights per row), each
+//              with its own named barrier and its own cp.async ring of raw nibbles + scales (coalesced along K:
+//              a warp-wide copy touches 4 cache lines; three super-stages per team).  A team is two groups of four
+//              warps (thread = weight row = TMEM lane); group g dequantises K blocks 2g and 2g+1 of the team's
+//              super-block: (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the multiply),
+//              tcgen05.st into the stage's columns, tcgen05.wait::st, one arrival per warp on the stage's "full"
+//              mbarrier.  One lane per group issues the TMA tile load of the stage's activations, which completes
+//              on the same barrier (expect_tx).
 //   warps 16-19 issue tcgen05.mma (one lane each): warp 16+w takes K block w of every super-block into accumulator
 //              set w, tcgen05.commit -> "empty" mbarrier of the stage, and after its last K block -> the
 //              accumulator barrier.  Issuing costs a thread ~70 cycles per MMA and ~150 per commit whatever the
 //              shape, which is why four warps share it.  Warp 16 also allocates and frees the TMEM columns.
-//   warps 0-3  epilogue: tcgen05.ld (32 lanes x MB columns per warp), convert, store Y (or f32 split-K
-//              partials to scratch, reduced in fixed order by a second small kernel).
-// Inside a 64-wide K block both operands use the same fixed permutation of K inside every 8-element chunk
-// ([0,2,1,3,4,6,5,7]), which is what the cheapest nibble extraction produces; a GEMM is invariant to a
-// permutation of K applied to both operands.
+//   warps 0-3  epilogue: tcgen05.ld (32 lanes x MB columns per warp, the four sets added in ascending order),
+//              convert, store Y (or f32 split-K partials to scratch, reduced in fixed order by a second kernel).
+// K order is natural in both operands: one byte permute per raw word puts the two nibbles of consecutive
+// elements 16 bits apart, where a half2 wants them.
 // Every mbarrier wait is bounded in time; an expired wait latches an error code (nve_b200_gemm_error) and the
 // CTA leaves through the normal path, freeing its TMEM columns.
 #include <cuda.h>
@@ -66,12 +68,6 @@ constexpr int kGemmThreads = kProducerThreads + 32 * kMmaWarps;
 constexpr unsigned long long kGemmWaitLimitNs = 50ull * 1000 * 1000;  // a legitimate wait lasts microseconds
 
 __device__ int g_gemm_device_error = 0;
-#ifdef NVE_GEMM_TRACE
-__device__ long long g_trace[5][64][8];
-#define TRACE(w, i, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 64) g_trace[w][i][k] = clock64(); } while (0)
-#else
-#define TRACE(w, i, k) do {} while (0)
-#endif
 
 struct GemmParams {
     const uint16_t* X;     // [M, K] 16-bit
@@ -507,9 +503,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             bool issued = false;
             for (int sb = 0; sb * kSuper + w < nkb; sb++) {
                 const int so = (sb % kSlots) * kSuper + w;
-                if (w == 0) TRACE(4, sb, 0);
                 const bool ready = mb_wait(&full[so], static_cast<unsigned>(sb / kSlots) & 1u);
-                if (w == 0) TRACE(4, sb, 1);
                 if (!ready || *reinterpret_cast<volatile int*>(abort_flag)) {
                     atomicCAS(&g_gemm_device_error, 0, 2);
                     atomicExch(abort_flag, 1);
@@ -523,9 +517,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
                     umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
                 }
-                if (w == 0) TRACE(4, sb, 2);
                 umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
-                if (w == 0) TRACE(4, sb, 3);
                 issued = true;
             }
             // this warp's accumulator set is complete (on an abandoned run the epilogue is not waiting any more)
@@ -542,11 +534,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     }
 }
 
-#ifdef NVE_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int nve_dbg_trace(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 5 * 64 * 8);
-}
-#endif
 // Sum the split-K partials in ascending split order and convert.
 template <int ODT> __global__ void gemm_splitk_reduce_kernel(const float* partial, void* Y, int ksplit, long long mn) {
     pdl_wait();
