@@ -78,11 +78,8 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle port)
-def cpu_layer_sample(shape, seed: int, budget_s: float):
-    """Time the reference CPU path for ONE layer's seven Q4 GEMVs (src/quantize.rs:466-488 matvec_f32 with
-    the AVX2 inner loop and rows in parallel) on all host threads; returns (seconds per layer, threads, reps)."""
-    import numpy as np
-
+def cpu_layer_mats(shape, seed: int):
+    """The 7 quantised projections of one layer plus an f32 activation vector each, and the thread count."""
     import oracle
     from nve_b200.bench_random import PROJ_STREAMS, proj_dims
 
@@ -93,13 +90,25 @@ def cpu_layer_sample(shape, seed: int, budget_s: float):
         w = oracle.fill_normal(n * k, seed, 1000 + PROJ_STREAMS[name], scale=0.02).reshape(n, k)
         mats.append((oracle.quantize_q4(w), oracle.fill_normal(k, seed, 77)))
         del w
-    for blocks, x in mats:  # warm-up
+    return mats, threads
+
+
+def cpu_one_layer(mats) -> None:
+    import oracle
+
+    for blocks, x in mats:
         oracle.q4_matvec_mt(blocks, x)
+
+
+def cpu_layer_sample(shape, seed: int, budget_s: float):
+    """Time one layer's 7 CPU Q4 GEMVs (the oracle's port of the reference's AVX2 path) for about budget_s seconds:
+    (seconds per layer, threads, repetitions)."""
+    mats, threads = cpu_layer_mats(shape, seed)
+    cpu_one_layer(mats)  # warm-up
     t0 = time.perf_counter()
     reps = 0
     while True:
-        for blocks, x in mats:
-            oracle.q4_matvec_mt(blocks, x)
+        cpu_one_layer(mats)
         reps += 1
         if time.perf_counter() - t0 > budget_s or reps >= 200:
             break
@@ -113,29 +122,13 @@ def run_reference(args) -> None:
     from nve_b200.bench_random import SHAPES
 
     shape = SHAPES[MODEL]
-    import numpy as np
-
-    import oracle
-    from nve_b200.bench_random import PROJ_STREAMS, proj_dims
-
-    threads = os.cpu_count() or 1
-    oracle.set_threads(threads)
-    mats = []
-    for name, (n, k) in proj_dims(shape).items():
-        w = oracle.fill_normal(n * k, SEED, 1000 + PROJ_STREAMS[name], scale=0.02).reshape(n, k)
-        mats.append((oracle.quantize_q4(w), oracle.fill_normal(k, SEED, 77)))
-        del w
-
-    def one_layer():
-        for blocks, x in mats:
-            oracle.q4_matvec_mt(blocks, x)
-
+    mats, threads = cpu_layer_mats(shape, SEED)
     for _ in range(max(1, args.warmup)):
-        one_layer()
+        cpu_one_layer(mats)
     steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
-        one_layer()
+        cpu_one_layer(mats)
     dt = (time.perf_counter() - t0) / steps
     tok_s = 1.0 / (dt * shape.num_layers)
     sample = (f"one layer (7 Q4 GEMVs, f32 activations) per step on {threads} threads, AVX2 inner loop; "
@@ -149,6 +142,9 @@ def run_reference(args) -> None:
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(line)
+
+
+NCU_TRAFFIC_RATIO = 1.0136  # (73.433 MB read + 0.967 MB written) / 73.400 MB algorithmic
 
 
 def workload_name() -> str:
@@ -291,7 +287,11 @@ def run_ours(args) -> None:
         "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
         "frac_of_8tbs_nominal": achieved / 8000.0, "launches_per_step": gemv_launches,
         "bytes_per_launch": gemv_bytes / gemv_launches, "us_per_launch": ms_gemv * 1e3 / gemv_launches,
-        "traffic": None,
+        # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of the gate/up launch in
+        # profiles/gemv_w4a8_gate_up_8b_ncu.md (74.40 MB against 73.40 MB of packed weights: every block is
+        # touched once, so traffic grows with the matrix) scaled to the average launch of the step
+        "traffic": NCU_TRAFFIC_RATIO * gemv_bytes / gemv_launches,
+        "traffic_source": "ncu capture of the gate/up launch (4-layer case, > L2), scaled by algorithmic bytes",
     }
 
     # ---- CPU baseline on a bounded sample (rank 0, N=1 only)
