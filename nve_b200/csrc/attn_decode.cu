@@ -11,8 +11,9 @@
 //   * 256 threads = PL position lanes x DC dim chunks (DC = head_dim/8 lanes hold one 16-byte slice of a
 //     row).  Each thread loads K and V of 4 positions per iteration (8 loads in flight), reduces the QH dot
 //     products over its DC lanes with xor shuffles and keeps a private online-softmax state.
-//   * The 256 thread states are merged through shared memory, the 8 CTA partials through distributed
-//     shared memory by rank 0 -- no global scratch, no second launch.
+//   * The 256 thread states are merged through shared memory; every CTA then pushes its partial into rank 0's
+//     shared memory (distributed shared memory stores), arrives on the cluster barrier and leaves; rank 0 waits
+//     and merges locally -- no global scratch, no second launch, no remote read round trip.
 //   * Fused form: q and the new k are rotated in-kernel (same IEEE operations and 16-bit rounding as the
 //     stand-alone RoPE kernel); the CTA that owns position `pos` takes the fresh k/v from shared memory
 //     instead of the cache, and one CTA per KV head writes them to the cache.
@@ -73,9 +74,8 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     __shared__ __align__(16) uint16_t vnew_s[HD];
     __shared__ float pm[PL][QH], ps[PL][QH];
     __shared__ float pacc[PL][QH][HD];
-    __shared__ AdCtaPartial<HD, QH> cta_part;
+    __shared__ AdCtaPartial<HD, QH> parts[kAdCluster];  // only rank 0's copy is used: every CTA pushes its partial there
 
-    pdl_wait();
     const int tid = threadIdx.x;
     const int dc = tid % DC, pl = tid / DC;
     const int rank = static_cast<int>(cluster.block_rank());
@@ -85,11 +85,36 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const int kvh = cluster_id / clusters_per_kv;
     const int h0 = kvh * groups + (cluster_id % clusters_per_kv) * QH;  // first query head of this cluster
 
-    int seq_len = p.d_seq_len != nullptr ? *p.d_seq_len : p.seq_len;
+    const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
+    const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
+
+    // Fused form: the cache rows of earlier positions were written by earlier steps, so the first batch of K/V
+    // loads can be in flight while the kernel still waits for its predecessor (which produces q and the new k/v,
+    // not the cache).  The scalars read here are only a guess used for addressing: they are read again after the
+    // wait and the prefetched rows are dropped if anything differs.
+    int pre_seq = -1, pre_pos = -2;
+    uint4 kpre[kAdUnroll], vpre[kAdUnroll];
+    if constexpr (FUSED) {
+        pre_seq = max(0, min(*p.d_seq_len, p.kv_stride));
+        pre_pos = *p.d_pos;
+        const int pchunk = (pre_seq + kAdCluster - 1) / kAdCluster;
+        const int pb = rank * pchunk, pe = min(pre_seq, pb + pchunk);
+#pragma unroll
+        for (int u = 0; u < kAdUnroll; u++) {
+            const int t = pb + u * PL + pl;
+            const int tc = t < pe ? t : (pb < p.kv_stride ? pb : 0);
+            kpre[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
+            vpre[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
+        }
+    }
+    pdl_wait();
+
+    int seq_len = p.d_seq_len != nullptr ? *reinterpret_cast<const volatile int*>(p.d_seq_len) : p.seq_len;
     seq_len = max(0, min(seq_len, p.kv_stride));
     int pos = -1;
-    if constexpr (FUSED) pos = *p.d_pos;
+    if constexpr (FUSED) pos = *reinterpret_cast<const volatile int*>(p.d_pos);
     const bool pos_ok = FUSED && pos >= 0 && pos < p.kv_stride;
+    const bool pre_ok = FUSED && pre_seq == seq_len && pre_pos == pos;
 
     // ---- stage q (rotated in the fused form) and the new k / v row
     if constexpr (FUSED) {
@@ -129,9 +154,6 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const int chunk = (seq_len + kAdCluster - 1) / kAdCluster;
     const int t_begin = rank * chunk;
     const int t_end = min(seq_len, t_begin + chunk);
-    const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
-    const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
-
     // one CTA per KV head stores the new row; every CTA that covers `pos` reads it from shared memory
     if constexpr (FUSED) {
         if (pos_ok && rank == 0 && (cluster_id % clusters_per_kv) == 0 && tid < 2 * DC) {
@@ -163,6 +185,9 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
             if (FUSED && tc == pos) {
                 kraw[u] = reinterpret_cast<const uint4*>(knew_s)[dc];
                 vraw[u] = reinterpret_cast<const uint4*>(vnew_s)[dc];
+            } else if (FUSED && it == 0 && pre_ok) {
+                kraw[u] = kpre[u];  // same t_begin, same t: the address computed before the wait
+                vraw[u] = vpre[u];
             } else {
                 kraw[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
                 vraw[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
@@ -228,43 +253,44 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
             ss = fmaf(ps[l][h], c, ss);
             a = fmaf(pacc[l][h][d], c, a);
         }
-        cta_part.acc[h][d] = a;
-        if (d == 0) { cta_part.m[h] = mm; cta_part.s[h] = ss; }
+        // push this CTA's partial into rank 0's shared memory (posted remote stores, no round trip)
+        AdCtaPartial<HD, QH>* dst = cluster.map_shared_rank(&parts[rank], 0);
+        dst->acc[h][d] = a;
+        if (d == 0) { dst->m[h] = mm; dst->s[h] = ss; }
     }
-    cluster.sync();
+    // release the stores / acquire everybody's; only rank 0 has anything left to do, the others arrive and leave
+    cluster.barrier_arrive();
+    if (rank != 0) return;
+    cluster.barrier_wait();
 
-    // ---- rank 0 merges the CTA partials through distributed shared memory, normalises and stores
-    if (rank == 0) {
-        for (int i = tid; i < QH * HD; i += kAdThreads) {
-            const int h = i / HD, d = i % HD;
-            float mm = -1e30f;
+    // ---- rank 0 merges the CTA partials from its own shared memory, normalises and stores
+    for (int i = tid; i < QH * HD; i += kAdThreads) {
+        const int h = i / HD, d = i % HD;
+        float mm = -1e30f;
 #pragma unroll
-            for (int r = 0; r < kAdCluster; r++) mm = fmaxf(mm, cluster.map_shared_rank(&cta_part, r)->m[h]);
-            float ss = 0.0f, a = 0.0f;
+        for (int r = 0; r < kAdCluster; r++) mm = fmaxf(mm, parts[r].m[h]);
+        float ss = 0.0f, a = 0.0f;
 #pragma unroll
-            for (int r = 0; r < kAdCluster; r++) {
-                const AdCtaPartial<HD, QH>* rp = cluster.map_shared_rank(&cta_part, r);
-                const float c = expf(rp->m[h] - mm);
-                ss = fmaf(rp->s[h], c, ss);
-                a = fmaf(rp->acc[h][d], c, a);
-            }
-            const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
-            const uint16_t o16 = Act16<NVE_DT_F16>::from_f32(a * inv);
-            const long long oi = static_cast<long long>(h0 + h) * HD + d;
-            p.out[oi] = o16;
-            if (p.out_q != nullptr) {
-                // i advances by whole warps and HD is a multiple of 32: the 32 lanes of a warp hold one group
-                const float v = Act16<NVE_DT_F16>::to_f32(o16);
-                const float amax = warp_max(fabsf(v));
-                const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-                int qv = __float2int_rn(__fmul_rn(v, __fdiv_rn(1.0f, scale)));
-                qv = max(-127, min(127, qv));
-                p.out_q[oi] = static_cast<int8_t>(qv);
-                if ((tid & 31) == 0) p.out_scales[oi >> 5] = scale;
-            }
+        for (int r = 0; r < kAdCluster; r++) {
+            const float c = expf(parts[r].m[h] - mm);
+            ss = fmaf(parts[r].s[h], c, ss);
+            a = fmaf(parts[r].acc[h][d], c, a);
+        }
+        const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
+        const uint16_t o16 = Act16<NVE_DT_F16>::from_f32(a * inv);
+        const long long oi = static_cast<long long>(h0 + h) * HD + d;
+        p.out[oi] = o16;
+        if (p.out_q != nullptr) {
+            // i advances by whole warps and HD is a multiple of 32: the 32 lanes of a warp hold one group
+            const float v = Act16<NVE_DT_F16>::to_f32(o16);
+            const float amax = warp_max(fabsf(v));
+            const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            int qv = __float2int_rn(__fmul_rn(v, __fdiv_rn(1.0f, scale)));
+            qv = max(-127, min(127, qv));
+            p.out_q[oi] = static_cast<int8_t>(qv);
+            if ((tid & 31) == 0) p.out_scales[oi >> 5] = scale;
         }
     }
-    cluster.sync();  // keep every CTA's shared memory alive until rank 0 has read it
 }
 
 template <int HD, int QH, bool FUSED> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
