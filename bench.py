@@ -148,8 +148,14 @@ NCU_TRAFFIC_RATIO = 1.0136  # (73.433 MB read + 0.967 MB written) / 73.400 MB al
 
 
 def workload_name() -> str:
-    return ("Llama-3.1-8B-shaped decode stack, batch 1, 32 layers, hidden 4096, FFN 14336, GQA 32/8, head_dim 128, "
-            "context 1024, 4-bit group-32 weights ~N(0,0.02), W4A8/W4A16 routed per layer from seeded scores (16/16)")
+    from nve_b200.bench_random import SHAPES
+
+    s = SHAPES[MODEL]
+    family = {"8b": "Llama-3.1-8B", "70b": "Llama-3-70B", "1b": "Llama-3.2-1B", "3b": "Llama-3.2-3B"}[MODEL]
+    half = s.num_layers // 2
+    return (f"{family}-shaped decode stack, batch 1, {s.num_layers} layers, hidden {s.hidden}, FFN {s.ffn}, "
+            f"GQA {s.num_heads}/{s.num_kv_heads}, head_dim {s.head_dim}, context {CONTEXT}, 4-bit group-32 weights "
+            f"~N(0,0.02), W4A8/W4A16 routed per layer from seeded scores ({s.num_layers - half}/{half})")
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -311,7 +317,7 @@ def run_ours(args) -> None:
         "config": {"workload": workload_name(), "model_shape": MODEL, "context": CONTEXT, "batch": 1,
                    "activations": "f16 (the reference ABI's activation type)", "kv_cache": "f16",
                    "w4a8_layers": int(sum(routes)), "w4a16_layers": int(len(routes) - sum(routes)),
-                   "parallelism": "tp1", "l2_policy": "inputs larger than L2: 4.36 GB of weights streamed per step",
+                   "parallelism": "tp1", "l2_policy": f"inputs larger than L2: {total_bytes / 1e9:.2f} GB streamed per step",
                    "launches_per_step": launches_per_step, "graph": "one CUDA graph per token",
                    "programmatic_dependent_launch": pdl},
         "hbm_gbs_whole_step": total_bytes / (ms_step * 1e-3) / 1e9,
@@ -341,7 +347,7 @@ def emit(line: dict) -> None:
 def main() -> None:
     # Libraries (NCCL, for one) print banners on file descriptor 1; keep stdout for the single JSON line by
     # pointing descriptor 1 at stderr for everything else.
-    global _REAL_STDOUT
+    global _REAL_STDOUT, MODEL
     sys.stdout.flush()
     _REAL_STDOUT = os.fdopen(os.dup(1), "w")
     os.dup2(2, 1)
@@ -351,7 +357,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default=MODEL, choices=["1b", "3b", "8b", "70b"],
+                    help="shape of the synthetic stack; the default is the configuration the headline metric names")
     args = ap.parse_args()
+    MODEL = args.model
     args.warmup = max(3, args.warmup) if args.impl == "ours" else max(1, args.warmup)
     if args.impl == "reference":
         run_reference(args)

@@ -185,6 +185,15 @@ NVE_API int nve_b200_rms_norm(const void* x, const void* weight, void* out, int 
 NVE_API int nve_b200_silu_mul_quantize_q8(const void* gate, const void* up, void* mid_out, int8_t* xq, float* scales,
                                   int n, int dtype, nve_stream_t stream);
 
+/* Fused silu(gate)*up -> 16-bit round -> [* awq] -> 16-bit fixed point per group of 32 (v = rint(x * 32767 / amax),
+ * low bytes to x_lo, high bytes to x_hi, amax / 32767 to x_scales): the activation form the W4A16 GEMV multiplies
+ * with, produced once here instead of by every CTA of the GEMV (nve_b200_matvec_w4a16_planes_multi consumes it).
+ * No counterpart in the reference (src/gpu_layer.rs:977-980 feeds the f16 product to nve_matvec_w4a16); the
+ * results are bit-identical to nve_b200_silu_mul followed by nve_b200_matvec_w4a16_multi.  mid_out and awq may
+ * be NULL; n % 32 == 0. */
+NVE_API int nve_b200_silu_mul_x16(const void* gate, const void* up, void* mid_out, uint8_t* x_lo, int8_t* x_hi,
+                                  float* x_scales, const float* awq, int n, int dtype, nve_stream_t stream);
+
 /* silu(gate)*up and residual add with selectable 16-bit type. */
 NVE_API int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_stream_t stream);
 NVE_API int nve_b200_add_inplace(void* dst, const void* src, int n, int dtype, nve_stream_t stream);
@@ -207,6 +216,12 @@ NVE_API int nve_b200_matvec_w4a8_multi(const int8_t* xq, const float* xq_scales,
  * matrices of the call).  Arithmetic as nve_matvec_w4a16 (cuda/nve_kernels.cu:349-370). */
 NVE_API int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mats,
                                 int num_mats, int K, int out_dtype, nve_stream_t stream);
+
+/* W4A16 GEMV over 1..3 matrices whose activations are already in the 16-bit fixed-point plane form written by
+ * nve_b200_silu_mul_x16 (x_lo / x_hi [K], x_scales [K/32]; all 16-byte aligned). */
+NVE_API int nve_b200_matvec_w4a16_planes_multi(const uint8_t* x_lo, const int8_t* x_hi, const float* x_scales,
+                                               const nve_b200_w4_matrix* mats, int num_mats, int K, int out_dtype,
+                                               nve_stream_t stream);
 
 /* The same GEMVs with the RMSNorm of the input fused into the kernel prologue: h is the un-normalised
  * 16-bit hidden state (act_dtype f16/bf16), norm_weight its RMSNorm weight.  Every CTA recomputes the norm
@@ -273,6 +288,13 @@ NVE_API size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K);
 NVE_API int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
                                 int y_dtype, int M, int N, int K, void* scratch, size_t scratch_bytes,
                                 nve_stream_t stream);
+/* The same GEMM over 1..3 matrices that share X (q/k/v, gate/up) in one launch: mats[i].{nibbles, scales, out, N},
+ * out [M, N_i] row-major, residual must be NULL.  Their 128-row tiles are laid side by side over the grid and
+ * split-K is chosen for the total, which is what lets the narrow k and v projections fill the GPU. */
+NVE_API size_t nve_b200_gemm_w4a16_multi_scratch_bytes(int M, const int* Ns, int num_mats, int K);
+NVE_API int nve_b200_gemm_w4a16_multi(const void* X, int x_dtype, const nve_b200_w4_matrix* mats, int num_mats,
+                                      int y_dtype, int M, int K, void* scratch, size_t scratch_bytes,
+                                      nve_stream_t stream);
 NVE_API int nve_b200_gemm_error(int reset);
 
 /* Allocation-free form of nve_b200_gemm_w4a16.  No counterpart in the reference: it exists for callers that have

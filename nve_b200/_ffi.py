@@ -92,10 +92,12 @@ SIGNATURES = {
     "nve_b200_rmsnorm_quantize_q8": (_I, [_P, _P, _P, _P, _P, _I, _F, _I, _P]),
     "nve_b200_rms_norm": (_I, [_P, _P, _P, _I, _F, _I, _P]),
     "nve_b200_silu_mul_quantize_q8": (_I, [_P, _P, _P, _P, _P, _I, _I, _P]),
+    "nve_b200_silu_mul_x16": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "nve_b200_silu_mul": (_I, [_P, _P, _I, _I, _P]),
     "nve_b200_add_inplace": (_I, [_P, _P, _I, _I, _P]),
     "nve_b200_matvec_w4a8_multi": (_I, [_P, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_matvec_w4a16_multi": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
+    "nve_b200_matvec_w4a16_planes_multi": (_I, [_P, _P, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a8_multi": (_I, [_P, _P, _F, _I, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a16_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_attn_decode_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
@@ -105,6 +107,8 @@ SIGNATURES = {
     "nve_b200_q4_repack_blocks": (_I, [_P, _P, _P, _I, _I, _P]),
     "nve_b200_gemm_w4a16_scratch_bytes": (_S, [_I, _I, _I]),
     "nve_b200_gemm_w4a16": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _S, _P]),
+    "nve_b200_gemm_w4a16_multi_scratch_bytes": (_S, [_I, _P, _I, _I]),
+    "nve_b200_gemm_w4a16_multi": (_I, [_P, _I, C.POINTER(W4Matrix), _I, _I, _I, _I, _P, _S, _P]),
     "nve_b200_gemm_error": (_I, [_I]),
     "nve_b200_gemm_w4a16_noalloc": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P]),
     "nve_b200_tp_create": (_I, [_I, _I, _I, _P]),

@@ -188,14 +188,13 @@ def _main() -> None:
     if a.batch > 1:
         xb = ck.fill_normal(a.batch * k, 1, 998, dtype=torch.float16).view(a.batch, k)
         yb = [torch.empty((a.batch, n), dtype=torch.float16, device="cuda") for n in ns]
-        nbytes_s = max(ck.gemm_w4a16_scratch_bytes(a.batch, n, k) for n in ns)
+        nbytes_s = ck.gemm_w4a16_multi_scratch_bytes(a.batch, ns, k)
         scratch = torch.empty(max(nbytes_s, 16), dtype=torch.uint8, device="cuda")
 
     def launches(_a=None, _b=None):
         for li in range(a.layers):
-            if a.batch > 1:  # one GEMM per matrix of the group
-                for w, y in zip(ws[li], yb):
-                    ck.gemm_w4a16(xb, w.nibbles, w.scales, w.n, k, out=y, scratch=scratch)
+            if a.batch > 1:  # the matrices of the group in one GEMM launch
+                ck.gemm_w4a16_multi(xb, [w.triple() for w in ws[li]], k, outs=yb, scratch=scratch)
                 continue
             trip = [w.triple() for w in ws[li]]
             if a.route == "w4a8":

@@ -167,9 +167,25 @@ __device__ __forceinline__ float silu_mul_f32(float g, float u) {
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
-template <int DT, bool QUANT>
+// Write the 16-bit fixed-point planes of the 8 values of this thread (the 4 threads of a quad hold one group).
+__device__ __forceinline__ void x16_quad(const float (&v)[8], uint8_t* xlo, int8_t* xhi, float* scales, long long chunk,
+                                         bool active) {
+    uint32_t l0, l1, h0, h1;
+    int sum;
+    const float scale = x16_quad_convert(v, l0, l1, h0, h1, sum);
+    if (active) {
+        reinterpret_cast<uint2*>(xlo)[chunk] = make_uint2(l0, l1);
+        reinterpret_cast<uint2*>(xhi)[chunk] = make_uint2(h0, h1);
+        if ((chunk & 3) == 0) scales[chunk >> 2] = scale;
+    }
+}
+
+// QUANT: 0 = 16-bit output only, 1 = + int8 codes (W4A8 route), 2 = + 16-bit fixed-point planes (W4A16 route; `awq`,
+// if given, multiplies each element first, as the W4A16 GEMV's own staging does).
+template <int DT, int QUANT>
 __global__ void __launch_bounds__(kActThreads) silu_mul_kernel(const uint16_t* gate, const uint16_t* up, uint16_t* out,
-                                                               int8_t* xq, float* scales, int n) {
+                                                               int8_t* xq, float* scales, int n, uint8_t* xlo,
+                                                               const float* awq) {
     pdl_wait();
     const long long c = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const bool active = c * 8 < n;
@@ -186,7 +202,14 @@ __global__ void __launch_bounds__(kActThreads) silu_mul_kernel(const uint16_t* g
         if (out != nullptr) store_chunk<true>(out, c, n, ho);
     }
     pdl_launch_dependents();
-    if constexpr (QUANT) quantize_quad(v, xq, scales, c, active);
+    if constexpr (QUANT == 1) quantize_quad(v, xq, scales, c, active);
+    if constexpr (QUANT == 2) {
+        if (active && awq != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], awq[c * 8 + e]);
+        }
+        x16_quad(v, xlo, xq, scales, c, active);
+    }
 }
 
 template <int DT> __global__ void silu_mul_scalar_kernel(uint16_t* gate, const uint16_t* up, int n) {
@@ -296,8 +319,9 @@ static int rmsnorm_impl(const void* x, const void* w, void* out, int8_t* xq, flo
     return set_cuda_status(e);
 }
 
-template <int DT, bool QUANT>
-static int silu_mul_impl(const void* gate, const void* up, void* out, int8_t* xq, float* scales, int n, cudaStream_t st) {
+template <int DT, int QUANT>
+static int silu_mul_impl(const void* gate, const void* up, void* out, int8_t* xq, float* scales, int n, cudaStream_t st,
+                         uint8_t* xlo = nullptr, const float* awq = nullptr) {
     if (!gate || !up) return set_status(NVE_ERR_BAD_POINTER);
     if (n <= 0) return set_status(NVE_ERR_BAD_SHAPE);
     const bool vec = (n % 8) == 0 && aligned(gate, 16) && aligned(up, 16) && (out == nullptr || aligned(out, 16));
@@ -305,6 +329,7 @@ static int silu_mul_impl(const void* gate, const void* up, void* out, int8_t* xq
         if (!xq || !scales) return set_status(NVE_ERR_BAD_POINTER);
         if ((n % 32) != 0) return set_status(NVE_ERR_BAD_SHAPE);
         if (!vec || !aligned(xq, 8)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+        if (QUANT == 2 && (!xlo || !aligned(xlo, 8))) return set_status(xlo ? NVE_ERR_BAD_ALIGNMENT : NVE_ERR_BAD_POINTER);
     }
     if (!vec) {
         if (out != gate) return set_status(NVE_ERR_BAD_ALIGNMENT);
@@ -317,7 +342,7 @@ static int silu_mul_impl(const void* gate, const void* up, void* out, int8_t* xq
     cudaLaunchAttribute attr[1];
     launch_cfg(cfg, attr, (n / 8 + kActThreads - 1) / kActThreads, st);
     cudaError_t e = cudaLaunchKernelEx(&cfg, silu_mul_kernel<DT, QUANT>, static_cast<const uint16_t*>(gate),
-                                       static_cast<const uint16_t*>(up), static_cast<uint16_t*>(out), xq, scales, n);
+                                       static_cast<const uint16_t*>(up), static_cast<uint16_t*>(out), xq, scales, n, xlo, awq);
     count_launch();
     return set_cuda_status(e);
 }
@@ -376,18 +401,25 @@ extern "C" int nve_b200_rmsnorm_quantize_q8(const void* x, const void* weight, v
 extern "C" int nve_b200_silu_mul_quantize_q8(const void* gate, const void* up, void* mid_out, int8_t* xq, float* scales,
                                              int n, int dtype, nve_stream_t stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return NVE_DISPATCH_16(dtype, (silu_mul_impl<NVE_DT_F16, true>(gate, up, mid_out, xq, scales, n, st)),
-                           (silu_mul_impl<NVE_DT_BF16, true>(gate, up, mid_out, xq, scales, n, st)));
+    return NVE_DISPATCH_16(dtype, (silu_mul_impl<NVE_DT_F16, 1>(gate, up, mid_out, xq, scales, n, st)),
+                           (silu_mul_impl<NVE_DT_BF16, 1>(gate, up, mid_out, xq, scales, n, st)));
+}
+
+extern "C" int nve_b200_silu_mul_x16(const void* gate, const void* up, void* mid_out, uint8_t* x_lo, int8_t* x_hi,
+                                     float* x_scales, const float* awq, int n, int dtype, nve_stream_t stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return NVE_DISPATCH_16(dtype, (silu_mul_impl<NVE_DT_F16, 2>(gate, up, mid_out, x_hi, x_scales, n, st, x_lo, awq)),
+                           (silu_mul_impl<NVE_DT_BF16, 2>(gate, up, mid_out, x_hi, x_scales, n, st, x_lo, awq)));
 }
 
 extern "C" int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_stream_t stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return NVE_DISPATCH_16(dtype, (silu_mul_impl<NVE_DT_F16, false>(gate, up, gate, nullptr, nullptr, n, st)),
-                           (silu_mul_impl<NVE_DT_BF16, false>(gate, up, gate, nullptr, nullptr, n, st)));
+    return NVE_DISPATCH_16(dtype, (silu_mul_impl<NVE_DT_F16, 0>(gate, up, gate, nullptr, nullptr, n, st)),
+                           (silu_mul_impl<NVE_DT_BF16, 0>(gate, up, gate, nullptr, nullptr, n, st)));
 }
 
 extern "C" void nve_silu_mul_f16(uint16_t* gate, const uint16_t* up, int n, nve_stream_t stream) {
-    silu_mul_impl<NVE_DT_F16, false>(gate, up, gate, nullptr, nullptr, n, static_cast<cudaStream_t>(stream));
+    silu_mul_impl<NVE_DT_F16, 0>(gate, up, gate, nullptr, nullptr, n, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_add_inplace(void* dst, const void* src, int n, int dtype, nve_stream_t stream) {

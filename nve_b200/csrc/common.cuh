@@ -186,4 +186,34 @@ __host__ __device__ __forceinline__ float gen_normal(unsigned long long st, unsi
     return static_cast<float>(s - 262140) * 0x1.3988e2p-16f;
 }
 
+// 16-bit fixed point of one 32-wide group held by the 4 threads of a quad (8 values each): v = rint(x * 32767 / amax),
+// split into an unsigned low-byte plane and a signed high-byte plane (the form the W4A16 GEMV multiplies with dp4a).
+// Returns the group's scale; `sum` is the sum of the group's 32 codes.
+__device__ __forceinline__ float x16_quad_convert(const float (&xe)[8], uint32_t& l0, uint32_t& l1, uint32_t& h0, uint32_t& h1,
+                                                  int& sum) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(xe[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float scale = amax > 0.0f ? __fdiv_rn(amax, 32767.0f) : 1.0f;
+    if (!(amax <= 3.0e38f)) scale = __int_as_float(0x7FC00000);
+    const float inv = __fdiv_rn(1.0f, scale);
+    l0 = l1 = h0 = h1 = 0;
+    sum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        int q = __float2int_rn(__fmul_rn(xe[e], inv));
+        q = max(-32767, min(32767, q));
+        sum += q;
+        const uint32_t lo8 = static_cast<uint32_t>(q) & 0xFFu;
+        const uint32_t hi8 = static_cast<uint32_t>(q >> 8) & 0xFFu;
+        if (e < 4) { l0 |= lo8 << (8 * e); h0 |= hi8 << (8 * e); }
+        else { l1 |= lo8 << (8 * (e - 4)); h1 |= hi8 << (8 * (e - 4)); }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    return scale;
+}
+
 }  // namespace nve

@@ -70,12 +70,15 @@ constexpr unsigned long long kGemmWaitLimitNs = 50ull * 1000 * 1000;  // a legit
 __device__ int g_gemm_device_error = 0;
 
 struct GemmParams {
-    const uint16_t* X;     // [M, K] 16-bit
-    const uint8_t* nib;    // [N, K/2]
-    const float* sc;       // [N, K/32]
-    void* Y;               // [M, N]
-    float* partial;        // [ksplit, M, N] f32 when ksplit > 1
-    int M, N, K;
+    const uint16_t* X;     // [M, K] f16
+    const uint8_t* nib[3]; // per matrix [N_i, K/2]
+    const float* sc[3];    // per matrix [N_i, K/32]
+    void* Y[3];            // per matrix [M, N_i]
+    int Nm[3];             // rows of each matrix
+    int tile_end[3];       // cumulative 128-row tiles
+    int col0[3];           // first column of each matrix in the concatenated [M, N] view
+    float* partial;        // [ksplit, M, N] f32 when ksplit > 1 (N = all matrices side by side)
+    int M, N, K;           // N = sum of Nm
     int nb;                // K / 32
     int kblocks;           // K / 64
     int ksplit;
@@ -262,7 +265,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kTileN;
+    // the tiles of the (up to three) matrices are laid side by side along blockIdx.x
+    const int tile = blockIdx.x;
+    const int mi = tile < p.tile_end[0] ? 0 : (tile < p.tile_end[1] ? 1 : 2);
+    const int n0 = (tile - (mi == 0 ? 0 : p.tile_end[mi - 1])) * kTileN;  // first row of the tile inside its matrix
+    const int Nloc = p.Nm[mi];
     const int split = blockIdx.y;
     const int kb_begin = static_cast<int>(static_cast<long long>(p.kblocks) * split / p.ksplit);
     const int kb_end = static_cast<int>(static_cast<long long>(p.kblocks) * (split + 1) / p.ksplit);
@@ -312,8 +319,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         for (int j = 0; j < kNibPer; j++) {
             const int id = tt + kTeamThreads * j;
             const int rr = id >> 3, c = id & 7;
-            const int grow = min(n0 + rr, p.N - 1);
-            gn[j] = p.nib + static_cast<long long>(grow) * (p.K / 2) + (kb_begin + team * kSuper) * 32 + c * 16;
+            const int grow = min(n0 + rr, Nloc - 1);
+            gn[j] = p.nib[mi] + static_cast<long long>(grow) * (p.K / 2) + (kb_begin + team * kSuper) * 32 + c * 16;
             sn[j] = s_addr(teamRawN) + rr * 128 + ((c ^ (rr & 7)) << 4);
             kn[j] = c >> 1;
         }
@@ -324,8 +331,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         for (int j = 0; j < kScPer; j++) {
             const int id = tt + kTeamThreads * j;
             const int rr = id >> 2, kbi = id & 3;
-            const int grow = min(n0 + rr, p.N - 1);
-            gs[j] = p.sc + static_cast<long long>(grow) * p.nb + (kb_begin + team * kSuper + kbi) * 2;
+            const int grow = min(n0 + rr, Nloc - 1);
+            gs[j] = p.sc[mi] + static_cast<long long>(grow) * p.nb + (kb_begin + team * kSuper + kbi) * 2;
             ss[j] = s_addr(teamRawS) + (rr * 8 + kbi * 2) * 4;
             ks[j] = kbi;
         }
@@ -480,13 +487,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 #pragma unroll
                         for (int j = 0; j < 8; j++) y[j] = a == 0 ? __uint_as_float(v[j]) : __fadd_rn(y[j], __uint_as_float(v[j]));
                     }
-                    if (n < p.N) {
+                    if (n < Nloc) {
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int m = cb + j;
                             if (m < p.M) {
-                                if (p.ksplit > 1) p.partial[(static_cast<long long>(split) * p.M + m) * p.N + n] = y[j];
-                                else store_out<ODT>(p.Y, static_cast<long long>(m) * p.N + n, y[j]);
+                                if (p.ksplit > 1) p.partial[(static_cast<long long>(split) * p.M + m) * p.N + p.col0[mi] + n] = y[j];
+                                else store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y[j]);
                             }
                         }
                     }
@@ -534,14 +541,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     }
 }
 
-// Sum the split-K partials in ascending split order and convert.
-template <int ODT> __global__ void gemm_splitk_reduce_kernel(const float* partial, void* Y, int ksplit, long long mn) {
+// Sum the split-K partials in ascending split order, convert and scatter to the matrices' outputs.
+template <int ODT> __global__ void gemm_splitk_reduce_kernel(const GemmParams p) {
     pdl_wait();
+    const long long mn = static_cast<long long>(p.M) * p.N;
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= mn) return;
-    float y = partial[i];
-    for (int s = 1; s < ksplit; s++) y = __fadd_rn(y, partial[static_cast<long long>(s) * mn + i]);
-    store_out<ODT>(Y, i, y);
+    float y = p.partial[i];
+    for (int s = 1; s < p.ksplit; s++) y = __fadd_rn(y, p.partial[static_cast<long long>(s) * mn + i]);
+    const int m = static_cast<int>(i / p.N), c = static_cast<int>(i - static_cast<long long>(m) * p.N);
+    const int mi = c < p.col0[1] ? 0 : (c < p.col0[2] ? 1 : 2);
+    store_out<ODT>(p.Y[mi], static_cast<long long>(m) * p.Nm[mi] + (c - p.col0[mi]), y);
 }
 
 static size_t gemm_smem_bytes(int mb) {
@@ -553,9 +563,12 @@ static size_t gemm_smem_bytes(int mb) {
     return need > half_sm ? need : half_sm;
 }
 
+static int choose_ksplit_tiles(int tiles, int K, bool have_scratch);
 static int choose_ksplit(int N, int K, bool have_scratch) {
+    return choose_ksplit_tiles((N + kTileN - 1) / kTileN, K, have_scratch);
+}
+static int choose_ksplit_tiles(int tiles, int K, bool have_scratch) {
     if (!have_scratch) return 1;
-    const int tiles = (N + kTileN - 1) / kTileN;
     int ks = sm_count() / tiles;
     const int kblocks = K / kKBlock;
     if (ks > kblocks / 8) ks = kblocks / 8;  // at least 8 K blocks (512 elements) per split
@@ -603,7 +616,7 @@ template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStrea
     int s = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(smem));
     if (s != NVE_OK) return s;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.N + kTileN - 1) / kTileN, p.ksplit);
+    cfg.gridDim = dim3(p.tile_end[2], p.ksplit);
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -619,7 +632,7 @@ template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStrea
     if (e != cudaSuccess) return set_cuda_status(e);
     if (p.ksplit > 1) {
         const long long mn = static_cast<long long>(p.M) * p.N;
-        gemm_splitk_reduce_kernel<ODT><<<static_cast<unsigned>((mn + 255) / 256), 256, 0, st>>>(p.partial, p.Y, p.ksplit, mn);
+        gemm_splitk_reduce_kernel<ODT><<<static_cast<unsigned>((mn + 255) / 256), 256, 0, st>>>(p);
         count_launch();
         return check_launch();
     }
@@ -653,8 +666,15 @@ static size_t x16_region_bytes(int M, int K) { return (static_cast<size_t>(M) * 
 
 // Shared by both entry points.  Scratch layout: [f16 copy of bf16 activations (x16_region_bytes)][split-K partials].
 // bf16 activations need the first region; split-K uses what is left.
-static int run_gemm(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y, int y_dtype, int M, int N,
-                    int K, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+struct GemmMat {
+    const uint8_t* nib;
+    const float* sc;
+    void* Y;
+    int N;
+};
+
+static int run_gemm_multi(const void* X, int x_dtype, const GemmMat* mats, int num_mats, int y_dtype, int M, int K, void* scratch,
+                          size_t scratch_bytes, cudaStream_t st) {
     unsigned char* sp = static_cast<unsigned char*>(scratch);
     GemmParams p;
     p.X = static_cast<const uint16_t*>(X);
@@ -671,18 +691,35 @@ static int run_gemm(const void* X, int x_dtype, const uint8_t* nibbles, const fl
         sp += xb;
         scratch_bytes -= xb;
     }
-    p.nib = nibbles;
-    p.sc = scales;
-    p.Y = Y;
-    p.M = M; p.N = N; p.K = K;
+    int tiles = 0, cols = 0;
+    for (int m = 0; m < 3; m++) {
+        const GemmMat& g = mats[m < num_mats ? m : 0];
+        p.nib[m] = g.nib; p.sc[m] = g.sc; p.Y[m] = g.Y;
+        p.Nm[m] = m < num_mats ? g.N : 0;
+        p.col0[m] = cols;
+        if (m < num_mats) {
+            tiles += (g.N + kTileN - 1) / kTileN;
+            cols += g.N;
+        }
+        p.tile_end[m] = tiles;
+    }
+    // matrices that are not there: col0 past the last column so that the reduce kernel never selects them
+    for (int m = num_mats; m < 3; m++) p.col0[m] = 0x7FFFFFFF;
+    p.M = M; p.N = cols; p.K = K;
     p.nb = K / 32;
     p.kblocks = K / kKBlock;
-    int ks = choose_ksplit(N, K, sp != nullptr);
-    while (ks > 1 && static_cast<size_t>(ks) * M * N * sizeof(float) > scratch_bytes) ks--;
+    int ks = choose_ksplit_tiles(tiles, K, sp != nullptr);
+    while (ks > 1 && static_cast<size_t>(ks) * M * cols * sizeof(float) > scratch_bytes) ks--;
     p.ksplit = ks;
     p.partial = reinterpret_cast<float*>(sp);
     if (y_dtype == NVE_DT_F32) return gemm_mb<NVE_DT_F32>(p, st);
     return y_dtype == NVE_DT_F16 ? gemm_mb<NVE_DT_F16>(p, st) : gemm_mb<NVE_DT_BF16>(p, st);
+}
+
+static int run_gemm(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y, int y_dtype, int M, int N,
+                    int K, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+    const GemmMat one = {nibbles, scales, Y, N};
+    return run_gemm_multi(X, x_dtype, &one, 1, y_dtype, M, K, scratch, scratch_bytes, st);
 }
 
 }  // namespace nve
@@ -693,6 +730,39 @@ extern "C" size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0 || (K % kKBlock) != 0) return 0;
     const int ks = choose_ksplit(N, K, true);
     return x16_region_bytes(M, K) + (ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0);
+}
+
+extern "C" size_t nve_b200_gemm_w4a16_multi_scratch_bytes(int M, const int* Ns, int num_mats, int K) {
+    if (M <= 0 || K <= 0 || (K % kKBlock) != 0 || Ns == nullptr || num_mats < 1 || num_mats > 3) return 0;
+    long long tiles = 0, cols = 0;
+    for (int m = 0; m < num_mats; m++) {
+        if (Ns[m] <= 0) return 0;
+        tiles += (Ns[m] + kTileN - 1) / kTileN;
+        cols += Ns[m];
+    }
+    const int ks = choose_ksplit_tiles(static_cast<int>(tiles), K, true);
+    return x16_region_bytes(M, K) + (ks > 1 ? static_cast<size_t>(ks) * M * cols * sizeof(float) : 0);
+}
+
+extern "C" int nve_b200_gemm_w4a16_multi(const void* X, int x_dtype, const nve_b200_w4_matrix* mats, int num_mats, int y_dtype,
+                                         int M, int K, void* scratch, size_t scratch_bytes, nve_stream_t stream) {
+    if (!X || !mats) return set_status(NVE_ERR_BAD_POINTER);
+    if (num_mats < 1 || num_mats > 3 || M < 1 || M > 64 || K < kKBlock || (K % kKBlock) != 0) return set_status(NVE_ERR_BAD_SHAPE);
+    if (x_dtype != NVE_DT_F16 && x_dtype != NVE_DT_BF16) return set_status(NVE_ERR_BAD_DTYPE);
+    if (y_dtype != x_dtype && y_dtype != NVE_DT_F32) return set_status(NVE_ERR_BAD_DTYPE);
+    if (!aligned(X, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    GemmMat g[3];
+    long long cols = 0;
+    for (int m = 0; m < num_mats; m++) {
+        if (!mats[m].nibbles || !mats[m].scales || !mats[m].out) return set_status(NVE_ERR_BAD_POINTER);
+        if (mats[m].residual != nullptr) return set_status(NVE_ERR_BAD_POINTER);  // no fused residual in the GEMM
+        if (mats[m].N < 1) return set_status(NVE_ERR_BAD_SHAPE);
+        if (!aligned(mats[m].nibbles, 16) || !aligned(mats[m].scales, 8)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+        g[m] = {mats[m].nibbles, mats[m].scales, mats[m].out, mats[m].N};
+        cols += mats[m].N;
+    }
+    if (cols > 0x7FFFFFF0ll) return set_status(NVE_ERR_BAD_SHAPE);
+    return run_gemm_multi(X, x_dtype, g, num_mats, y_dtype, M, K, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y, int y_dtype,

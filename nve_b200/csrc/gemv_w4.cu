@@ -374,7 +374,7 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.K = K;
     p.nb = K / kBlockK;
     p.S = (p.nb + kWarp - 1) / kWarp;
-    p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.awq = nullptr; p.idot = nullptr;
+    p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.xlo = nullptr; p.awq = nullptr; p.idot = nullptr;
     p.norm_w = nullptr; p.eps = 0.0f;
     p.tp.world = 0; p.tp.rank = 0; p.tp.rows_cap = 0; p.tp.err = nullptr;
     p.tp.counter = nullptr;
@@ -409,6 +409,23 @@ extern "C" int nve_b200_matvec_w4a16_multi(const void* x, int x_dtype, const flo
     if (x_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 0>(p, num_mats, out_dtype, cs);
     if (x_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 0>(p, num_mats, out_dtype, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+extern "C" int nve_b200_matvec_w4a16_planes_multi(const uint8_t* x_lo, const int8_t* x_hi, const float* x_scales,
+                                                  const nve_b200_w4_matrix* mats, int num_mats, int K, int out_dtype,
+                                                  nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mats, num_mats, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!x_lo || !x_hi || !x_scales) return set_status(NVE_ERR_BAD_POINTER);
+    if (!aligned(x_lo, 16) || !aligned(x_hi, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    for (int m = 0; m < num_mats; m++)
+        if (!aligned(mats[m].nibbles, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    p.xlo = x_lo;
+    p.xq = x_hi;
+    p.xs = x_scales;
+    p.x16 = x_lo;  // only its alignment is looked at
+    return dispatch_out<2, NVE_DT_F16, 0>(p, num_mats, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int32_t* I, int N, int K,

@@ -38,6 +38,7 @@ struct GemvParams {
     const int8_t* xq;   // W4A8 codes
     const float* xs;    // W4A8 scales
     const void* x16;    // W4A16 activations
+    const uint8_t* xlo; // W4A16 activations already in fixed point: low-byte plane (high bytes in xq, scales in xs)
     const float* awq;   // optional per-column multiplier (W4A16)
     const void* norm_w; // RMSNorm weight of the fused prologue (16-bit, same type as x16)
     float eps;
@@ -191,28 +192,9 @@ __device__ __forceinline__ void stage_chunk_q8(Smem<1>& sm, int c, const float (
 //   low plane = v & 0xFF (unsigned), high plane = v >> 8 (signed) ; bias = 8 * sum(v)
 // A non-finite amax makes the scale NaN so that the affected outputs are NaN, as an f32 path would give.
 __device__ __forceinline__ void stage_chunk_x16(Smem<2>& sm, int c, const float (&xe)[8], bool active) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(xe[e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    float scale = amax > 0.0f ? __fdiv_rn(amax, 32767.0f) : 1.0f;
-    if (!(amax <= 3.0e38f)) scale = __int_as_float(0x7FC00000);
-    const float inv = __fdiv_rn(1.0f, scale);
-    uint32_t l0 = 0, l1 = 0, h0 = 0, h1 = 0;
-    int sum = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        int q = __float2int_rn(__fmul_rn(xe[e], inv));
-        q = max(-32767, min(32767, q));
-        sum += q;
-        const uint32_t lo8 = static_cast<uint32_t>(q) & 0xFFu;
-        const uint32_t hi8 = static_cast<uint32_t>(q >> 8) & 0xFFu;
-        if (e < 4) { l0 |= lo8 << (8 * e); h0 |= hi8 << (8 * e); }
-        else { l1 |= lo8 << (8 * (e - 4)); h1 |= hi8 << (8 * (e - 4)); }
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    uint32_t l0, l1, h0, h1;
+    int sum;
+    const float scale = x16_quad_convert(xe, l0, l1, h0, h1, sum);
     if (active) {
         store_chunk_planes<2>(sm, c, 0, l0, l1);
         store_chunk_planes<2>(sm, c, 1, h0, h1);
@@ -220,6 +202,30 @@ __device__ __forceinline__ void stage_chunk_x16(Smem<2>& sm, int c, const float 
             sm.xs[c >> 2] = scale;
             sm.bias[c >> 2] = 8 * sum;
         }
+    }
+}
+
+// W4A16 activations that a producer kernel already converted to the two byte planes (nve_b200_silu_mul_x16):
+// a straight copy, plus the group's code sum for the bias term.
+__device__ __forceinline__ void stage_x16_planes(const GemvParams& p, Smem<2>& sm) {
+    for (int b = threadIdx.x; b < p.nb; b += kGemvThreads) {
+        const uint4* lo = reinterpret_cast<const uint4*>(p.xlo + static_cast<long long>(b) * 32);
+        const uint4* hi = reinterpret_cast<const uint4*>(p.xq + static_cast<long long>(b) * 32);
+        const uint4 l0 = lo[0], l1 = lo[1], h0 = hi[0], h1 = hi[1];
+        int ul = 0, sh = 0;
+        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            ul = dp4a_uu(lw[j], 0x01010101u, ul);
+            sh = __dp4a(static_cast<int>(hw[j]), 0x01010101, sh);
+        }
+        sm.plane[0 * sm.nbp + b] = l0;
+        sm.plane[1 * sm.nbp + b] = l1;
+        sm.plane[2 * sm.nbp + b] = h0;
+        sm.plane[3 * sm.nbp + b] = h1;
+        sm.xs[b] = p.xs[b];
+        sm.bias[b] = 8 * (sh * 256 + ul);
     }
 }
 
@@ -258,6 +264,12 @@ template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_ac
         stage_q8(p, sm);
         return;
     } else {
+        if constexpr (PLANES == 2 && PRO == 0) {
+            if (p.xlo != nullptr) {  // uniform over the grid
+                stage_x16_planes(p, sm);
+                return;
+            }
+        }
         const uint16_t* x = static_cast<const uint16_t*>(p.x16);
         const int chunks = p.K >> 3;
         float r = 1.0f;

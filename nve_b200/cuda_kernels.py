@@ -363,6 +363,25 @@ def silu_mul_quantize_q8(gate: Tensor, up: Tensor, want_mid: bool = False, xq: O
     return xq, scales, mid
 
 
+def silu_mul_x16(gate: Tensor, up: Tensor, awq: Optional[Tensor] = None, want_mid: bool = False,
+                 x_lo: Optional[Tensor] = None, x_hi: Optional[Tensor] = None, scales: Optional[Tensor] = None,
+                 mid: Optional[Tensor] = None):
+    """silu(gate)*up -> 16-bit round -> [* awq] -> 16-bit fixed-point byte planes for the W4A16 GEMV, one launch;
+    returns (x_lo uint8 [n], x_hi int8 [n], scales f32 [n/32], mid|None)."""
+    n = gate.numel()
+    dev = gate.device
+    x_lo = torch.empty(n, dtype=torch.uint8, device=dev) if x_lo is None else x_lo
+    x_hi = torch.empty(n, dtype=torch.int8, device=dev) if x_hi is None else x_hi
+    scales = torch.empty(n // 32, dtype=torch.float32, device=dev) if scales is None else scales
+    if mid is None and want_mid:
+        mid = torch.empty_like(gate)
+    _ffi.check("nve_b200_silu_mul_x16",
+               _lib().nve_b200_silu_mul_x16(_ptr(gate), _ptr(up, gate.dtype), _ptr(mid, gate.dtype), _ptr(x_lo, torch.uint8),
+                                            _ptr(x_hi, _Q8), _ptr(scales, torch.float32), _ptr(awq, torch.float32), n,
+                                            _dt(gate), stream()))
+    return x_lo, x_hi, scales, mid
+
+
 def silu_mul(gate: Tensor, up: Tensor) -> None:
     _ffi.check("nve_b200_silu_mul", _lib().nve_b200_silu_mul(_ptr(gate), _ptr(up, gate.dtype), gate.numel(), _dt(gate),
                                                              stream()))
@@ -405,6 +424,19 @@ def matvec_w4a16_multi(x: Tensor, awq: Optional[Tensor], weights: Sequence, k: i
                _lib().nve_b200_matvec_w4a16_multi(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
                                                   _ptr(awq, torch.float32), arr, len(weights), k, _TORCH_DT[out_dtype],
                                                   stream()))
+    return list(outs)
+
+
+def matvec_w4a16_planes_multi(x_lo: Tensor, x_hi: Tensor, x_scales: Tensor, weights: Sequence, k: int,
+                              out_dtype=torch.float16, outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """W4A16 GEMV over 1..3 matrices from activations already in fixed-point plane form (silu_mul_x16)."""
+    if outs is None:
+        outs = [torch.empty((1, n), dtype=out_dtype, device=x_lo.device) for (_, _, n) in weights]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_matvec_w4a16_planes_multi",
+               _lib().nve_b200_matvec_w4a16_planes_multi(_ptr(x_lo, torch.uint8), _ptr(x_hi, _Q8),
+                                                         _ptr(x_scales, torch.float32), arr, len(weights), k,
+                                                         _TORCH_DT[out_dtype], stream()))
     return list(outs)
 
 
@@ -496,6 +528,31 @@ def gemm_w4a16(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out_d
                                           _ptr(scales, torch.float32), _ptr(out, out_dtype, "out"), _TORCH_DT[out_dtype], m, n, k,
                                           _ptr(scratch), sb, stream()))
     return out
+
+
+def gemm_w4a16_multi_scratch_bytes(m: int, ns: Sequence[int], k: int) -> int:
+    import ctypes
+
+    arr = (ctypes.c_int * len(ns))(*[int(n) for n in ns])
+    return int(_lib().nve_b200_gemm_w4a16_multi_scratch_bytes(m, ctypes.cast(arr, ctypes.c_void_p), len(ns), k))
+
+
+def gemm_w4a16_multi(x: Tensor, weights: Sequence, k: int, out_dtype=None, outs: Optional[Sequence[Tensor]] = None,
+                     scratch: Optional[Tensor] = None):
+    """The batched W4A16 GEMM over 1..3 matrices sharing x [M, K] (q/k/v or gate/up) in one launch.
+    weights: [(nibbles, scales, n), ...] -> [M, n] each."""
+    m = x.shape[0]
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    if outs is None:
+        outs = [torch.empty((m, n), dtype=out_dtype, device=x.device) for (_, _, n) in weights]
+    if scratch is None and x.dtype == torch.bfloat16:
+        scratch = torch.empty(((m * k * 2 + 255) // 256) * 256, dtype=torch.uint8, device=x.device)
+    sb = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    arr = _mats(weights, outs, None, out_dtype)
+    _ffi.check("nve_b200_gemm_w4a16_multi",
+               _lib().nve_b200_gemm_w4a16_multi(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x), arr, len(weights),
+                                                _TORCH_DT[out_dtype], m, k, _ptr(scratch), sb, stream()))
+    return list(outs)
 
 
 def gemm_w4a16_noalloc(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out: Tensor) -> Tensor:

@@ -38,6 +38,7 @@ class _LayerScratch:
     xs_a: Tensor
     xq_f: Tensor
     xs_f: Tensor
+    xlo_f: Tensor
 
 
 class StaticDecodeGraph:
@@ -70,6 +71,7 @@ class StaticDecodeGraph:
             xs_a=torch.zeros(nh * hd // 32, dtype=torch.float32, device=dev),
             xq_f=torch.zeros(ffn_size, dtype=torch.int8, device=dev),
             xs_f=torch.zeros(ffn_size // 32, dtype=torch.float32, device=dev),
+            xlo_f=torch.zeros(ffn_size, dtype=torch.uint8, device=dev),
         )
         self.s = s
         self.routes: List[bool] = [state.routing.use_w4a8(x) for x in self.importance]

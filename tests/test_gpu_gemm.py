@@ -64,6 +64,34 @@ def test_gemm_matches_gemv_rows(cuda, orc):
         assert rel_rms_err(Y[m], y) < 3e-3
 
 
+@pytest.mark.parametrize("M,Ns,K", [(16, (4096, 1024, 1024), 4096), (8, (256, 128), 512), (64, (1024, 1000, 40), 1024)])
+def test_gemm_multi_matrix_equals_single_calls(cuda, orc, M, Ns, K):
+    """q/k/v (or gate/up) in one launch: same numbers as one call per matrix without split-K, and within f32
+    reassociation of them with split-K over the combined tile count."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    X16 = orc.to_act16(orc.fill_normal(M * K, 950, 2)).reshape(M, K)
+    dx = dev(X16, torch.float16)
+    ws, singles = [], []
+    for i, N in enumerate(Ns):
+        nib, sc, _, _ = _case(orc, M, N, K, 960 + i, False)
+        dn, ds = dev(nib), dev(sc)
+        ws.append((dn, ds, N))
+        singles.append(ck.gemm_w4a16(dx, dn, ds, N, K, out_dtype=torch.float32))
+    outs = ck.gemm_w4a16_multi(dx, ws, K, out_dtype=torch.float32)
+    for y, want in zip(outs, singles):
+        assert torch.equal(y, want)
+    scratch = torch.empty(ck.gemm_w4a16_multi_scratch_bytes(M, Ns, K), dtype=torch.uint8, device="cuda")
+    outs = ck.gemm_w4a16_multi(dx, ws, K, out_dtype=torch.float32, scratch=scratch)
+    for y, want in zip(outs, singles):
+        assert rel_rms_err(y.cpu().numpy(), want.cpu().numpy()) < 1e-5
+    outs16 = ck.gemm_w4a16_multi(dx, ws, K, scratch=scratch)
+    for y16, y in zip(outs16, outs):
+        assert torch.equal(y16, y.to(torch.float16))
+    assert ck.gemm_error() == 0
+
+
 def test_gemm_rejects_bad_arguments(cuda):
     from nve_b200 import _ffi
     from nve_b200 import cuda_kernels as ck

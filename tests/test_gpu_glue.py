@@ -67,6 +67,39 @@ def test_silu_mul_and_fused_quantize(cuda, orc, n):
     assert np.array_equal(xq.cpu().numpy(), eq) and np.array_equal(xs.cpu().numpy().view(np.uint32), es.view(np.uint32))
 
 
+@pytest.mark.parametrize("n,N,use_awq", [(64, 40, False), (8192, 256, True), (14336, 512, False)])
+def test_silu_mul_x16_planes_feed_the_w4a16_gemv(cuda, orc, n, N, use_awq):
+    """silu*up -> fixed-point planes in one launch: the planes equal the oracle's fixed-point codes of the device's
+    own silu*up values, and the GEMV fed with them is bit-identical to the GEMV fed with the 16-bit values."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    g16 = orc.to_act16(orc.fill_normal(n, 41, 1) * 2.0)
+    u16 = orc.to_act16(orc.fill_normal(n, 41, 2))
+    gate, up = dev(g16, torch.float16), dev(u16, torch.float16)
+    awq_np = (0.5 + np.abs(orc.fill_normal(n, 41, 3))).astype(np.float32) if use_awq else None
+    awq = dev(awq_np) if use_awq else None
+    mid_ref = gate.clone()
+    ck.silu_mul_inplace(mid_ref, up)
+    x_lo, x_hi, xs, mid = ck.silu_mul_x16(gate, up, awq, want_mid=True)
+    assert torch.equal(mid, mid_ref)
+    codes, scales = orc.x16_fixedpoint(f16_bits(mid_ref), False, awq_np)
+    got = x_lo.cpu().numpy().astype(np.int32) + 256 * x_hi.cpu().numpy().astype(np.int32)
+    assert np.array_equal(got, codes)
+    assert np.array_equal(xs.cpu().numpy().view(np.uint32), scales.view(np.uint32))
+    # the GEMV from planes == the GEMV from the 16-bit vector (same kernel arithmetic after staging)
+    W = orc.fill_normal(N * n, 42, 1, scale=0.02).reshape(N, n)
+    nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+    dn, ds = dev(nib), dev(sc)
+    res = dev(orc.to_act16(orc.fill_normal(N, 42, 9)), torch.float16).view(1, N)
+    y_ref = ck.matvec_w4a16_multi(mid_ref.view(-1), awq, [(dn, ds, N)], n, out_dtype=torch.float32)[0]
+    y_pl = ck.matvec_w4a16_planes_multi(x_lo, x_hi, xs, [(dn, ds, N)], n, out_dtype=torch.float32)[0]
+    assert torch.equal(y_ref, y_pl)
+    o_ref = ck.matvec_w4a16_multi(mid_ref.view(-1), awq, [(dn, ds, N)], n, residuals=[res])[0]
+    o_pl = ck.matvec_w4a16_planes_multi(x_lo, x_hi, xs, [(dn, ds, N)], n, residuals=[res])[0]
+    assert torch.equal(o_ref, o_pl)
+
+
 def test_add_inplace_and_layer_norm(cuda, orc):
     from nve_b200 import cuda_kernels as ck
 
