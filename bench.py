@@ -262,7 +262,9 @@ def run_ours(args) -> None:
                 ck.rmsnorm_matvec_w4a16_multi(hbuf, w.input_norm, eps, None, qkv, w.q_proj.k, outs=[qv, kv_, vv])
                 ck.matvec_w4a16_multi(s.attn, None, [w.o_proj.triple()], w.o_proj.k, outs=[hbuf], residuals=[hbuf])
                 ck.rmsnorm_matvec_w4a16_multi(hbuf, w.post_attn_norm, eps, None, gu, w.gate_proj.k, outs=[s.gate, s.up])
-                ck.matvec_w4a16_multi(s.gate, None, [w.down_proj.triple()], w.down_proj.k, outs=[hbuf], residuals=[hbuf])
+                # as in the step: the SiLU kernel has left the fixed-point planes of its result in the scratch buffers
+                ck.matvec_w4a16_planes_multi(s.xlo_f, s.xq_f, s.xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[hbuf],
+                                             residuals=[hbuf])
 
     seq = CapturedSequence(record_gemvs)
     gemv_launches = seq.launches
