@@ -93,18 +93,23 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     // not the cache).  The scalars read here are only a guess used for addressing: they are read again after the
     // wait and the prefetched rows are dropped if anything differs.
     int pre_seq = -1, pre_pos = -2;
-    uint4 kpre[kAdUnroll], vpre[kAdUnroll];
+    constexpr int kPre = 2;  // batches of rows in flight before the wait (all of them up to context 1024)
+    uint4 kpre[kPre][kAdUnroll], vpre[kPre][kAdUnroll];
     if constexpr (FUSED) {
         pre_seq = max(0, min(*p.d_seq_len, p.kv_stride));
         pre_pos = *p.d_pos;
         const int pchunk = (pre_seq + kAdCluster - 1) / kAdCluster;
         const int pb = rank * pchunk, pe = min(pre_seq, pb + pchunk);
+        const int safe = pb < p.kv_stride ? pb : 0;
 #pragma unroll
-        for (int u = 0; u < kAdUnroll; u++) {
-            const int t = pb + u * PL + pl;
-            const int tc = t < pe ? t : (pb < p.kv_stride ? pb : 0);
-            kpre[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
-            vpre[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
+        for (int b = 0; b < kPre; b++) {
+#pragma unroll
+            for (int u = 0; u < kAdUnroll; u++) {
+                const int t = pb + b * (PL * kAdUnroll) + u * PL + pl;
+                const int tc = t < pe ? t : safe;
+                kpre[b][u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
+                vpre[b][u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
+            }
         }
     }
     pdl_wait();
@@ -174,7 +179,8 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
 
     const int span = PL * kAdUnroll;
     const int iters = (max(0, t_end - t_begin) + span - 1) / span;  // uniform over the CTA
-    for (int it = 0; it < iters; it++) {
+    // one batch of PL * kAdUnroll positions; `kp`/`vp` are rows fetched before the dependency wait (use_pre)
+    auto batch = [&](int it, bool use_pre, const uint4 (&kp)[kAdUnroll], const uint4 (&vp)[kAdUnroll]) {
         uint4 kraw[kAdUnroll], vraw[kAdUnroll];
         bool valid[kAdUnroll];
 #pragma unroll
@@ -185,9 +191,9 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
             if (FUSED && tc == pos) {
                 kraw[u] = reinterpret_cast<const uint4*>(knew_s)[dc];
                 vraw[u] = reinterpret_cast<const uint4*>(vnew_s)[dc];
-            } else if (FUSED && it == 0 && pre_ok) {
-                kraw[u] = kpre[u];  // same t_begin, same t: the address computed before the wait
-                vraw[u] = vpre[u];
+            } else if (FUSED && use_pre) {
+                kraw[u] = kp[u];  // same t_begin, same t: the address computed before the wait
+                vraw[u] = vp[u];
             } else {
                 kraw[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
                 vraw[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
@@ -233,7 +239,12 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
                 for (int i = 0; i < 8; i++) acc[h][i] = fmaf(pe[u], vf[i], acc[h][i]);
             }
         }
-    }
+    };
+
+    static_assert(kPre == 2, "the first two batches are peeled so that the prefetched rows stay in registers");
+    if (iters > 0) batch(0, pre_ok, kpre[0], vpre[0]);
+    if (iters > 1) batch(1, pre_ok, kpre[1], vpre[1]);
+    for (int it = kPre; it < iters; it++) batch(it, false, kpre[0], vpre[0]);
 
     // ---- merge the position lanes of this CTA
 #pragma unroll
