@@ -199,6 +199,10 @@ def run_ours(args) -> None:
     pdl = os.environ.get("NVE_B200_PDL", "1") != "0"
     ck.set_pdl(pdl)
     shape = SHAPES[MODEL]
+    if args.layers:  # profiling aid: a shorter stack of the same layers (not the headline workload)
+        import dataclasses
+
+        shape = dataclasses.replace(shape, num_layers=args.layers)
     t_build = time.perf_counter()
     state, importance = build_state(shape, SEED, CONTEXT, max_seq=CONTEXT)
     torch.cuda.synchronize()
@@ -316,7 +320,8 @@ def run_ours(args) -> None:
         "metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": workload_name(), "model_shape": MODEL, "context": CONTEXT, "batch": 1,
+        "config": {"workload": workload_name() + (f" -- TRUNCATED to {args.layers} layers" if args.layers else ""),
+                   "model_shape": MODEL, "context": CONTEXT, "batch": 1,
                    "activations": "f16 (the reference ABI's activation type)", "kv_cache": "f16",
                    "w4a8_layers": int(sum(routes)), "w4a16_layers": int(len(routes) - sum(routes)),
                    "parallelism": "tp1", "l2_policy": f"inputs larger than L2: {total_bytes / 1e9:.2f} GB streamed per step",
@@ -359,6 +364,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling aid: run only this many layers of the stack (default: all; changes the workload)")
     ap.add_argument("--model", default=MODEL, choices=["1b", "3b", "8b", "70b"],
                     help="shape of the synthetic stack; the default is the configuration the headline metric names")
     args = ap.parse_args()
