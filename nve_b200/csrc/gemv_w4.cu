@@ -89,8 +89,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     int q = warp;  // item index inside the chunk: tile q / CG, column group q % CG
     if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
 
+    NormRegs nr;
+    if constexpr (PRO == 1) load_norm_regs(p, nr);  // static data: fetched before the dependency wait
     pdl_wait();
-    stage_activations<PLANES, XDT, PRO>(p, sm);
+    stage_activations<PLANES, XDT, PRO>(p, sm, nr);
     // tensor parallel: this launch's epoch is this CTA's own launch counter + 1; slots of the parity it selects
     // are used (a peer can be at most one all-reduce ahead, so two parities never collide)
     __shared__ unsigned tp_epoch_s;

@@ -121,6 +121,7 @@ inline size_t gemv_smem_bytes(int planes, int S) {
 
 // Stage the caller's int8 codes (W4A8).
 __device__ __forceinline__ void stage_q8(const GemvParams& p, Smem<1>& sm) {
+#pragma unroll 2
     for (int b = threadIdx.x; b < sm.nbp; b += kGemvThreads) {
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
         float xs = 0.0f;
@@ -208,6 +209,7 @@ __device__ __forceinline__ void stage_chunk_x16(Smem<2>& sm, int c, const float 
 // W4A16 activations that a producer kernel already converted to the two byte planes (nve_b200_silu_mul_x16):
 // a straight copy, plus the group's code sum for the bias term.
 __device__ __forceinline__ void stage_x16_planes(const GemvParams& p, Smem<2>& sm) {
+#pragma unroll 2
     for (int b = threadIdx.x; b < p.nb; b += kGemvThreads) {
         const uint4* lo = reinterpret_cast<const uint4*>(p.xlo + static_cast<long long>(b) * 32);
         const uint4* hi = reinterpret_cast<const uint4*>(p.xq + static_cast<long long>(b) * 32);
@@ -253,12 +255,38 @@ template <int PLANES> __device__ __forceinline__ void zero_padding(const GemvPar
 // warp (the producer) that must not take part.
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
+// RMSNorm weights of the fused prologue held in registers: they are static, so the kernel fetches them before it
+// waits for its predecessor (they are cold in L2 by the time a layer comes round again: a DRAM round trip that
+// would otherwise sit on the critical path between the wait and the first dot product).  Covers K <= 8192.
+constexpr int kNormRegChunks = 4;  // 8-element chunks per thread
+struct NormRegs {
+    uint4 w[kNormRegChunks];
+};
+__device__ __forceinline__ void load_norm_regs(const GemvParams& p, NormRegs& nr) {
+    const int chunks = p.K >> 3;
+#pragma unroll
+    for (int j = 0; j < kNormRegChunks; j++) {
+        const int c = j * kGemvThreads + threadIdx.x;
+        nr.w[j] = make_uint4(0, 0, 0, 0);
+        if (c < chunks && chunks <= kNormRegChunks * kGemvThreads) nr.w[j] = reinterpret_cast<const uint4*>(p.norm_w)[c];
+    }
+}
+__device__ __forceinline__ void unpack8(const uint4& raw, uint16_t (&h)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        h[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
+        h[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
+    }
+}
+
 // Stage the activations.  PRO = 0: the caller's vector (int8 codes for W4A8, 16-bit values for W4A16).
 // PRO = 1: RMSNorm of the caller's 16-bit vector first, in the library's fixed order (256 threads; thread t
 // adds x^2 over the 8-element chunks t, t+256, ... ; xor butterfly per warp; warp sums added in ascending
 // order; r = 1/sqrt(sum/n + eps); o = round16((x*r)*w)), then quantised exactly as the separate kernels do.
 template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_activations(const GemvParams& p,
-                                                                                           Smem<PLANES>& sm) {
+                                                                                           Smem<PLANES>& sm,
+                                                                                           const NormRegs& nr) {
     zero_padding<PLANES>(p, sm);
     if constexpr (PLANES == 1 && PRO == 0) {
         stage_q8(p, sm);
@@ -273,6 +301,68 @@ template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_ac
         const uint16_t* x = static_cast<const uint16_t*>(p.x16);
         const int chunks = p.K >> 3;
         float r = 1.0f;
+        if constexpr (PRO == 1) {
+            if (chunks <= kNormRegChunks * kGemvThreads) {
+                // Register-resident form: the vector is read once (all loads in flight together), the norm weights
+                // came in before the dependency wait.  Same arithmetic and the same summation order as below.
+                __shared__ float warp_part_r[kGemvThreads / 32];
+                uint4 xr[kNormRegChunks];
+#pragma unroll
+                for (int j = 0; j < kNormRegChunks; j++) {
+                    const int c = j * kGemvThreads + threadIdx.x;
+                    xr[j] = make_uint4(0, 0, 0, 0);
+                    if (c < chunks) xr[j] = reinterpret_cast<const uint4*>(x)[c];
+                }
+                float acc = 0.0f;
+#pragma unroll
+                for (int j = 0; j < kNormRegChunks; j++) {
+                    if (j * kGemvThreads + static_cast<int>(threadIdx.x) < chunks) {
+                        uint16_t h[8];
+                        unpack8(xr[j], h);
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            const float v = Act16<XDT>::to_f32(h[e]);
+                            acc = __fmaf_rn(v, v, acc);
+                        }
+                    }
+                }
+                acc = warp_sum(acc);
+                if ((threadIdx.x & 31) == 0) warp_part_r[threadIdx.x >> 5] = acc;
+                consumer_barrier();
+                float total = warp_part_r[0];
+#pragma unroll
+                for (int w = 1; w < kGemvThreads / 32; w++) total = __fadd_rn(total, warp_part_r[w]);
+                r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.K)), p.eps)));
+                const int iters_r = (chunks + kGemvThreads - 1) / kGemvThreads;
+#pragma unroll
+                for (int j = 0; j < kNormRegChunks; j++) {
+                    if (j < iters_r) {  // uniform over the CTA: the quad shuffles inside stage_chunk_* need whole warps
+                        const int c = j * kGemvThreads + threadIdx.x;
+                        const bool active = c < chunks;
+                        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        if (active) {
+                            uint16_t h[8], hw[8];
+                            unpack8(xr[j], h);
+                            unpack8(nr.w[j], hw);
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const float o = __fmul_rn(__fmul_rn(Act16<XDT>::to_f32(h[e]), r), Act16<XDT>::to_f32(hw[e]));
+                                v[e] = Act16<XDT>::to_f32(Act16<XDT>::from_f32(o));
+                            }
+                            if constexpr (PLANES == 2) {
+                                if (p.awq != nullptr) {
+#pragma unroll
+                                    for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
+                                }
+                            }
+                        }
+                        if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);
+                        else stage_chunk_x16(sm, c, v, active);
+                    }
+                }
+                return;
+            }
+        }
         if constexpr (PRO == 1) {
             __shared__ float warp_part[kGemvThreads / 32];
             float acc = 0.0f;
