@@ -330,6 +330,10 @@ NVE_API int nve_b200_matvec_w4a8_allreduce(const int8_t* xq, const float* xq_sca
                                            int K, int out_dtype, nve_stream_t stream);
 NVE_API int nve_b200_matvec_w4a16_allreduce(const void* x, int x_dtype, const float* awq,
                                             const nve_b200_w4_matrix* mat, int K, int out_dtype, nve_stream_t stream);
+/* The W4A16 form fed with the fixed-point planes of nve_b200_silu_mul_x16 (this rank's K shard of them). */
+NVE_API int nve_b200_matvec_w4a16_planes_allreduce(const uint8_t* x_lo, const int8_t* x_hi, const float* x_scales,
+                                                   const nve_b200_w4_matrix* mat, int K, int out_dtype,
+                                                   nve_stream_t stream);
 
 #ifdef __cplusplus
 }

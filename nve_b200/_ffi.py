@@ -118,6 +118,7 @@ SIGNATURES = {
     "nve_b200_tp_destroy": (_I, []),
     "nve_b200_matvec_w4a8_allreduce": (_I, [_P, _P, C.POINTER(W4Matrix), _I, _I, _P]),
     "nve_b200_matvec_w4a16_allreduce": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _P]),
+    "nve_b200_matvec_w4a16_planes_allreduce": (_I, [_P, _P, _P, C.POINTER(W4Matrix), _I, _I, _P]),
     "nve_b200_fill_normal": (_I, [_P, _LL, _ULL, _ULL, _ULL, _F, _P]),
     "nve_b200_fill_normal_16": (_I, [_P, _LL, _ULL, _ULL, _ULL, _F, _I, _P]),
 }

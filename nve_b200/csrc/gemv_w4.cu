@@ -501,6 +501,23 @@ extern "C" int nve_b200_matvec_w4a8_allreduce(const int8_t* xq, const float* xq_
     return dispatch_out<1, NVE_DT_F16, 0>(p, 1, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int nve_b200_matvec_w4a16_planes_allreduce(const uint8_t* x_lo, const int8_t* x_hi, const float* x_scales,
+                                                      const nve_b200_w4_matrix* mat, int K, int out_dtype,
+                                                      nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mat, 1, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!x_lo || !x_hi || !x_scales) return set_status(NVE_ERR_BAD_POINTER);
+    p.xlo = x_lo;
+    p.xq = x_hi;
+    p.xs = x_scales;
+    p.x16 = x_lo;  // only its alignment is looked at
+    if (!aligned(x_hi, 16) || !all_aligned(p, 1, 2, 0)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    st = attach_tp(p);
+    if (st != NVE_OK) return set_status(st);
+    return dispatch_out<2, NVE_DT_F16, 0>(p, 1, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int nve_b200_matvec_w4a16_allreduce(const void* x, int x_dtype, const float* awq, const nve_b200_w4_matrix* mat,
                                                int K, int out_dtype, nve_stream_t stream) {
     GemvParams p;

@@ -508,6 +508,21 @@ def matvec_w4a16_allreduce(x: Tensor, awq: Optional[Tensor], weights: Sequence, 
     return list(outs)
 
 
+def matvec_w4a16_planes_allreduce(x_lo: Tensor, x_hi: Tensor, x_scales: Tensor, weights: Sequence, k: int,
+                                  out_dtype=torch.float16, outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """matvec_w4a16_allreduce fed with the fixed-point planes written by silu_mul_x16."""
+    if len(weights) != 1:
+        raise ValueError("the fused all-reduce takes one matrix")
+    if outs is None:
+        outs = [torch.empty((1, weights[0][2]), dtype=out_dtype, device=x_lo.device)]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_matvec_w4a16_planes_allreduce",
+               _lib().nve_b200_matvec_w4a16_planes_allreduce(_ptr(x_lo, torch.uint8), _ptr(x_hi, _Q8),
+                                                             _ptr(x_scales, torch.float32), arr, k, _TORCH_DT[out_dtype],
+                                                             stream()))
+    return list(outs)
+
+
 def gemm_w4a16_scratch_bytes(m: int, n: int, k: int) -> int:
     return int(_lib().nve_b200_gemm_w4a16_scratch_bytes(m, n, k))
 

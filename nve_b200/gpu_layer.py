@@ -269,16 +269,12 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
         gemv16(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
         ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
                                       [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
-        if allreduce:
-            ck.silu_mul_inplace(gate, up)
-            gemv16(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
-        else:
-            # the fixed-point form of silu(gate)*up is produced once here instead of by every CTA of the GEMV
-            xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
-            xlo_f = buf("xlo_f", (ffn,), torch.uint8)
-            ck.silu_mul_x16(gate, up, w.down_proj.awq_scales, x_lo=xlo_f, x_hi=xq_f, scales=xs_f)
-            ck.matvec_w4a16_planes_multi(xlo_f, xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1],
-                                         residuals=[h1])
+        # the fixed-point form of silu(gate)*up is produced once here instead of by every CTA of the GEMV
+        xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
+        xlo_f = buf("xlo_f", (ffn,), torch.uint8)
+        ck.silu_mul_x16(gate, up, w.down_proj.awq_scales, x_lo=xlo_f, x_hi=xq_f, scales=xs_f)
+        down16 = ck.matvec_w4a16_planes_allreduce if allreduce else ck.matvec_w4a16_planes_multi
+        down16(xlo_f, xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
     return h1
 
 
