@@ -312,6 +312,74 @@ NVE_API int nve_b200_gemm_error(int reset);
 NVE_API int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
                                         int y_dtype, int M, int N, int K, nve_stream_t stream);
 
+/* ---- whole decode step in one persistent kernel ------------------------------------------------------------
+ * nve_b200_decode_step runs one token through every layer of a Llama-style W4 stack in ONE cooperative launch:
+ * per layer RMSNorm -> q/k/v GEMV -> RoPE + KV write + attention -> o_proj + residual -> RMSNorm -> gate/up GEMV ->
+ * SiLU*up -> down GEMV + residual, i.e. the kernel sequence of src/decode_graph.rs:206-343 (and of
+ * src/gpu_layer.rs:633-997 with the W4A8 route of :1017-1025 chosen per layer by use_w4a8), optionally followed
+ * by the final RMSNorm and the lm_head GEMV that the reference computes on the host (src/paged_model.rs:1424-1433).
+ * The hidden state it leaves is bit-identical to the fused six-launch-per-layer sequence of this library.
+ *
+ *   - `layers_dev` is a DEVICE array of model->num_layers descriptors (the caller copies it there once); all
+ *     pointers inside are device addresses.  Weights in the library's W4 format; norm weights f16 [hidden];
+ *     caches f16 [num_kv_heads, max_seq, head_dim]; rope tables f16 [max_seq, head_dim/2].
+ *   - awq[i] (may be NULL) multiplies the activations of the W4A16 route in front of q/k/v (0), o_proj (1),
+ *     gate/up (2) and down_proj (3), as nve_matvec_w4a16's awq argument does.
+ *   - `hidden` [hidden] f16 is updated in place; *d_pos / *d_seq_len as for nve_b200_attn_decode_fused.
+ *   - `workspace`: nve_b200_decode_step_workspace_bytes(model) bytes, 256-byte aligned, zeroed once with
+ *     nve_b200_decode_step_init; one workspace serves one stream of steps (steps sharing it must not overlap).
+ *   - head_dim 64 or 128, an even number of query heads per KV head, hidden / ffn multiples of 32, every
+ *     projection's row count a multiple of 8, hidden and num_heads*head_dim <= 8192.
+ *   - The launch is cooperative (one 512-thread CTA per SM must be co-resident; otherwise NVE_ERR_CUDA and nothing
+ *     runs).  Every device-wide wait inside is bounded (100 ms): if one expires the kernel finishes with an
+ *     undefined hidden state and nve_b200_decode_step_error returns NVE_ERR_TIMEOUT until reset.
+ *   - With lm_nibbles != NULL the kernel ends with logits[vocab] (f32) = lm_head . RMSNorm(hidden, final_norm).
+ */
+typedef struct {
+    const uint8_t* nibbles[7]; /* q, k, v, o, gate, up, down */
+    const float* scales[7];
+    const float* awq[4];
+    const uint16_t* input_norm;
+    const uint16_t* post_attn_norm;
+    uint16_t* k_cache;
+    uint16_t* v_cache;
+    int use_w4a8; /* 1: int8 activations (W4A8), 0: 16-bit activations (W4A16) */
+    int reserved;
+} nve_b200_decode_layer;
+
+typedef struct {
+    int hidden, ffn, num_heads, num_kv_heads, head_dim, max_seq, num_layers;
+    float norm_eps, attn_scale;
+    const uint16_t* rope_cos;
+    const uint16_t* rope_sin;
+    /* optional head (all NULL / 0 when unused) */
+    const uint16_t* final_norm;
+    const uint8_t* lm_nibbles; /* [vocab, hidden/2] */
+    const float* lm_scales;    /* [vocab, hidden/32] */
+    float* logits;             /* [vocab] f32 */
+    int vocab;
+    int lm_use_w4a8;
+} nve_b200_decode_model;
+
+NVE_API size_t nve_b200_decode_step_workspace_bytes(const nve_b200_decode_model* model);
+NVE_API int nve_b200_decode_step_init(void* workspace, size_t workspace_bytes, nve_stream_t stream);
+NVE_API int nve_b200_decode_step(const nve_b200_decode_model* model, const nve_b200_decode_layer* layers_dev, void* hidden,
+                                 const int* d_pos, const int* d_seq_len, void* workspace, size_t workspace_bytes,
+                                 nve_stream_t stream);
+/* Synchronous: the latched error word of the workspace (0 = none); reset != 0 clears it and the barrier state. */
+NVE_API int nve_b200_decode_step_error(void* workspace, int reset);
+/* Run-ahead distance in bytes of the kernel's L2 prefetch stream (0 disables it); returns the previous value;
+ * a negative argument only queries. */
+NVE_API long long nve_b200_decode_step_set_prefetch(long long bytes);
+/* Debugging aid: when `buf` (device memory, 2 * phases * 4 u64; phases = 7 per layer + 1 with an lm_head) is set,
+ * CTA 0 and the last CTA record nanosecond timestamps per phase: phase entry, barrier passed, activations staged,
+ * phase done.  NULL (the default) switches it off. */
+NVE_API void nve_b200_decode_step_set_trace(unsigned long long* buf);
+/* Test hook for the bounded wait: a one-CTA kernel waits (at most wait_ns <= 100 ms) at the workspace's barrier
+ * for an arrival that never comes; afterwards nve_b200_decode_step_error reports NVE_ERR_TIMEOUT.  Reset the
+ * workspace (nve_b200_decode_step_error(ws, 1)) before using it for a step again. */
+NVE_API int nve_b200_decode_step_wait_probe(void* workspace, unsigned long long wait_ns, nve_stream_t stream);
+
 /* ---- tensor parallel (no counterpart in the reference, which is single-GPU) -------------------------------
  * One process per GPU.  nve_b200_tp_create allocates this rank's symmetric buffer (partial sums for up to
  * max_rows output rows, per-CTA launch counters) and returns its 64-byte CUDA IPC handle; after the handles of

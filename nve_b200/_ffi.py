@@ -49,6 +49,35 @@ class W4Matrix(C.Structure):
     ]
 
 
+class DecodeLayer(C.Structure):
+    """nve_b200_decode_layer."""
+
+    _fields_ = [
+        ("nibbles", C.c_void_p * 7),
+        ("scales", C.c_void_p * 7),
+        ("awq", C.c_void_p * 4),
+        ("input_norm", C.c_void_p),
+        ("post_attn_norm", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("use_w4a8", C.c_int),
+        ("reserved", C.c_int),
+    ]
+
+
+class DecodeModel(C.Structure):
+    """nve_b200_decode_model."""
+
+    _fields_ = [
+        ("hidden", C.c_int), ("ffn", C.c_int), ("num_heads", C.c_int), ("num_kv_heads", C.c_int),
+        ("head_dim", C.c_int), ("max_seq", C.c_int), ("num_layers", C.c_int),
+        ("norm_eps", C.c_float), ("attn_scale", C.c_float),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("final_norm", C.c_void_p), ("lm_nibbles", C.c_void_p), ("lm_scales", C.c_void_p), ("logits", C.c_void_p),
+        ("vocab", C.c_int), ("lm_use_w4a8", C.c_int),
+    ]
+
+
 _P, _I, _F, _S = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 _LL, _ULL = C.c_longlong, C.c_ulonglong
 
@@ -111,6 +140,13 @@ SIGNATURES = {
     "nve_b200_gemm_w4a16_multi": (_I, [_P, _I, C.POINTER(W4Matrix), _I, _I, _I, _I, _P, _S, _P]),
     "nve_b200_gemm_error": (_I, [_I]),
     "nve_b200_gemm_w4a16_noalloc": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "nve_b200_decode_step_workspace_bytes": (_S, [C.POINTER(DecodeModel)]),
+    "nve_b200_decode_step_init": (_I, [_P, _S, _P]),
+    "nve_b200_decode_step": (_I, [C.POINTER(DecodeModel), _P, _P, _P, _P, _P, _S, _P]),
+    "nve_b200_decode_step_error": (_I, [_P, _I]),
+    "nve_b200_decode_step_set_prefetch": (_LL, [_LL]),
+    "nve_b200_decode_step_wait_probe": (_I, [_P, _ULL, _P]),
+    "nve_b200_decode_step_set_trace": (None, [_P]),
     "nve_b200_tp_create": (_I, [_I, _I, _I, _P]),
     "nve_b200_tp_connect": (_I, [_P]),
     "nve_b200_tp_world": (_I, []),

@@ -11,28 +11,11 @@
 //   RMSNorm  : 256 threads; thread t adds x^2 (fma chain) over the 8-element chunks t, t+256, ... in
 //              ascending element order; xor-butterfly per warp; the 8 warp sums added in ascending order;
 //              r = 1/sqrt(sum/n + eps); out = round16((x*r)*w)
-#include "common.cuh"
+#include "act_ops.cuh"
 
 namespace nve {
 
 constexpr int kActThreads = 256;
-
-__device__ __forceinline__ void unpack8(const uint4& raw, uint16_t (&h)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        h[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
-        h[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
-    }
-}
-__device__ __forceinline__ uint4 pack8(const uint16_t (&h)[8]) {
-    uint4 r;
-    r.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
-    r.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
-    r.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
-    r.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
-    return r;
-}
 
 // Load / store one 8-element chunk; the scalar path also handles a ragged tail (elements >= n read as 0).
 template <bool VEC> __device__ __forceinline__ void load_chunk(const uint16_t* p, long long c, int n, uint16_t (&h)[8]) {
@@ -50,31 +33,6 @@ template <bool VEC> __device__ __forceinline__ void store_chunk(uint16_t* p, lon
 #pragma unroll
         for (int e = 0; e < 8; e++)
             if (c * 8 + e < n) p[c * 8 + e] = h[e];
-    }
-}
-
-// Quantise the 8 values of this thread; the 4 threads of a quad hold one 32-wide group.
-__device__ __forceinline__ void quantize_quad(const float (&v)[8], int8_t* xq, float* scales, long long chunk,
-                                              bool active) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-    const float inv = __fdiv_rn(1.0f, scale);
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        int q = __float2int_rn(__fmul_rn(v[e], inv));
-        q = max(-127, min(127, q));
-        const uint32_t byte = static_cast<uint32_t>(q) & 0xFFu;
-        if (e < 4) lo |= byte << (8 * e);
-        else hi |= byte << (8 * (e - 4));
-    }
-    if (active) {
-        reinterpret_cast<uint2*>(xq)[chunk] = make_uint2(lo, hi);
-        if ((chunk & 3) == 0) scales[chunk >> 2] = scale;
     }
 }
 
@@ -160,23 +118,6 @@ __global__ void __launch_bounds__(kActThreads) rmsnorm_kernel(const uint16_t* x,
             if (out != nullptr) store_chunk<VEC>(out, c, n, ho);
         }
         if constexpr (QUANT) quantize_quad(v, xq, scales, c, active);
-    }
-}
-
-__device__ __forceinline__ float silu_mul_f32(float g, float u) {
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
-}
-
-// Write the 16-bit fixed-point planes of the 8 values of this thread (the 4 threads of a quad hold one group).
-__device__ __forceinline__ void x16_quad(const float (&v)[8], uint8_t* xlo, int8_t* xhi, float* scales, long long chunk,
-                                         bool active) {
-    uint32_t l0, l1, h0, h1;
-    int sum;
-    const float scale = x16_quad_convert(v, l0, l1, h0, h1, sum);
-    if (active) {
-        reinterpret_cast<uint2*>(xlo)[chunk] = make_uint2(l0, l1);
-        reinterpret_cast<uint2*>(xhi)[chunk] = make_uint2(h0, h1);
-        if ((chunk & 3) == 0) scales[chunk >> 2] = scale;
     }
 }
 

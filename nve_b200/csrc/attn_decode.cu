@@ -19,15 +19,13 @@
 //     instead of the cache, and one CTA per KV head writes them to the cache.
 #include <cooperative_groups.h>
 
-#include "common.cuh"
+#include "attn_core.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace nve {
 
-constexpr int kAdCluster = 8;
-constexpr int kAdThreads = 256;
-constexpr int kAdUnroll = 4;
+constexpr int kAdCluster = kAdRanks;
 
 struct AttnParams {
     const uint16_t* q;        // [nh, hd]
@@ -47,33 +45,16 @@ struct AttnParams {
     float scale;
 };
 
-__device__ __forceinline__ void unpack8_f32(const uint4& raw, float (&o)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        o[2 * j] = Act16<NVE_DT_F16>::to_f32(static_cast<uint16_t>(w[j] & 0xFFFFu));
-        o[2 * j + 1] = Act16<NVE_DT_F16>::to_f32(static_cast<uint16_t>(w[j] >> 16));
-    }
-}
-
-template <int HD, int QH> struct AdCtaPartial {
-    float m[QH];
-    float s[QH];
-    float acc[QH][HD];
-};
-
 template <int HD, int QH, bool FUSED>
 __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParams p) {
     constexpr int DC = HD / 8;            // lanes per row
     constexpr int PL = kAdThreads / DC;   // position lanes
-    constexpr int HALF = HD / 2;
     cg::cluster_group cluster = cg::this_cluster();
+    // Phase 1 of the cluster barrier: every CTA announces that it runs, so that the pushes into rank 0's shared
+    // memory below never touch a CTA that has not started (matched by the wait in front of the push).
+    cluster.barrier_arrive();
 
-    __shared__ float q_s[QH][HD];
-    __shared__ __align__(16) uint16_t knew_s[HD];
-    __shared__ __align__(16) uint16_t vnew_s[HD];
-    __shared__ float pm[PL][QH], ps[PL][QH];
-    __shared__ float pacc[PL][QH][HD];
+    __shared__ AdShared<HD, QH> sh;
     __shared__ AdCtaPartial<HD, QH> parts[kAdCluster];  // only rank 0's copy is used: every CTA pushes its partial there
 
     const int tid = threadIdx.x;
@@ -88,13 +69,12 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
     const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
 
-    // Fused form: the cache rows of earlier positions were written by earlier steps, so the first batch of K/V
+    // Fused form: the cache rows of earlier positions were written by earlier steps, so the first batches of K/V
     // loads can be in flight while the kernel still waits for its predecessor (which produces q and the new k/v,
     // not the cache).  The scalars read here are only a guess used for addressing: they are read again after the
     // wait and the prefetched rows are dropped if anything differs.
     int pre_seq = -1, pre_pos = -2;
-    constexpr int kPre = 2;  // batches of rows in flight before the wait (all of them up to context 1024)
-    uint4 kpre[kPre][kAdUnroll], vpre[kPre][kAdUnroll];
+    AdPrefetch pre;
     if constexpr (FUSED) {
         pre_seq = max(0, min(*p.d_seq_len, p.kv_stride));
         pre_pos = *p.d_pos;
@@ -102,13 +82,13 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
         const int pb = rank * pchunk, pe = min(pre_seq, pb + pchunk);
         const int safe = pb < p.kv_stride ? pb : 0;
 #pragma unroll
-        for (int b = 0; b < kPre; b++) {
+        for (int b = 0; b < kAdPre; b++) {
 #pragma unroll
             for (int u = 0; u < kAdUnroll; u++) {
                 const int t = pb + b * (PL * kAdUnroll) + u * PL + pl;
                 const int tc = t < pe ? t : safe;
-                kpre[b][u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
-                vpre[b][u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
+                pre.k[b][u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
+                pre.v[b][u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
             }
         }
     }
@@ -121,40 +101,9 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const bool pos_ok = FUSED && pos >= 0 && pos < p.kv_stride;
     const bool pre_ok = FUSED && pre_seq == seq_len && pre_pos == pos;
 
-    // ---- stage q (rotated in the fused form) and the new k / v row
-    if constexpr (FUSED) {
-        const uint16_t* cr = p.cos_tab + static_cast<long long>(pos_ok ? pos : 0) * HALF;
-        const uint16_t* sr = p.sin_tab + static_cast<long long>(pos_ok ? pos : 0) * HALF;
-        for (int i = tid; i < QH * HALF; i += kAdThreads) {
-            const int h = i / HALF, e = i % HALF;
-            const uint16_t* qp = p.q + static_cast<long long>(h0 + h) * HD;
-            const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
-            const float x0 = Act16<NVE_DT_F16>::to_f32(qp[e]), x1 = Act16<NVE_DT_F16>::to_f32(qp[e + HALF]);
-            const uint16_t r0 = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
-            const uint16_t r1 = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
-            q_s[h][e] = Act16<NVE_DT_F16>::to_f32(r0);
-            q_s[h][e + HALF] = Act16<NVE_DT_F16>::to_f32(r1);
-        }
-        for (int e = tid; e < HALF; e += kAdThreads) {
-            const uint16_t* kp = p.k_new + static_cast<long long>(kvh) * HD;
-            const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
-            const float x0 = Act16<NVE_DT_F16>::to_f32(kp[e]), x1 = Act16<NVE_DT_F16>::to_f32(kp[e + HALF]);
-            knew_s[e] = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
-            knew_s[e + HALF] = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
-        }
-        for (int e = tid; e < HD; e += kAdThreads) vnew_s[e] = p.v_new[static_cast<long long>(kvh) * HD + e];
-    } else {
-        for (int i = tid; i < QH * HD; i += kAdThreads)
-            q_s[i / HD][i % HD] = Act16<NVE_DT_F16>::to_f32(p.q[static_cast<long long>(h0) * HD + i]);
-    }
+    attn_stage_q<HD, QH, FUSED>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
     __syncthreads();
     pdl_launch_dependents();
-
-    float qr[QH][8];
-#pragma unroll
-    for (int h = 0; h < QH; h++)
-#pragma unroll
-        for (int i = 0; i < 8; i++) qr[h][i] = q_s[h][dc * 8 + i];
 
     const int chunk = (seq_len + kAdCluster - 1) / kAdCluster;
     const int t_begin = rank * chunk;
@@ -164,112 +113,24 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
         if (pos_ok && rank == 0 && (cluster_id % clusters_per_kv) == 0 && tid < 2 * DC) {
             const int which = tid / DC, d = tid % DC;
             uint16_t* dst = (which == 0 ? p.k_cache : p.v_cache) + (static_cast<long long>(kvh) * p.kv_stride + pos) * HD;
-            reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? knew_s : vnew_s)[d];
+            reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
         }
     }
 
-    float m[QH], s[QH], acc[QH][8];
-#pragma unroll
-    for (int h = 0; h < QH; h++) {
-        m[h] = -1e30f;
-        s[h] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[h][i] = 0.0f;
-    }
-
-    const int span = PL * kAdUnroll;
-    const int iters = (max(0, t_end - t_begin) + span - 1) / span;  // uniform over the CTA
-    // one batch of PL * kAdUnroll positions; `kp`/`vp` are rows fetched before the dependency wait (use_pre)
-    auto batch = [&](int it, bool use_pre, const uint4 (&kp)[kAdUnroll], const uint4 (&vp)[kAdUnroll]) {
-        uint4 kraw[kAdUnroll], vraw[kAdUnroll];
-        bool valid[kAdUnroll];
-#pragma unroll
-        for (int u = 0; u < kAdUnroll; u++) {
-            const int t = t_begin + it * span + u * PL + pl;
-            valid[u] = t < t_end;
-            const int tc = valid[u] ? t : t_begin;
-            if (FUSED && tc == pos) {
-                kraw[u] = reinterpret_cast<const uint4*>(knew_s)[dc];
-                vraw[u] = reinterpret_cast<const uint4*>(vnew_s)[dc];
-            } else if (FUSED && use_pre) {
-                kraw[u] = kp[u];  // same t_begin, same t: the address computed before the wait
-                vraw[u] = vp[u];
-            } else {
-                kraw[u] = ld_stream_u4(kh + static_cast<long long>(tc) * HD + dc * 8);
-                vraw[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
-            }
-        }
-        float sc[kAdUnroll][QH];
-#pragma unroll
-        for (int u = 0; u < kAdUnroll; u++) {
-            float kf[8];
-            unpack8_f32(kraw[u], kf);
-#pragma unroll
-            for (int h = 0; h < QH; h++) {
-                float d = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) d = fmaf(qr[h][i], kf[i], d);
-#pragma unroll
-                for (int msk = DC / 2; msk > 0; msk >>= 1) d += __shfl_xor_sync(0xffffffffu, d, msk);
-                sc[u][h] = valid[u] ? d * p.scale : -1e30f;
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < QH; h++) {
-            float new_m = m[h];
-#pragma unroll
-            for (int u = 0; u < kAdUnroll; u++) new_m = fmaxf(new_m, sc[u][h]);
-            const float corr = expf(m[h] - new_m);
-            float pe[kAdUnroll];
-            float psum = 0.0f;
-#pragma unroll
-            for (int u = 0; u < kAdUnroll; u++) {
-                pe[u] = valid[u] ? expf(sc[u][h] - new_m) : 0.0f;
-                psum += pe[u];
-            }
-            s[h] = fmaf(s[h], corr, psum);
-            m[h] = new_m;
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc[h][i] *= corr;
-#pragma unroll
-            for (int u = 0; u < kAdUnroll; u++) {
-                float vf[8];
-                unpack8_f32(vraw[u], vf);
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc[h][i] = fmaf(pe[u], vf[i], acc[h][i]);
-            }
-        }
-    };
-
-    static_assert(kPre == 2, "the first two batches are peeled so that the prefetched rows stay in registers");
-    if (iters > 0) batch(0, pre_ok, kpre[0], vpre[0]);
-    if (iters > 1) batch(1, pre_ok, kpre[1], vpre[1]);
-    for (int it = kPre; it < iters; it++) batch(it, false, kpre[0], vpre[0]);
-
-    // ---- merge the position lanes of this CTA
-#pragma unroll
-    for (int h = 0; h < QH; h++) {
-        if (dc == 0) { pm[pl][h] = m[h]; ps[pl][h] = s[h]; }
-#pragma unroll
-        for (int i = 0; i < 8; i++) pacc[pl][h][dc * 8 + i] = acc[h][i];
-    }
-    __syncthreads();
-    for (int i = tid; i < QH * HD; i += kAdThreads) {
-        const int h = i / HD, d = i % HD;
-        float mm = -1e30f;
-        for (int l = 0; l < PL; l++) mm = fmaxf(mm, pm[l][h]);
-        float ss = 0.0f, a = 0.0f;
-        for (int l = 0; l < PL; l++) {
-            const float c = expf(pm[l][h] - mm);
-            ss = fmaf(ps[l][h], c, ss);
-            a = fmaf(pacc[l][h][d], c, a);
-        }
-        // push this CTA's partial into rank 0's shared memory (posted remote stores, no round trip)
-        AdCtaPartial<HD, QH>* dst = cluster.map_shared_rank(&parts[rank], 0);
-        dst->acc[h][d] = a;
-        if (d == 0) { dst->m[h] = mm; dst->s[h] = ss; }
-    }
-    // release the stores / acquire everybody's; only rank 0 has anything left to do, the others arrive and leave
+    // push this CTA's partial into rank 0's shared memory (posted remote stores, no round trip)
+    AdCtaPartial<HD, QH>* dst = cluster.map_shared_rank(&parts[rank], 0);
+    // the level-1 merge starts with a CTA barrier; the matching cluster wait rides on it (all CTAs run by then)
+    attn_partial<HD, QH, FUSED, FUSED>(
+        sh, tid, kh, vh, t_begin, t_end, pos, p.scale, pre_ok, &pre,
+        [&] {
+            __syncthreads();
+            cluster.barrier_wait();
+        },
+        [&](int h, int d, float mm, float ss, float a) {
+            dst->acc[h][d] = a;
+            if (d == 0) { dst->m[h] = mm; dst->s[h] = ss; }
+        });
+    // phase 2: release the stores / acquire everybody's; only rank 0 has anything left to do
     cluster.barrier_arrive();
     if (rank != 0) return;
     cluster.barrier_wait();
@@ -277,27 +138,13 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     // ---- rank 0 merges the CTA partials from its own shared memory, normalises and stores
     for (int i = tid; i < QH * HD; i += kAdThreads) {
         const int h = i / HD, d = i % HD;
-        float mm = -1e30f;
-#pragma unroll
-        for (int r = 0; r < kAdCluster; r++) mm = fmaxf(mm, parts[r].m[h]);
-        float ss = 0.0f, a = 0.0f;
-#pragma unroll
-        for (int r = 0; r < kAdCluster; r++) {
-            const float c = expf(parts[r].m[h] - mm);
-            ss = fmaf(parts[r].s[h], c, ss);
-            a = fmaf(parts[r].acc[h][d], c, a);
-        }
-        const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
-        const uint16_t o16 = Act16<NVE_DT_F16>::from_f32(a * inv);
+        const uint16_t o16 = attn_merge_ranks<HD, QH>(parts, h, d);
         const long long oi = static_cast<long long>(h0 + h) * HD + d;
         p.out[oi] = o16;
         if (p.out_q != nullptr) {
             // i advances by whole warps and HD is a multiple of 32: the 32 lanes of a warp hold one group
-            const float v = Act16<NVE_DT_F16>::to_f32(o16);
-            const float amax = warp_max(fabsf(v));
-            const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-            int qv = __float2int_rn(__fmul_rn(v, __fdiv_rn(1.0f, scale)));
-            qv = max(-127, min(127, qv));
+            float scale;
+            const int qv = attn_quantize_lane(o16, scale);
             p.out_q[oi] = static_cast<int8_t>(qv);
             if ((tid & 31) == 0) p.out_scales[oi >> 5] = scale;
         }

@@ -1,7 +1,7 @@
 // Device code shared by the W4 GEMV kernels: parameters, shared-memory layout, activation staging and the
 // per-block integer dot product.  See gemv_w4.cu for the description of the algorithm.
 #pragma once
-#include "common.cuh"
+#include "act_ops.cuh"
 
 namespace nve {
 
@@ -271,15 +271,6 @@ __device__ __forceinline__ void load_norm_regs(const GemvParams& p, NormRegs& nr
         if (c < chunks && chunks <= kNormRegChunks * kGemvThreads) nr.w[j] = reinterpret_cast<const uint4*>(p.norm_w)[c];
     }
 }
-__device__ __forceinline__ void unpack8(const uint4& raw, uint16_t (&h)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        h[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
-        h[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
-    }
-}
-
 // Stage the activations.  PRO = 0: the caller's vector (int8 codes for W4A8, 16-bit values for W4A16).
 // PRO = 1: RMSNorm of the caller's 16-bit vector first, in the library's fixed order (256 threads; thread t
 // adds x^2 over the 8-element chunks t, t+256, ... ; xor butterfly per warp; warp sums added in ascending

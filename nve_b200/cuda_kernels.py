@@ -480,6 +480,38 @@ def attn_decode_fused(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, 
                                                  num_kv_heads, head_dim, max_seq_len, float(scale), stream()))
 
 
+# --------------------------------------------------------------------------- whole step in one kernel
+def decode_step_workspace_bytes(model: "_ffi.DecodeModel") -> int:
+    n = int(_lib().nve_b200_decode_step_workspace_bytes(C.byref(model)))
+    _ffi.check_last("nve_b200_decode_step_workspace_bytes")
+    return n
+
+
+def decode_step_init(workspace: Tensor) -> None:
+    _ffi.check("nve_b200_decode_step_init",
+               _lib().nve_b200_decode_step_init(_ptr(workspace), workspace.numel() * workspace.element_size(), stream()))
+
+
+def decode_step(model: "_ffi.DecodeModel", layers_dev: Tensor, hidden: Tensor, d_pos: int, d_seqlen: int,
+                workspace: Tensor) -> None:
+    """One token through all layers in one persistent kernel (nve_b200_decode_step); `hidden` is updated in place."""
+    _ffi.check("nve_b200_decode_step",
+               _lib().nve_b200_decode_step(C.byref(model), _ptr(layers_dev), _ptr(hidden, _F16, "hidden"), d_pos, d_seqlen,
+                                           _ptr(workspace), workspace.numel() * workspace.element_size(), stream()))
+
+
+def decode_step_error(workspace: Tensor, reset: bool = False) -> int:
+    return int(_lib().nve_b200_decode_step_error(_ptr(workspace), int(reset)))
+
+
+def decode_step_set_prefetch(nbytes: int) -> int:
+    return int(_lib().nve_b200_decode_step_set_prefetch(int(nbytes)))
+
+
+def decode_step_wait_probe(workspace: Tensor, wait_ns: int) -> None:
+    _ffi.check("nve_b200_decode_step_wait_probe", _lib().nve_b200_decode_step_wait_probe(_ptr(workspace), int(wait_ns), stream()))
+
+
 def matvec_w4a8_allreduce(xq: Tensor, xq_scales: Tensor, weights: Sequence, k: int, out_dtype=torch.float16,
                           outs: Optional[Sequence[Tensor]] = None, residuals=None):
     """Row-parallel W4A8 GEMV of one matrix with the all-reduce over the tensor-parallel ranks fused in."""

@@ -119,6 +119,97 @@ class StaticDecodeGraph:
         self.captured = False
 
 
+class PersistentDecode:
+    """The same decode step as `StaticDecodeGraph`, run by ONE persistent kernel (nve_b200_decode_step) instead of
+    six launches per layer.  The launch is recorded into the library's graph like the layer sequence is, so
+    `replay` / `replay_resident` drive it through the same pinned position scalars; the hidden state it leaves is
+    bit-identical to the six-launch graph.  `lm_head` = (GpuW4, final_norm weight, use_w4a8) adds the device-side
+    final RMSNorm + lm_head GEMV; logits land in `self.logits` (f32)."""
+
+    def __init__(self, state: GpuInferenceState, hidden_size: int, ffn_size: int, importance: Sequence[float],
+                 lm_head=None):
+        import ctypes as C
+
+        from . import _ffi
+
+        self.state = state
+        self.hidden_size, self.ffn_size = hidden_size, ffn_size
+        self.importance = list(importance)
+        self.routes: List[bool] = [state.routing.use_w4a8(x) for x in self.importance]
+        dev = state.rope_cos.device
+        self.hidden_buf = torch.zeros((1, hidden_size), dtype=torch.float16, device=dev)
+        m = _ffi.DecodeModel()
+        m.hidden, m.ffn = hidden_size, ffn_size
+        m.num_heads, m.num_kv_heads, m.head_dim = state.num_heads, state.num_kv_heads, state.head_dim
+        m.max_seq, m.num_layers = state.kv_cache.max_seq, len(state.layer_weights)
+        m.norm_eps, m.attn_scale = state.norm_eps, float(state.head_dim) ** -0.5
+        m.rope_cos, m.rope_sin = state.rope_cos.data_ptr(), state.rope_sin.data_ptr()
+        self.logits = None
+        self._keep = []
+        if lm_head is not None:
+            w, final_norm, use_w4a8 = lm_head
+            self.logits = torch.zeros(w.n, dtype=torch.float32, device=dev)
+            m.final_norm, m.lm_nibbles, m.lm_scales = final_norm.data_ptr(), w.nibbles.data_ptr(), w.scales.data_ptr()
+            m.logits, m.vocab, m.lm_use_w4a8 = self.logits.data_ptr(), w.n, int(bool(use_w4a8))
+            self._keep += [w, final_norm]
+        self.model = m
+        descs = (_ffi.DecodeLayer * m.num_layers)()
+        for li, lw in enumerate(state.layer_weights):
+            d = descs[li]
+            projs = [lw.q_proj, lw.k_proj, lw.v_proj, lw.o_proj, lw.gate_proj, lw.up_proj, lw.down_proj]
+            for j, w in enumerate(projs):
+                d.nibbles[j], d.scales[j] = w.nibbles.data_ptr(), w.scales.data_ptr()
+            if not (lw.q_proj.awq_scales is lw.k_proj.awq_scales is lw.v_proj.awq_scales) or \
+                    lw.gate_proj.awq_scales is not lw.up_proj.awq_scales:
+                raise ValueError("q/k/v (and gate/up) must share one activation multiplier")
+            for j, w in enumerate((lw.q_proj, lw.o_proj, lw.gate_proj, lw.down_proj)):
+                d.awq[j] = w.awq_scales.data_ptr() if w.awq_scales is not None else None
+            d.input_norm, d.post_attn_norm = lw.input_norm.data_ptr(), lw.post_attn_norm.data_ptr()
+            d.k_cache, d.v_cache = state.kv_cache.k[li].data_ptr(), state.kv_cache.v[li].data_ptr()
+            d.use_w4a8 = int(self.routes[li])
+        raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8)
+        self.layers_dev = raw.to(dev)
+        nbytes = ck.decode_step_workspace_bytes(m)
+        self.workspace = torch.zeros(nbytes + 256, dtype=torch.uint8, device=dev)
+        off = (-self.workspace.data_ptr()) % 256
+        self.workspace = self.workspace[off:off + nbytes]
+        ck.decode_step_init(self.workspace)
+        self.launches_per_replay = 1
+        self.captured = False
+
+    def step(self, d_pos: int, d_seqlen: int) -> None:
+        """Enqueue the kernel on the current (or capture) stream with device position scalars."""
+        ck.decode_step(self.model, self.layers_dev, self.hidden_buf, d_pos, d_seqlen, self.workspace)
+
+    def capture(self) -> None:
+        ck.graph_init()
+        ck.graph_begin_capture()
+        try:
+            self.step(ck.graph_d_pos_ptr(), ck.graph_d_seqlen_ptr())
+        finally:
+            ck.graph_end_capture()
+        if not ck.graph_ready():
+            raise RuntimeError("decode graph instantiation failed")
+        self.captured = True
+
+    def replay(self, hidden_in: Tensor, pos: int, copy_out: bool = True) -> Optional[Tensor]:
+        if not self.captured:
+            raise RuntimeError("capture() first")
+        ck.device_copy(self.hidden_buf, hidden_in)
+        ck.graph_launch(pos, min(pos + 1, self.state.kv_cache.max_seq))
+        return self.hidden_buf.clone() if copy_out else None
+
+    def replay_resident(self, pos: int) -> None:
+        ck.graph_launch(pos, min(pos + 1, self.state.kv_cache.max_seq))
+
+    def error(self, reset: bool = False) -> int:
+        return ck.decode_step_error(self.workspace, reset)
+
+    def destroy(self) -> None:
+        ck.graph_destroy()
+        self.captured = False
+
+
 class CapturedSequence:
     """Record an arbitrary sequence of library launches into the library's (single, process-global) graph and
     replay it.  Used by the measurement harness to time subsets of the decode step (e.g. the GEMV launches
