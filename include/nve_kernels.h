@@ -368,9 +368,9 @@ NVE_API int nve_b200_decode_step(const nve_b200_decode_model* model, const nve_b
                                  nve_stream_t stream);
 /* Synchronous: the latched error word of the workspace (0 = none); reset != 0 clears it and the barrier state. */
 NVE_API int nve_b200_decode_step_error(void* workspace, int reset);
-/* Run-ahead distance in bytes of the kernel's L2 prefetch stream (0 disables it); returns the previous value;
- * a negative argument only queries. */
-NVE_API long long nve_b200_decode_step_set_prefetch(long long bytes);
+/* Run-ahead distance of the kernel's L2 prefetch walk, in weight items (5 KB) per warp (0 disables it, at most 64);
+ * returns the previous value; a negative argument only queries. */
+NVE_API int nve_b200_decode_step_set_prefetch(int items);
 /* Debugging aid: when `buf` (device memory, 2 * phases * 4 u64; phases = 7 per layer + 1 with an lm_head) is set,
  * CTA 0 and the last CTA record nanosecond timestamps per phase: phase entry, barrier passed, activations staged,
  * phase done.  NULL (the default) switches it off. */

@@ -144,7 +144,7 @@ SIGNATURES = {
     "nve_b200_decode_step_init": (_I, [_P, _S, _P]),
     "nve_b200_decode_step": (_I, [C.POINTER(DecodeModel), _P, _P, _P, _P, _P, _S, _P]),
     "nve_b200_decode_step_error": (_I, [_P, _I]),
-    "nve_b200_decode_step_set_prefetch": (_LL, [_LL]),
+    "nve_b200_decode_step_set_prefetch": (_I, [_I]),
     "nve_b200_decode_step_wait_probe": (_I, [_P, _ULL, _P]),
     "nve_b200_decode_step_set_trace": (None, [_P]),
     "nve_b200_tp_create": (_I, [_I, _I, _I, _P]),

@@ -4,7 +4,8 @@
 //
 //   * a "virtual CTA" is 256 threads = PL position lanes x DC dim chunks (DC = head_dim/8 lanes hold one 16-byte
 //     slice of a row); it serves QH query heads that share one KV head and owns the positions
-//     [rank*chunk, (rank+1)*chunk), chunk = ceil(seq_len / kAdRanks);
+//     [rank*chunk, (rank+1)*chunk), chunk = ceil(seq_len / kAdRanks) (the stand-alone kernel's cluster of
+//     kAdCluster CTAs runs kAdRanks / kAdCluster of them per CTA, the persistent kernel one per half CTA);
 //   * every thread keeps a private online-softmax state over the positions t_begin + it*PL*4 + u*PL + pl;
 //   * level 1: the PL lane states of a virtual CTA are merged in ascending lane order (attn_merge_lanes);
 //   * level 2: the kAdRanks partials of a head are merged in ascending rank order (attn_merge_ranks).
@@ -16,7 +17,8 @@
 
 namespace nve {
 
-constexpr int kAdRanks = 8;      // position slices per head (cluster size of the stand-alone kernel)
+constexpr int kAdRanks = 8;      // position slices per head
+constexpr int kAdCluster = 8;    // CTAs per cluster of the stand-alone kernel (portable cluster size)
 constexpr int kAdThreads = 256;  // threads of a virtual CTA
 constexpr int kAdUnroll = 4;
 
@@ -43,12 +45,18 @@ template <int HD, int QH> struct AdShared {
     __align__(16) uint16_t knew_s[HD];
     __align__(16) uint16_t vnew_s[HD];
     float pm[PL][QH], ps[PL][QH];
+    float pc[PL][QH];  // exp(pm - max over lanes): computed once per (lane, head) for the level-1 merge
     float pacc[PL][QH][HD];
 };
 
 // Stage q (rotated at `pos` in the fused form) and the rotated new k row / new v row of the KV head.
-// tid in [0, 256).  The caller synchronises the virtual CTA afterwards.
-template <int HD, int QH, bool FUSED>
+// tid in [0, 256).  The caller synchronises the virtual CTA afterwards.  L2ONLY: q / k_new / v_new were written by
+// other CTAs of the same (persistent) kernel and are read past L1.
+template <bool L2ONLY> __device__ __forceinline__ uint16_t attn_ld16(const uint16_t* p) {
+    if constexpr (L2ONLY) return __ldcg(p);
+    else return *p;
+}
+template <int HD, int QH, bool FUSED, bool L2ONLY = false>
 __device__ __forceinline__ void attn_stage_q(AdShared<HD, QH>& sh, int tid, const uint16_t* q, const uint16_t* k_new,
                                              const uint16_t* v_new, const uint16_t* cos_tab, const uint16_t* sin_tab,
                                              int h0, int kvh, int pos, bool pos_ok) {
@@ -60,7 +68,8 @@ __device__ __forceinline__ void attn_stage_q(AdShared<HD, QH>& sh, int tid, cons
             const int h = i / HALF, e = i % HALF;
             const uint16_t* qp = q + static_cast<long long>(h0 + h) * HD;
             const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
-            const float x0 = Act16<NVE_DT_F16>::to_f32(qp[e]), x1 = Act16<NVE_DT_F16>::to_f32(qp[e + HALF]);
+            const float x0 = Act16<NVE_DT_F16>::to_f32(attn_ld16<L2ONLY>(qp + e));
+            const float x1 = Act16<NVE_DT_F16>::to_f32(attn_ld16<L2ONLY>(qp + e + HALF));
             const uint16_t r0 = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
             const uint16_t r1 = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
             sh.q_s[h][e] = Act16<NVE_DT_F16>::to_f32(r0);
@@ -69,14 +78,15 @@ __device__ __forceinline__ void attn_stage_q(AdShared<HD, QH>& sh, int tid, cons
         for (int e = tid; e < HALF; e += kAdThreads) {
             const uint16_t* kp = k_new + static_cast<long long>(kvh) * HD;
             const float c = Act16<NVE_DT_F16>::to_f32(cr[e]), s = Act16<NVE_DT_F16>::to_f32(sr[e]);
-            const float x0 = Act16<NVE_DT_F16>::to_f32(kp[e]), x1 = Act16<NVE_DT_F16>::to_f32(kp[e + HALF]);
+            const float x0 = Act16<NVE_DT_F16>::to_f32(attn_ld16<L2ONLY>(kp + e));
+            const float x1 = Act16<NVE_DT_F16>::to_f32(attn_ld16<L2ONLY>(kp + e + HALF));
             sh.knew_s[e] = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
             sh.knew_s[e + HALF] = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
         }
-        for (int e = tid; e < HD; e += kAdThreads) sh.vnew_s[e] = v_new[static_cast<long long>(kvh) * HD + e];
+        for (int e = tid; e < HD; e += kAdThreads) sh.vnew_s[e] = attn_ld16<L2ONLY>(v_new + static_cast<long long>(kvh) * HD + e);
     } else {
         for (int i = tid; i < QH * HD; i += kAdThreads)
-            sh.q_s[i / HD][i % HD] = Act16<NVE_DT_F16>::to_f32(q[static_cast<long long>(h0) * HD + i]);
+            sh.q_s[i / HD][i % HD] = Act16<NVE_DT_F16>::to_f32(attn_ld16<L2ONLY>(q + static_cast<long long>(h0) * HD + i));
     }
 }
 
@@ -191,13 +201,21 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
         for (int i = 0; i < 8; i++) sh.pacc[pl][h][dc * 8 + i] = acc[h][i];
     }
     sync();
+    // the rescaling factor of a lane state is the same for all 8*DC elements of its head: one thread computes it
+    if (tid < PL * QH) {
+        const int l = tid / QH, h = tid % QH;
+        float mm = -1e30f;
+        for (int k = 0; k < PL; k++) mm = fmaxf(mm, sh.pm[k][h]);
+        sh.pc[l][h] = expf(__fsub_rn(sh.pm[l][h], mm));
+    }
+    sync();
     for (int i = tid; i < QH * HD; i += kAdThreads) {
         const int h = i / HD, d = i % HD;
         float mm = -1e30f;
         for (int l = 0; l < PL; l++) mm = fmaxf(mm, sh.pm[l][h]);
         float ss = 0.0f, a = 0.0f;
         for (int l = 0; l < PL; l++) {
-            const float c = expf(__fsub_rn(sh.pm[l][h], mm));
+            const float c = sh.pc[l][h];
             ss = __fmaf_rn(sh.ps[l][h], c, ss);
             a = __fmaf_rn(sh.pacc[l][h][d], c, a);
         }
@@ -207,17 +225,28 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
 
 // Level 2 for element (h, d): merge the kAdRanks partials in ascending rank order and normalise; returns the
 // 16-bit rounded output.  `parts` points at kAdRanks consecutive partials of the virtual cluster.
-template <int HD, int QH>
+template <bool L2ONLY> __device__ __forceinline__ float attn_ldf(const float* p) {
+    if constexpr (L2ONLY) return __ldcg(p);
+    else return *p;
+}
+template <int HD, int QH, bool L2ONLY = false>
 __device__ __forceinline__ uint16_t attn_merge_ranks(const AdCtaPartial<HD, QH>* parts, int h, int d) {
+    float pm[kAdRanks], ps[kAdRanks], pa[kAdRanks];
+#pragma unroll
+    for (int r = 0; r < kAdRanks; r++) {  // all loads in flight together
+        pm[r] = attn_ldf<L2ONLY>(&parts[r].m[h]);
+        ps[r] = attn_ldf<L2ONLY>(&parts[r].s[h]);
+        pa[r] = attn_ldf<L2ONLY>(&parts[r].acc[h][d]);
+    }
     float mm = -1e30f;
 #pragma unroll
-    for (int r = 0; r < kAdRanks; r++) mm = fmaxf(mm, parts[r].m[h]);
+    for (int r = 0; r < kAdRanks; r++) mm = fmaxf(mm, pm[r]);
     float ss = 0.0f, a = 0.0f;
 #pragma unroll
     for (int r = 0; r < kAdRanks; r++) {
-        const float c = expf(__fsub_rn(parts[r].m[h], mm));
-        ss = __fmaf_rn(parts[r].s[h], c, ss);
-        a = __fmaf_rn(parts[r].acc[h][d], c, a);
+        const float c = expf(__fsub_rn(pm[r], mm));
+        ss = __fmaf_rn(ps[r], c, ss);
+        a = __fmaf_rn(pa[r], c, a);
     }
     const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
     return Act16<NVE_DT_F16>::from_f32(__fmul_rn(a, inv));

@@ -25,8 +25,6 @@ namespace cg = cooperative_groups;
 
 namespace nve {
 
-constexpr int kAdCluster = kAdRanks;
-
 struct AttnParams {
     const uint16_t* q;        // [nh, hd]
     const uint16_t* k_new;    // [nkv, hd] (fused form)
@@ -55,7 +53,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     cluster.barrier_arrive();
 
     __shared__ AdShared<HD, QH> sh;
-    __shared__ AdCtaPartial<HD, QH> parts[kAdCluster];  // only rank 0's copy is used: every CTA pushes its partial there
+    __shared__ AdCtaPartial<HD, QH> parts[kAdRanks];  // only rank 0's copy is used: every CTA pushes its partials there
 
     const int tid = threadIdx.x;
     const int dc = tid % DC, pl = tid / DC;
@@ -78,7 +76,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     if constexpr (FUSED) {
         pre_seq = max(0, min(*p.d_seq_len, p.kv_stride));
         pre_pos = *p.d_pos;
-        const int pchunk = (pre_seq + kAdCluster - 1) / kAdCluster;
+        const int pchunk = (pre_seq + kAdRanks - 1) / kAdRanks;
         const int pb = rank * pchunk, pe = min(pre_seq, pb + pchunk);
         const int safe = pb < p.kv_stride ? pb : 0;
 #pragma unroll
@@ -105,9 +103,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     __syncthreads();
     pdl_launch_dependents();
 
-    const int chunk = (seq_len + kAdCluster - 1) / kAdCluster;
-    const int t_begin = rank * chunk;
-    const int t_end = min(seq_len, t_begin + chunk);
+    const int chunk = (seq_len + kAdRanks - 1) / kAdRanks;
     // one CTA per KV head stores the new row; every CTA that covers `pos` reads it from shared memory
     if constexpr (FUSED) {
         if (pos_ok && rank == 0 && (cluster_id % clusters_per_kv) == 0 && tid < 2 * DC) {
@@ -117,14 +113,21 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
         }
     }
 
-    // push this CTA's partial into rank 0's shared memory (posted remote stores, no round trip)
+    // push this CTA's partial into rank 0's shared memory (posted remote stores, no round trip); the level-1 merge
+    // starts with a CTA barrier and the matching cluster wait rides on it (all CTAs of the cluster run by then)
+    static_assert(kAdRanks == kAdCluster, "one position slice per CTA of the cluster");
+    const int t_begin = rank * chunk;
+    const int t_end = min(seq_len, t_begin + chunk);
     AdCtaPartial<HD, QH>* dst = cluster.map_shared_rank(&parts[rank], 0);
-    // the level-1 merge starts with a CTA barrier; the matching cluster wait rides on it (all CTAs run by then)
+    bool first = true;
     attn_partial<HD, QH, FUSED, FUSED>(
         sh, tid, kh, vh, t_begin, t_end, pos, p.scale, pre_ok, &pre,
         [&] {
             __syncthreads();
-            cluster.barrier_wait();
+            if (first) {
+                cluster.barrier_wait();
+                first = false;
+            }
         },
         [&](int h, int d, float mm, float ss, float a) {
             dst->acc[h][d] = a;

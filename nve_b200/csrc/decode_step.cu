@@ -18,6 +18,10 @@
 //     GEMV does): RMSNorm + int8 / 16-bit fixed-point conversion into shared-memory planes by 512 threads.
 //   * GEMV phases are warp-autonomous: a warp owns whole rows (R rows x all column groups, ascending), so there
 //     is no shared-memory partial-sum exchange and no CTA barrier inside a phase.
+//   * Five phases (= five device-wide barriers) per layer: [RMSNorm + q/k/v], [RoPE + KV write + attention, the
+//     CTA that finishes a head pair last merges its position slices], [o_proj + residual], [RMSNorm + gate/up with
+//     SiLU*up in the epilogue: a warp owns gate row i and up row i], [down + residual].  The int8 / fixed-point
+//     conversion of the attention output and of SiLU*up happens in the consumer's staging, once per SM.
 //   * Arithmetic and summation order are those of the stand-alone kernels (gemv_w4.cu, act_quant.cu,
 //     attn_decode.cu: same device functions), so the hidden state equals the six-launch-per-layer graph bit for
 //     bit.
@@ -37,19 +41,14 @@ constexpr unsigned long long kDsWaitNs = 100ull * 1000 * 1000;  // bound of ever
 // Workspace carved out of the caller's buffer (offsets fixed by ds_layout()).
 struct DsWork {
     unsigned long long* bar;  // arrival counter of the device-wide barrier (monotonic)
-    int* err;                 // 0, or NVE_DS_ERR_* latched by an expired wait
+    int* err;                 // 0, or NVE_ERR_TIMEOUT latched by an expired wait
+    int* attn_cnt;            // per pair of head pairs: position slices finished (returns to 0 in every layer)
     uint16_t* q;              // [nh*hd] f16
     uint16_t* k;              // [nkv*hd]
     uint16_t* v;
     void* parts;              // attention partials: [virtual clusters][kAdRanks] AdCtaPartial<hd, 2>
     uint16_t* attn;           // [nh*hd] f16
-    int8_t* xq_a;             // int8 codes of attn (W4A8 route)
-    float* xs_a;
-    uint16_t* gate;           // [ffn] f16
-    uint16_t* up;
-    int8_t* xq_f;             // codes (W4A8) or high bytes (W4A16 fixed point) of silu(gate)*up
-    uint8_t* xlo_f;           // low bytes (W4A16)
-    float* xs_f;
+    uint16_t* mid;            // [ffn] f16: silu(gate) * up
 };
 
 struct DsParams {
@@ -60,7 +59,7 @@ struct DsParams {
     const int* d_seq_len;
     DsWork w;
     unsigned long long wait_ns;
-    long long pf_bytes;  // run-ahead distance of the L2 prefetch stream (0 = off)
+    int pf_items;  // run-ahead distance of the L2 prefetch walk in items per warp (0 = off)
     unsigned long long* trace;  // debugging aid: per phase 4 globaltimer stamps of CTA 0 and of the last CTA, or NULL
 };
 
@@ -80,6 +79,7 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 __device__ __forceinline__ void red_release_add_u64(unsigned long long* p, unsigned long long v) {
     asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void l2_prefetch_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void l2_prefetch_bulk(const void* p, unsigned bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
@@ -112,7 +112,7 @@ __device__ __forceinline__ void grid_barrier(const DsParams& p, unsigned long lo
 // ---------------------------------------------------------------------------------------------
 // GEMV phase
 // ---------------------------------------------------------------------------------------------
-enum { kEpiF16 = 0, kEpiResidual = 1, kEpiF32 = 2 };
+enum { kEpiF16 = 0, kEpiResidual = 1, kEpiF32 = 2, kEpiSiluMul = 3 };
 
 struct PhaseMats {
     const uint8_t* nib[3];
@@ -123,6 +123,8 @@ struct PhaseMats {
     int K, nb, S;
     int epi;
     int planes;  // 1 = W4A8, 2 = W4A16
+    int paired;  // gate/up: a tile holds R/2 gate rows and the R/2 up rows of the same indices
+    int tb, te;  // tile range of this CTA
 };
 
 struct WFlat {  // one warp item: R rows x C column sets (R*C = 8 blocks per lane), index c*R + r
@@ -133,46 +135,88 @@ struct WFlat {  // one warp item: R rows x C column sets (R*C = 8 blocks per lan
 __device__ __forceinline__ int pm_rows_per_tile(const PhaseMats& pm) { return pm.S >= 3 ? 2 : (pm.S == 2 ? 4 : 8); }
 
 __device__ __forceinline__ void pm_locate(const PhaseMats& pm, int grow, const uint8_t*& nib, const float*& sc, int& lrow,
-                                          int& lend, int& mat) {
+                                          int& lend, void*& out) {
     if (grow < pm.row_end[0]) {
-        nib = pm.nib[0]; sc = pm.sc[0]; lrow = grow; lend = pm.row_end[0]; mat = 0;
+        nib = pm.nib[0]; sc = pm.sc[0]; lrow = grow; lend = pm.row_end[0]; out = pm.out[0];
     } else if (grow < pm.row_end[1]) {
-        nib = pm.nib[1]; sc = pm.sc[1]; lrow = grow - pm.row_end[0]; lend = pm.row_end[1] - pm.row_end[0]; mat = 1;
+        nib = pm.nib[1]; sc = pm.sc[1]; lrow = grow - pm.row_end[0]; lend = pm.row_end[1] - pm.row_end[0]; out = pm.out[1];
     } else {
-        nib = pm.nib[2]; sc = pm.sc[2]; lrow = grow - pm.row_end[1]; lend = pm.row_end[2] - pm.row_end[1]; mat = 2;
+        nib = pm.nib[2]; sc = pm.sc[2]; lrow = grow - pm.row_end[1]; lend = pm.row_end[2] - pm.row_end[1]; out = pm.out[2];
     }
 }
 
+// Tile range of this CTA for a phase (computed once when the phase is published).
+__device__ __forceinline__ void pm_set_cta_tiles(PhaseMats& pm) {
+    const int R = pm_rows_per_tile(pm);
+    const int tiles = (pm.n_total + R - 1) / R;
+    pm.tb = static_cast<int>(static_cast<long long>(tiles) * blockIdx.x / gridDim.x);
+    pm.te = static_cast<int>(static_cast<long long>(tiles) * (blockIdx.x + 1) / gridDim.x);
+}
+__device__ __forceinline__ void pm_cta_tiles(const PhaseMats& pm, int& tb, int& te) {
+    tb = pm.tb;
+    te = pm.te;
+}
+
+struct ItemIt {
+    int g;   // GEMV phase (execution order)
+    int t;   // tile, or -1: not yet placed in phase g
+    int cg;  // column group
+};
+
+// Row r of a tile: matrix pointers and the row's first block index (rows past the end of a matrix are clamped for
+// the load and discarded at the store).
+__device__ __forceinline__ void item_row(const PhaseMats& pm, int tile, int r, int R, const uint8_t*& nib, const float*& sc,
+                                         long long& rb) {
+    int lrow, lend;
+    if (pm.paired) {
+        const int half = R >> 1;
+        const bool up = r >= half;
+        nib = up ? pm.nib[1] : pm.nib[0];
+        sc = up ? pm.sc[1] : pm.sc[0];
+        lrow = tile * half + (up ? r - half : r);
+        lend = pm.row_end[0];
+    } else {
+        void* out_unused;
+        pm_locate(pm, tile * R, nib, sc, lrow, lend, out_unused);
+        lrow += r;
+    }
+    rb = static_cast<long long>(min(lrow, lend - 1)) * pm.nb;
+}
+
+// Load one item into registers.  pf_tiles > 0: the lanes that own the first 16 bytes of a 128-byte line also ask L2
+// for the same lines of the tile `pf_tiles` tiles further down this warp's sequence (same phase only; the rows of a
+// matrix are evenly spaced, so that is a constant byte offset from the addresses computed for the load).
 template <int R, int C>
-__device__ __forceinline__ void ds_load_item(const PhaseMats& pm, int tile, int cg, int lane, WFlat& t) {
-    const uint8_t* nib;
-    const float* sc;
-    int lrow, lend, mat;
-    pm_locate(pm, tile * R, nib, sc, lrow, lend, mat);
+__device__ __forceinline__ void ds_load_item(const PhaseMats& pm, int tile, int cg, int lane, WFlat& t, int pf_tiles = 0) {
+    bool pf = pf_tiles > 0 && tile + pf_tiles * kDsWarps < pm.te;
+    if (pf && !pm.paired && pm.row_end[0] != pm.n_total) {
+        // several matrices in one launch: only when the far tile lies in the same matrix as this one
+        const int r0 = tile * R, r1 = (tile + pf_tiles * kDsWarps) * R;
+        const int m0 = r0 < pm.row_end[0] ? 0 : (r0 < pm.row_end[1] ? 1 : 2);
+        const int m1 = r1 < pm.row_end[0] ? 0 : (r1 < pm.row_end[1] ? 1 : 2);
+        pf = m0 == m1;
+    }
+    const long long pf_rows = static_cast<long long>(pf_tiles) * kDsWarps * (pm.paired ? R / 2 : R);
 #pragma unroll
     for (int r = 0; r < R; r++) {
-        // rows past the end of a matrix are clamped for the load and discarded at the store
-        const long long rb = static_cast<long long>(min(lrow + r, lend - 1)) * pm.nb;
+        const uint8_t* nib;
+        const float* sc;
+        long long rb;
+        item_row(pm, tile, r, R, nib, sc, rb);
 #pragma unroll
         for (int c = 0; c < C; c++) {
             const int b = (cg * C + c) * kWarp + lane;
             if (b < pm.nb) {
                 t.w[c * R + r] = ld_stream_u4(nib + (rb + b) * 16);
                 t.s[c * R + r] = ld_stream_f32(sc + rb + b);
+                if (pf && (lane & 7) == 0) l2_prefetch_line(nib + (rb + pf_rows * pm.nb + b) * 16);
+                if (pf && lane == 0) l2_prefetch_line(sc + rb + pf_rows * pm.nb + b);
             } else {
                 t.w[c * R + r] = make_uint4(0, 0, 0, 0);
                 t.s[c * R + r] = 0.0f;
             }
         }
     }
-}
-
-// Tile range of this CTA for a phase.
-__device__ __forceinline__ void pm_cta_tiles(const PhaseMats& pm, int& tb, int& te) {
-    const int R = pm_rows_per_tile(pm);
-    const int tiles = (pm.n_total + R - 1) / R;
-    tb = static_cast<int>(static_cast<long long>(tiles) * blockIdx.x / gridDim.x);
-    te = static_cast<int>(static_cast<long long>(tiles) * (blockIdx.x + 1) / gridDim.x);
 }
 
 // First item of this warp for the phase (issued before the barrier in front of the phase).
@@ -186,13 +230,63 @@ __device__ __forceinline__ void pm_load_first(const PhaseMats& pm, int warp, int
     else ds_load_item<8, 1>(pm, t, 0, lane, it);
 }
 
+// ---------------------------------------------------------------------------------------------
+// L2 prefetch stream.  Weights never depend on activations, so every warp walks the sequence of its own future
+// items -- across phase boundaries -- and asks for their cache lines (`prefetch.global.L2`) a fixed number of items
+// ahead of the item it computes.  DRAM therefore stays busy while the CTA waits at a barrier or stages activations,
+// and the register loads of an item mostly hit L2.  The matrices of the next kPmSlots - 1 GEMV phases are
+// published in shared memory (pms[g % kPmSlots]) so that the walk can look that far.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPmSlots = 4;
+
+// The 40 cache lines of one item: lane l asks for 128-byte line l % 4 of nibble slot l / 4; lanes 0..7 for the
+// scale line of slot l.
+__device__ __forceinline__ void pf_item(const PhaseMats& pm, int tile, int cg, int lane) {
+    const int R = pm_rows_per_tile(pm);
+    const int C = 8 / R;
+    {
+        const int j = lane >> 2, c = j / R, r = j % R;
+        const uint8_t* nib;
+        const float* sc;
+        long long rb;
+        item_row(pm, tile, r, R, nib, sc, rb);
+        const int b = (cg * C + c) * kWarp + (lane & 3) * 8;
+        if (b < pm.nb) l2_prefetch_line(nib + (rb + b) * 16);
+    }
+    if (lane < 8) {
+        const int c = lane / R, r = lane % R;
+        const uint8_t* nib;
+        const float* sc;
+        long long rb;
+        item_row(pm, tile, r, R, nib, sc, rb);
+        const int b = (cg * C + c) * kWarp;
+        if (b < pm.nb) l2_prefetch_line(sc + rb + b);
+    }
+}
+
+// Ask L2 for this warp's first `items` items of a phase that has not started yet (called when the warp has finished
+// the phase in front of it: the requests are served while the CTA waits at the barrier and stages activations).
+__device__ __forceinline__ void pf_head(const PhaseMats& pm, int items, int warp, int lane) {
+    const int C = pm.S >= 3 ? 4 : (pm.S == 2 ? 2 : 1);
+    const int CG = (pm.S + C - 1) / C;
+    int t = pm.tb + warp, cg = 0;
+    for (int i = 0; i < items && t < pm.te; i++) {
+        pf_item(pm, t, cg, lane);
+        if (++cg >= CG) {
+            cg = 0;
+            t += kDsWarps;
+        }
+    }
+}
+
 template <int PLANES, int R, int C>
 __device__ __forceinline__ void ds_run_gemv(const PhaseMats& pm, Smem<PLANES>& sm, const uint16_t* residual, int warp,
-                                            int lane, WFlat& it) {
+                                            int lane, WFlat& it, int dist) {
     const int S = pm.S;
     const int CG = (S + C - 1) / C;
     int tb, te;
     pm_cta_tiles(pm, tb, te);
+    const int pf_tiles = dist > 0 ? (dist + CG - 1) / CG : 0;  // tiles ahead that cover `dist` items
     for (int t = tb + warp; t < te; t += kDsWarps) {
         float y = 0.0f;
         for (int cg = 0; cg < CG; cg++) {
@@ -217,28 +311,41 @@ __device__ __forceinline__ void ds_run_gemv(const PhaseMats& pm, Smem<PLANES>& s
                     a[r] = (c == 0) ? v : __fadd_rn(a[r], v);
                 }
             }
-            // issue the next item's loads before reducing this one
-            if (cg + 1 < CG) ds_load_item<R, C>(pm, t, cg + 1, lane, it);
-            else if (t + kDsWarps < te) ds_load_item<R, C>(pm, t + kDsWarps, 0, lane, it);
+            // issue the next item's loads before reducing this one, and keep the L2 prefetch walk `dist` items ahead
+            if (cg + 1 < CG) ds_load_item<R, C>(pm, t, cg + 1, lane, it, pf_tiles);
+            else if (t + kDsWarps < te) ds_load_item<R, C>(pm, t + kDsWarps, 0, lane, it, pf_tiles);
             warp_sum_multi<R>(a, lane);
             y = (cg == 0) ? a[0] : __fadd_rn(y, a[0]);  // column groups of a row in ascending order
         }
-        if (multi_row_writer<R>(lane)) {
+        if (pm.epi == kEpiSiluMul) {
+            // lanes l and l ^ 16 hold gate row i and up row i: mid[i] = f16(silu(f16 gate) * f16 up), the bits of the
+            // separate GEMV (f16 outputs) + SiLU*up kernels
+            const float yu = __shfl_xor_sync(0xffffffffu, y, 16);
+            if (multi_row_writer<R>(lane) && (lane & 16) == 0) {
+                const int i = t * (R / 2) + multi_row_of<R>(lane);
+                if (i < pm.row_end[0]) {
+                    const float g = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(y));
+                    const float u = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(yu));
+                    static_cast<uint16_t*>(pm.out[0])[i] = Act16<NVE_DT_F16>::from_f32(silu_mul_f32(g, u));
+                }
+            }
+        } else if (multi_row_writer<R>(lane)) {
             const int grow = t * R + multi_row_of<R>(lane);
             if (grow < pm.n_total) {
                 const uint8_t* nib;
                 const float* sc;
-                int lrow, lend, mat;
-                pm_locate(pm, grow, nib, sc, lrow, lend, mat);
+                int lrow, lend;
+                void* out;
+                pm_locate(pm, grow, nib, sc, lrow, lend, out);
                 if (pm.epi == kEpiResidual) {
                     // same bits as a GEMV with f16 output followed by the residual-add kernel
                     const float yr = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(y));
                     const float h = __fadd_rn(Act16<NVE_DT_F16>::to_f32(__ldcg(residual + lrow)), yr);
-                    static_cast<uint16_t*>(pm.out[mat])[lrow] = Act16<NVE_DT_F16>::from_f32(h);
+                    static_cast<uint16_t*>(out)[lrow] = Act16<NVE_DT_F16>::from_f32(h);
                 } else if (pm.epi == kEpiF32) {
-                    static_cast<float*>(pm.out[mat])[lrow] = y;
+                    static_cast<float*>(out)[lrow] = y;
                 } else {
-                    static_cast<uint16_t*>(pm.out[mat])[lrow] = Act16<NVE_DT_F16>::from_f32(y);
+                    static_cast<uint16_t*>(out)[lrow] = Act16<NVE_DT_F16>::from_f32(y);
                 }
             }
         }
@@ -247,11 +354,11 @@ __device__ __forceinline__ void ds_run_gemv(const PhaseMats& pm, Smem<PLANES>& s
 
 template <int PLANES>
 __device__ __forceinline__ void ds_run_gemv_rc(const PhaseMats& pm, unsigned char* smem_raw, const uint16_t* residual,
-                                               int warp, int lane, WFlat& it) {
+                                               int warp, int lane, WFlat& it, int dist) {
     Smem<PLANES> sm(smem_raw, pm.S * kWarp);
-    if (pm.S >= 3) ds_run_gemv<PLANES, 2, 4>(pm, sm, residual, warp, lane, it);
-    else if (pm.S == 2) ds_run_gemv<PLANES, 4, 2>(pm, sm, residual, warp, lane, it);
-    else ds_run_gemv<PLANES, 8, 1>(pm, sm, residual, warp, lane, it);
+    if (pm.S >= 3) ds_run_gemv<PLANES, 2, 4>(pm, sm, residual, warp, lane, it, dist);
+    else if (pm.S == 2) ds_run_gemv<PLANES, 4, 2>(pm, sm, residual, warp, lane, it, dist);
+    else ds_run_gemv<PLANES, 8, 1>(pm, sm, residual, warp, lane, it, dist);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -271,15 +378,15 @@ __device__ __forceinline__ void ds_load8(const uint16_t* p, int c, uint16_t (&h)
 }
 
 constexpr int kDsStageIters = 2;                            // 8-element chunks per thread held in registers
-constexpr int kDsMaxStageK = kDsStageIters * kDsThreads * 8;  // 8192: largest K of a 16-bit staged vector
+constexpr int kDsMaxStageK = kDsStageIters * kDsThreads * 8;  // 8192: largest K of a vector that is RMS-normalised
 
-// RMSNorm of x (K values, f16) in the library's fixed order, then int8 codes (PLANES 1) or 16-bit fixed-point
-// planes (PLANES 2, after the optional awq multiply).  NORM = false: no normalisation (x is staged as it is).
-// The vector is read once: every thread keeps its chunks in registers for the second pass and leaves a copy in
-// `stash` so that the first 256 threads can take the sum of squares in the stand-alone kernel's order.
-template <int PLANES, bool NORM>
-__device__ __forceinline__ void ds_stage_f16(const uint16_t* x, const uint16_t* norm_w, float eps, const float* awq, int K,
-                                             Smem<PLANES>& sm, float* warp_part, uint4* stash) {
+// RMSNorm of x (K <= kDsMaxStageK values, f16) in the library's fixed order, then int8 codes (PLANES 1) or 16-bit
+// fixed-point planes (PLANES 2, after the optional awq multiply).  The vector is read once: every thread keeps its
+// chunks in registers for the second pass and leaves a copy in `stash` so that the first 256 threads can take the
+// sum of squares in the stand-alone kernel's order.
+template <int PLANES>
+__device__ __forceinline__ void ds_stage_norm(const uint16_t* x, const uint16_t* norm_w, float eps, const float* awq, int K,
+                                              Smem<PLANES>& sm, float* warp_part, uint4* stash) {
     ds_zero_padding<PLANES>(K / kBlockK, sm);
     const int chunks = K >> 3;
     const int iters = (chunks + kDsThreads - 1) / kDsThreads;  // <= kDsStageIters (checked by the launcher)
@@ -291,39 +398,32 @@ __device__ __forceinline__ void ds_stage_f16(const uint16_t* x, const uint16_t* 
         wr[it] = make_uint4(0, 0, 0, 0);
         if (it < iters && c < chunks) {
             xr[it] = __ldcg(reinterpret_cast<const uint4*>(x) + c);
-            if constexpr (NORM) wr[it] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);
+            wr[it] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c);
+            stash[c] = xr[it];
         }
     }
-    float r = 1.0f;
-    if constexpr (NORM) {
+    __syncthreads();
+    // sum of squares: thread t < 256 adds the chunks t, t+256, ... (fma chain, ascending), xor butterfly per warp,
+    // the 8 warp sums in ascending order -- the order of the stand-alone RMSNorm kernel
+    float acc = 0.0f;
+    if (threadIdx.x < kGemvThreads) {
+        for (int c = threadIdx.x; c < chunks; c += kGemvThreads) {
+            uint16_t h[8];
+            unpack8(stash[c], h);
 #pragma unroll
-        for (int it = 0; it < kDsStageIters; it++) {
-            const int c = it * kDsThreads + threadIdx.x;
-            if (it < iters && c < chunks) stash[c] = xr[it];
-        }
-        __syncthreads();
-        // sum of squares: thread t < 256 adds the chunks t, t+256, ... (fma chain, ascending), xor butterfly per
-        // warp, the 8 warp sums in ascending order -- the order of the stand-alone RMSNorm kernel
-        float acc = 0.0f;
-        if (threadIdx.x < kGemvThreads) {
-            for (int c = threadIdx.x; c < chunks; c += kGemvThreads) {
-                uint16_t h[8];
-                unpack8(stash[c], h);
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float v = Act16<NVE_DT_F16>::to_f32(h[e]);
-                    acc = __fmaf_rn(v, v, acc);
-                }
+            for (int e = 0; e < 8; e++) {
+                const float v = Act16<NVE_DT_F16>::to_f32(h[e]);
+                acc = __fmaf_rn(v, v, acc);
             }
         }
-        acc = warp_sum(acc);
-        if (threadIdx.x < kGemvThreads && (threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
-        __syncthreads();
-        float total = warp_part[0];
-#pragma unroll
-        for (int w = 1; w < kGemvThreads / 32; w++) total = __fadd_rn(total, warp_part[w]);
-        r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(K)), eps)));
     }
+    acc = warp_sum(acc);
+    if (threadIdx.x < kGemvThreads && (threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    float total = warp_part[0];
+#pragma unroll
+    for (int w = 1; w < kGemvThreads / 32; w++) total = __fadd_rn(total, warp_part[w]);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(K)), eps)));
 #pragma unroll
     for (int it = 0; it < kDsStageIters; it++) {
         if (it < iters) {  // uniform over the CTA: the quad shuffles inside stage_chunk_* need whole warps
@@ -331,19 +431,13 @@ __device__ __forceinline__ void ds_stage_f16(const uint16_t* x, const uint16_t* 
             const bool active = c < chunks;
             float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (active) {
-                uint16_t h[8];
+                uint16_t h[8], hw[8];
                 unpack8(xr[it], h);
-                if constexpr (NORM) {
-                    uint16_t hw[8];
-                    unpack8(wr[it], hw);
+                unpack8(wr[it], hw);
 #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        const float o = __fmul_rn(__fmul_rn(Act16<NVE_DT_F16>::to_f32(h[e]), r), Act16<NVE_DT_F16>::to_f32(hw[e]));
-                        v[e] = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(o));
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) v[e] = Act16<NVE_DT_F16>::to_f32(h[e]);
+                for (int e = 0; e < 8; e++) {
+                    const float o = __fmul_rn(__fmul_rn(Act16<NVE_DT_F16>::to_f32(h[e]), r), Act16<NVE_DT_F16>::to_f32(hw[e]));
+                    v[e] = Act16<NVE_DT_F16>::to_f32(Act16<NVE_DT_F16>::from_f32(o));
                 }
                 if constexpr (PLANES == 2) {
                     if (awq != nullptr) {
@@ -358,94 +452,55 @@ __device__ __forceinline__ void ds_stage_f16(const uint16_t* x, const uint16_t* 
     }
 }
 
-// int8 codes + scales written by an earlier phase (W4A8 o_proj / down_proj input).
-__device__ __forceinline__ void ds_stage_q8(const int8_t* xq, const float* xs, int K, Smem<1>& sm) {
-    const int nb = K / kBlockK;
-    ds_zero_padding<1>(nb, sm);
-    for (int b = threadIdx.x; b < nb; b += kDsThreads) {
-        const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<long long>(b) * 32);
-        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);
-        int sum = 0;
-        sum = __dp4a((int)lo.x, 0x01010101, sum); sum = __dp4a((int)lo.y, 0x01010101, sum);
-        sum = __dp4a((int)lo.z, 0x01010101, sum); sum = __dp4a((int)lo.w, 0x01010101, sum);
-        sum = __dp4a((int)hi.x, 0x01010101, sum); sum = __dp4a((int)hi.y, 0x01010101, sum);
-        sum = __dp4a((int)hi.z, 0x01010101, sum); sum = __dp4a((int)hi.w, 0x01010101, sum);
-        sm.plane[b] = lo;
-        sm.plane[sm.nbp + b] = hi;
-        sm.xs[b] = __ldcg(xs + b);
-        sm.bias[b] = 8 * sum;
-    }
-}
-
-// 16-bit fixed-point planes written by the SiLU phase (W4A16 down_proj input).
-__device__ __forceinline__ void ds_stage_x16_planes(const uint8_t* xlo, const int8_t* xhi, const float* xs, int K,
-                                                    Smem<2>& sm) {
-    const int nb = K / kBlockK;
-    ds_zero_padding<2>(nb, sm);
-    for (int b = threadIdx.x; b < nb; b += kDsThreads) {
-        const uint4* lo = reinterpret_cast<const uint4*>(xlo + static_cast<long long>(b) * 32);
-        const uint4* hi = reinterpret_cast<const uint4*>(xhi + static_cast<long long>(b) * 32);
-        const uint4 l0 = __ldcg(lo), l1 = __ldcg(lo + 1), h0 = __ldcg(hi), h1 = __ldcg(hi + 1);
-        int ul = 0, sh = 0;
-        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-        const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+// A 16-bit vector written by an earlier phase (attention output, SiLU*up) -> int8 codes (PLANES 1, the arithmetic of
+// the stand-alone quantiser) or fixed-point planes (PLANES 2, after the optional awq multiply).  Any K.
+template <int PLANES>
+__device__ __forceinline__ void ds_stage_vec(const uint16_t* x, const float* awq, int K, Smem<PLANES>& sm) {
+    ds_zero_padding<PLANES>(K / kBlockK, sm);
+    const int chunks = K >> 3;
+    const int iters = (chunks + kDsThreads - 1) / kDsThreads;
+    for (int it0 = 0; it0 < iters; it0 += 4) {
+        uint4 xr[4];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            ul = dp4a_uu(lw[j], 0x01010101u, ul);
-            sh = __dp4a(static_cast<int>(hw[j]), 0x01010101, sh);
+        for (int j = 0; j < 4; j++) {  // up to four L2 loads in flight per thread
+            const int c = (it0 + j) * kDsThreads + threadIdx.x;
+            xr[j] = make_uint4(0, 0, 0, 0);
+            if (it0 + j < iters && c < chunks) xr[j] = __ldcg(reinterpret_cast<const uint4*>(x) + c);
         }
-        sm.plane[0 * sm.nbp + b] = l0;
-        sm.plane[1 * sm.nbp + b] = l1;
-        sm.plane[2 * sm.nbp + b] = h0;
-        sm.plane[3 * sm.nbp + b] = h1;
-        sm.xs[b] = __ldcg(xs + b);
-        sm.bias[b] = 8 * (sh * 256 + ul);
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// SiLU*up -> int8 codes (W4A8) or fixed-point planes (W4A16), spread over the grid one warp (32 chunks) at a time
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void ds_silu_phase(const DsParams& p, const nve_b200_decode_layer& ly, int warp, int lane) {
-    const int n = p.m.ffn;
-    const int chunks = n >> 3;
-    const int warp_chunks = (chunks + 31) / 32;
-    const float* awq = ly.awq[3];
-    for (int j = warp * gridDim.x + blockIdx.x; j < warp_chunks; j += kDsWarps * gridDim.x) {
-        const int c = j * 32 + lane;
-        const bool active = c < chunks;
-        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (active) {
-            uint16_t hg[8], hu[8];
-            ds_load8(p.w.gate, c, hg);
-            ds_load8(p.w.up, c, hu);
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const uint16_t ho = Act16<NVE_DT_F16>::from_f32(
-                    silu_mul_f32(Act16<NVE_DT_F16>::to_f32(hg[e]), Act16<NVE_DT_F16>::to_f32(hu[e])));
-                v[e] = Act16<NVE_DT_F16>::to_f32(ho);
+        for (int j = 0; j < 4; j++) {
+            if (it0 + j < iters) {
+                const int c = (it0 + j) * kDsThreads + threadIdx.x;
+                const bool active = c < chunks;
+                float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (active) {
+                    uint16_t h[8];
+                    unpack8(xr[j], h);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) v[e] = Act16<NVE_DT_F16>::to_f32(h[e]);
+                    if constexpr (PLANES == 2) {
+                        if (awq != nullptr) {
+#pragma unroll
+                            for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], __ldg(awq + c * 8 + e));
+                        }
+                    }
+                }
+                if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);
+                else stage_chunk_x16(sm, c, v, active);
             }
         }
-        if (ly.use_w4a8) {
-            quantize_quad(v, p.w.xq_f, p.w.xs_f, c, active);
-        } else {
-            if (active && awq != nullptr) {
-#pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], __ldg(awq + c * 8 + e));
-            }
-            x16_quad(v, p.w.xlo_f, p.w.xq_f, p.w.xs_f, c, active);
-        }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Attention: partial pass (RoPE + KV write + per-slice online softmax) and the merge of the slices
+// Attention phase: RoPE + KV write + per-slice online softmax; the CTA that completes the last slice of a pair of
+// head pairs merges the slices (level 2), so no device-wide barrier separates the two steps.
 // ---------------------------------------------------------------------------------------------
 // A CTA runs two virtual CTAs of 256 threads side by side: the two query-head pairs 2u, 2u+1 on the same position
 // slice (for the usual group size 4 they share the KV head, so the second reader hits L1/L2).
 template <int HD>
-__device__ __forceinline__ void ds_attn_partial(const DsParams& p, const nve_b200_decode_layer& ly, unsigned char* smem_raw,
-                                                int seq_len, int pos) {
+__device__ __forceinline__ void ds_attn_phase(const DsParams& p, const nve_b200_decode_layer& ly, unsigned char* smem_raw,
+                                              int seq_len, int pos, int* last_flag) {
     constexpr int QH = 2;
     constexpr int DC = HD / 8;
     AdShared<HD, QH>* shs = reinterpret_cast<AdShared<HD, QH>*>(smem_raw);
@@ -453,20 +508,21 @@ __device__ __forceinline__ void ds_attn_partial(const DsParams& p, const nve_b20
     AdShared<HD, QH>& sh = shs[half];
     const int groups = p.m.num_heads / p.m.num_kv_heads;
     const int clusters_per_kv = groups / QH;
-    const int nvc = p.m.num_heads / QH;  // virtual clusters
+    const int nvc = p.m.num_heads / QH;  // virtual clusters (head pairs)
     const int units = ((nvc + 1) / 2) * kAdRanks;
     const bool pos_ok = pos >= 0 && pos < p.m.max_seq;
     const int chunk = (seq_len + kAdRanks - 1) / kAdRanks;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
         const int rank = u % kAdRanks;
-        const int vc = (u / kAdRanks) * 2 + half;
+        const int pair = u / kAdRanks;
+        const int vc = pair * 2 + half;
         const bool live = vc < nvc;
-        const int vcc = live ? vc : nvc - 1;  // an idle half repeats the last cluster's work and discards it
+        const int vcc = live ? vc : nvc - 1;  // an idle half repeats the last head pair's work and discards it
         const int kvh = vcc / clusters_per_kv;
         const int h0 = kvh * groups + (vcc % clusters_per_kv) * QH;
         const uint16_t* kh = ly.k_cache + static_cast<long long>(kvh) * p.m.max_seq * HD;
         const uint16_t* vh = ly.v_cache + static_cast<long long>(kvh) * p.m.max_seq * HD;
-        attn_stage_q<HD, QH, true>(sh, tid, p.w.q, p.w.k, p.w.v, p.m.rope_cos, p.m.rope_sin, h0, kvh, pos, pos_ok);
+        attn_stage_q<HD, QH, true, true>(sh, tid, p.w.q, p.w.k, p.w.v, p.m.rope_cos, p.m.rope_sin, h0, kvh, pos, pos_ok);
         __syncthreads();
         const int t_begin = rank * chunk;
         const int t_end = min(seq_len, t_begin + chunk);
@@ -475,50 +531,46 @@ __device__ __forceinline__ void ds_attn_partial(const DsParams& p, const nve_b20
             uint16_t* dst = (which == 0 ? ly.k_cache : ly.v_cache) + (static_cast<long long>(kvh) * p.m.max_seq + pos) * HD;
             reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
         }
-        AdCtaPartial<HD, QH>* dst = static_cast<AdCtaPartial<HD, QH>*>(p.w.parts) + (static_cast<long long>(vcc) * kAdRanks + rank);
+        AdCtaPartial<HD, QH>* parts = static_cast<AdCtaPartial<HD, QH>*>(p.w.parts);
+        AdCtaPartial<HD, QH>* dst = parts + (static_cast<long long>(vcc) * kAdRanks + rank);
         attn_partial<HD, QH, true, false>(
             sh, tid, kh, vh, t_begin, t_end, pos, p.m.attn_scale, false, nullptr, [] { __syncthreads(); },
             [&](int h, int d, float mm, float ss, float a) {
                 if (live) {
-                    dst->acc[h][d] = a;
-                    if (d == 0) { dst->m[h] = mm; dst->s[h] = ss; }
+                    __stcg(&dst->acc[h][d], a);
+                    if (d == 0) { __stcg(&dst->m[h], mm); __stcg(&dst->s[h], ss); }
                 }
             });
-        __syncthreads();  // shared memory is reused by the next unit
-    }
-}
-
-template <int HD>
-__device__ __forceinline__ void ds_attn_merge(const DsParams& p, const nve_b200_decode_layer& ly) {
-    constexpr int QH = 2;
-    const int nvc = p.m.num_heads / QH;
-    const int groups = p.m.num_heads / p.m.num_kv_heads;
-    const int clusters_per_kv = groups / QH;
-    for (int vc = blockIdx.x; vc < nvc; vc += gridDim.x) {
-        const int kvh = vc / clusters_per_kv;
-        const int h0 = kvh * groups + (vc % clusters_per_kv) * QH;
-        const AdCtaPartial<HD, QH>* parts = static_cast<const AdCtaPartial<HD, QH>*>(p.w.parts) + static_cast<long long>(vc) * kAdRanks;
-        for (int i = threadIdx.x; i < QH * HD; i += kDsThreads) {
-            const int h = i / HD, d = i % HD;
-            const uint16_t o16 = attn_merge_ranks<HD, QH>(parts, h, d);
-            const long long oi = static_cast<long long>(h0 + h) * HD + d;
-            p.w.attn[oi] = o16;
-            if (ly.use_w4a8) {
-                float scale;
-                const int qv = attn_quantize_lane(o16, scale);
-                p.w.xq_a[oi] = static_cast<int8_t>(qv);
-                if ((threadIdx.x & 31) == 0) p.w.xs_a[oi >> 5] = scale;
+        // ---- count this slice; whoever completes the pair's last slice merges all of them
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const int old = atomicAdd(p.w.attn_cnt + pair, 1);
+            const int last = old == kAdRanks - 1;
+            if (last) {
+                p.w.attn_cnt[pair] = 0;  // ready for the next layer (a device-wide barrier comes first)
+                __threadfence();
+            }
+            *last_flag = last;
+        }
+        __syncthreads();
+        if (*last_flag && live) {
+            for (int i = tid; i < QH * HD; i += kAdThreads) {
+                const int h = i / HD, d = i % HD;
+                const uint16_t o16 = attn_merge_ranks<HD, QH, true>(parts + static_cast<long long>(vcc) * kAdRanks, h, d);
+                p.w.attn[static_cast<long long>(h0 + h) * HD + d] = o16;
             }
         }
+        __syncthreads();  // shared memory (and the flag) are reused by the next unit
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Phase table
 // ---------------------------------------------------------------------------------------------
-enum { kPhQkv = 0, kPhAttn = 1, kPhMerge = 2, kPhO = 3, kPhGateUp = 4, kPhSilu = 5, kPhDown = 6, kPhPerLayer = 7 };
+enum { kPhQkv = 0, kPhAttn = 1, kPhO = 2, kPhGateUp = 3, kPhDown = 4, kPhPerLayer = 5 };
 
-__device__ __forceinline__ bool ph_is_gemv(int kind) { return kind == kPhQkv || kind == kPhO || kind == kPhGateUp || kind == kPhDown; }
+__device__ __forceinline__ bool ph_is_gemv(int kind) { return kind != kPhAttn; }
 
 // Matrices of GEMV phase `kind` of layer `ly` (kind < 0: the lm_head).
 __device__ __forceinline__ void pm_set(PhaseMats& pm, int m, const nve_b200_decode_layer* ly, int proj, void* out, int row_end) {
@@ -532,6 +584,7 @@ __device__ __forceinline__ void pm_build(const DsParams& p, const nve_b200_decod
     const int qd = p.m.num_heads * p.m.head_dim, kvd = p.m.num_kv_heads * p.m.head_dim;
     int K = p.m.hidden;
     pm.epi = kEpiF16;
+    pm.paired = 0;
     if (kind < 0) {
         pm.nib[0] = pm.nib[1] = pm.nib[2] = p.m.lm_nibbles;
         pm.sc[0] = pm.sc[1] = pm.sc[2] = p.m.lm_scales;
@@ -545,9 +598,11 @@ __device__ __forceinline__ void pm_build(const DsParams& p, const nve_b200_decod
             pm_set(pm, 1, ly, 1, p.w.k, qd + kvd);
             pm_set(pm, 2, ly, 2, p.w.v, qd + 2 * kvd);
         } else if (kind == kPhGateUp) {
-            pm_set(pm, 0, ly, 4, p.w.gate, p.m.ffn);
-            pm_set(pm, 1, ly, 5, p.w.up, 2 * p.m.ffn);
-            pm_set(pm, 2, ly, 5, p.w.up, 2 * p.m.ffn);
+            pm_set(pm, 0, ly, 4, p.w.mid, p.m.ffn);
+            pm_set(pm, 1, ly, 5, p.w.mid, 2 * p.m.ffn);
+            pm_set(pm, 2, ly, 5, p.w.mid, 2 * p.m.ffn);
+            pm.paired = 1;
+            pm.epi = kEpiSiluMul;
         } else {
             const int proj = kind == kPhO ? 3 : 6;
             K = kind == kPhO ? qd : p.m.ffn;
@@ -562,97 +617,18 @@ __device__ __forceinline__ void pm_build(const DsParams& p, const nve_b200_decod
     pm.K = K;
     pm.nb = K / kBlockK;
     pm.S = (pm.nb + kWarp - 1) / kWarp;
+    pm_set_cta_tiles(pm);
 }
 
-// ---------------------------------------------------------------------------------------------
-// L2 prefetch stream: the GEMV phases in execution order form one byte stream; at the start of GEMV phase g every
-// CTA makes sure that its own share of the stream up to `pf_bytes` beyond the end of phase g has been requested.
-// A phase is cut into kPfSlabs slabs of each CTA's tile range; all CTAs advance the same (uniform) frontier.
-// ---------------------------------------------------------------------------------------------
-constexpr int kPfSlabs = 8;
-
-struct PfState {
-    int s;            // frontier: global slab index (GEMV index * kPfSlabs + slab)
-    long long ahead;  // bytes of the stream requested beyond the end of the phase that is running
-};
-
-__device__ __forceinline__ long long pm_bytes(const PhaseMats& pm) {
-    return static_cast<long long>(pm.n_total) * pm.nb * 20;  // 16 nibble bytes + one f32 scale per block
-}
-
-// Bytes of GEMV phase g (uniform arithmetic on the model's dimensions).
-__device__ __forceinline__ long long pf_phase_bytes(const DsParams& p, int g) {
-    const long long qd = static_cast<long long>(p.m.num_heads) * p.m.head_dim, kvd = static_cast<long long>(p.m.num_kv_heads) * p.m.head_dim;
-    const long long H = p.m.hidden, F = p.m.ffn;
-    if (g >= p.m.num_layers * 4) return static_cast<long long>(p.m.vocab) * H / 32 * 20;
-    switch (g & 3) {
-        case 0: return (qd + 2 * kvd) * H / 32 * 20;
-        case 1: return H * qd / 32 * 20;
-        case 2: return 2 * F * H / 32 * 20;
-        default: return H * F / 32 * 20;
+// Matrices of GEMV phase g in execution order (four per layer, then the lm_head).
+__device__ __forceinline__ void ds_build_gemv(const DsParams& p, int g, PhaseMats& pm) {
+    const int layer = g >> 2;
+    if (layer < p.m.num_layers) {
+        const int kind = (g & 3) == 0 ? kPhQkv : ((g & 3) == 1 ? kPhO : ((g & 3) == 2 ? kPhGateUp : kPhDown));
+        pm_build(p, p.layers + layer, kind, pm);
+    } else {
+        pm_build(p, nullptr, -1, pm);
     }
-}
-
-__device__ __forceinline__ void pf_issue_slab(const PhaseMats& pm, int slab) {
-    int tb, te;
-    pm_cta_tiles(pm, tb, te);
-    const int R = pm_rows_per_tile(pm);
-    const int t0 = tb + static_cast<int>(static_cast<long long>(te - tb) * slab / kPfSlabs);
-    const int t1 = tb + static_cast<int>(static_cast<long long>(te - tb) * (slab + 1) / kPfSlabs);
-    const int r0 = t0 * R, r1 = min(t1 * R, pm.n_total);
-    int mat_begin = 0;
-#pragma unroll
-    for (int m = 0; m < 3; m++) {
-        const int mat_end = pm.row_end[m];
-        const int a = max(r0, mat_begin), b = min(r1, mat_end);
-        if (a < b) {
-            const long long row0 = a - mat_begin, rows = b - a;
-            const unsigned char* nb0 = pm.nib[m] + row0 * pm.nb * 16;
-            l2_prefetch_bulk(nb0, static_cast<unsigned>(rows * pm.nb * 16));
-            // scale rows are nb*4 bytes: round the range inwards to 16-byte boundaries
-            const uintptr_t s0 = reinterpret_cast<uintptr_t>(pm.sc[m] + row0 * pm.nb);
-            const uintptr_t s1 = s0 + static_cast<uintptr_t>(rows) * pm.nb * 4;
-            const uintptr_t sa = (s0 + 15) & ~static_cast<uintptr_t>(15), sb = s1 & ~static_cast<uintptr_t>(15);
-            if (sb > sa) l2_prefetch_bulk(reinterpret_cast<const void*>(sa), static_cast<unsigned>(sb - sa));
-        }
-        mat_begin = mat_end;
-    }
-}
-
-// Called by one whole warp per CTA when GEMV phase g starts: the (uniform) frontier moves until `pf_bytes` of the
-// stream beyond the end of phase g have been requested; the lanes issue the new slabs side by side.
-__device__ __forceinline__ void pf_advance(const DsParams& p, PfState& pf, int g, int total_gemvs, int lane) {
-    if (p.pf_bytes <= 0) return;
-    if (pf.s < (g + 1) * kPfSlabs) {  // the frontier fell behind the running phase: restart right after it
-        pf.s = (g + 1) * kPfSlabs;
-        pf.ahead = 0;
-    }
-    const int s_begin = pf.s;
-    while (pf.s < total_gemvs * kPfSlabs && pf.ahead < p.pf_bytes) {
-        pf.ahead += pf_phase_bytes(p, pf.s / kPfSlabs) / kPfSlabs;
-        pf.s++;
-    }
-    for (int s = s_begin + lane; s < pf.s; s += 32) {
-        const int fg = s / kPfSlabs;
-        PhaseMats pm;
-        const int layer = fg / 4;
-        if (layer < p.m.num_layers) {
-            const int kind = (fg & 3) == 0 ? kPhQkv : ((fg & 3) == 1 ? kPhO : ((fg & 3) == 2 ? kPhGateUp : kPhDown));
-            pm_build(p, p.layers + layer, kind, pm);
-        } else {
-            pm_build(p, nullptr, -1, pm);
-        }
-        pf_issue_slab(pm, s % kPfSlabs);
-    }
-}
-
-// When phase g_next - 1 ends, the requested bytes of phase g_next stop counting as "ahead".
-__device__ __forceinline__ void pf_retire(const DsParams& p, PfState& pf, int g_next) {
-    const long long nb = pf_phase_bytes(p, g_next);
-    const int done = pf.s - g_next * kPfSlabs;  // slabs of phase g_next already requested
-    if (done >= kPfSlabs) pf.ahead -= nb;
-    else if (done > 0) pf.ahead -= nb / kPfSlabs * done;
-    if (pf.ahead < 0) pf.ahead = 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -664,6 +640,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     __shared__ float warp_part[kGemvThreads / 32];
     __shared__ uint4 stash[kDsMaxStageK / 8];
     __shared__ unsigned long long bar_base_s;
+    __shared__ int last_flag_s;
+    __shared__ PhaseMats pms[kPmSlots];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 
@@ -680,12 +658,17 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
     const int total_phases = layer_phases + (has_head ? 1 : 0);
     const int total_gemvs = p.m.num_layers * 4 + (has_head ? 1 : 0);
 
-    PfState pf = {0, 0};
-    PhaseMats pm;
-    WFlat item;
-    pm_build(p, p.layers, kPhQkv, pm);
-    pm_load_first(pm, warp, lane, item);
+    // The matrices of GEMV phase g live in pms[g % kPmSlots]; thread 0 publishes phase g + kPmSlots - 1 while phase g
+    // is staged, so the prefetch walk can look kPmSlots - 1 phases ahead.
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kPmSlots - 1 && i < total_gemvs; i++) ds_build_gemv(p, i, pms[i]);
+    }
+    __syncthreads();
     int g = 0;  // index of the next GEMV phase
+    const int dist = p.pf_items;
+    WFlat item;
+    pm_load_first(pms[0], warp, lane, item);
+    if (dist > 0) pf_head(pms[0], dist + 1, warp, lane);
 
     for (int ph = 0; ph < total_phases; ph++) {
         const int layer = ph / kPhPerLayer;
@@ -696,62 +679,82 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_step_kernel(const DsPara
         if (tracer) tr[0] = ds_globaltimer();
         if (ph > 0) grid_barrier(p, bar_target);
         if (tracer) tr[1] = ds_globaltimer();
-        if (kind < 0 || ph_is_gemv(kind)) {
+        if (kind != kPhAttn) {
+            const PhaseMats& pm = pms[g % kPmSlots];
+            if (threadIdx.x == 0 && g + kPmSlots - 1 < total_gemvs) ds_build_gemv(p, g + kPmSlots - 1, pms[(g + kPmSlots - 1) % kPmSlots]);
+            // ---- small read-only data that a later phase waits for goes to L2 now: the RMSNorm weight of the next
+            // normalising phase (cold in L2 by the time its layer comes round), this CTA's K/V slice of the attention
+            if (threadIdx.x == 32) {
+                const unsigned nbytes = static_cast<unsigned>(p.m.hidden) * 2u;
+                if (kind == kPhQkv && static_cast<int>(blockIdx.x) == (layer + 1) % static_cast<int>(gridDim.x))
+                    l2_prefetch_bulk(ly->post_attn_norm, nbytes);
+                if (kind == kPhGateUp && static_cast<int>(blockIdx.x) == (layer + 2) % static_cast<int>(gridDim.x)) {
+                    if (layer + 1 < p.m.num_layers) l2_prefetch_bulk((ly + 1)->input_norm, nbytes);
+                    else if (has_head) l2_prefetch_bulk(p.m.final_norm, nbytes);
+                }
+            }
+            if (kind == kPhQkv && threadIdx.x >= 64 && threadIdx.x < 66) {
+                const int groups = p.m.num_heads / p.m.num_kv_heads;
+                const int nvc = p.m.num_heads / 2;
+                const int units = ((nvc + 1) / 2) * kAdRanks;
+                const int chunk = (seq_len + kAdRanks - 1) / kAdRanks;
+                for (int u = blockIdx.x; u < units; u += gridDim.x) {
+                    const int rank = u % kAdRanks;
+                    const int vc = min((u / kAdRanks) * 2, nvc - 1);
+                    const int kvh = vc / (groups / 2);
+                    const int t0 = rank * chunk, t1 = min(seq_len, t0 + chunk);
+                    if (t1 > t0) {
+                        const uint16_t* base = (threadIdx.x == 64 ? ly->k_cache : ly->v_cache) +
+                                               (static_cast<long long>(kvh) * p.m.max_seq + t0) * HD;
+                        l2_prefetch_bulk(base, static_cast<unsigned>(t1 - t0) * HD * 2u);
+                    }
+                }
+            }
             // ---- stage the activation vector of the phase once for this SM
             const uint16_t* residual = nullptr;
+            const int planes = kind < 0 ? (p.m.lm_use_w4a8 ? 1 : 2) : (ly->use_w4a8 ? 1 : 2);
+            const int K = kind == kPhO ? p.m.num_heads * p.m.head_dim : (kind == kPhDown ? p.m.ffn : p.m.hidden);
+            const int nbp = ((K / kBlockK + kWarp - 1) / kWarp) * kWarp;
             if (kind == kPhQkv || kind == kPhGateUp || kind < 0) {
                 const uint16_t* nw = kind == kPhQkv ? ly->input_norm : (kind == kPhGateUp ? ly->post_attn_norm : p.m.final_norm);
                 const float* awq = kind < 0 ? nullptr : ly->awq[kind == kPhQkv ? 0 : 2];
-                if (pm.planes == 1) {
-                    Smem<1> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_f16<1, true>(p.hidden, nw, p.m.norm_eps, nullptr, pm.K, sm, warp_part, stash);
+                if (planes == 1) {
+                    Smem<1> sm(smem_raw, nbp);
+                    ds_stage_norm<1>(p.hidden, nw, p.m.norm_eps, nullptr, K, sm, warp_part, stash);
                 } else {
-                    Smem<2> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_f16<2, true>(p.hidden, nw, p.m.norm_eps, awq, pm.K, sm, warp_part, stash);
+                    Smem<2> sm(smem_raw, nbp);
+                    ds_stage_norm<2>(p.hidden, nw, p.m.norm_eps, awq, K, sm, warp_part, stash);
                 }
-            } else if (kind == kPhO) {
+            } else {
                 residual = p.hidden;
-                if (pm.planes == 1) {
-                    Smem<1> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_q8(p.w.xq_a, p.w.xs_a, pm.K, sm);
+                const uint16_t* x = kind == kPhO ? p.w.attn : p.w.mid;
+                if (planes == 1) {
+                    Smem<1> sm(smem_raw, nbp);
+                    ds_stage_vec<1>(x, nullptr, K, sm);
                 } else {
-                    Smem<2> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_f16<2, false>(p.w.attn, nullptr, 0.0f, ly->awq[1], pm.K, sm, warp_part, stash);
-                }
-            } else {  // down_proj
-                residual = p.hidden;
-                if (pm.planes == 1) {
-                    Smem<1> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_q8(p.w.xq_f, p.w.xs_f, pm.K, sm);
-                } else {
-                    Smem<2> sm(smem_raw, pm.S * kWarp);
-                    ds_stage_x16_planes(p.w.xlo_f, p.w.xq_f, p.w.xs_f, pm.K, sm);
+                    Smem<2> sm(smem_raw, nbp);
+                    ds_stage_vec<2>(x, ly->awq[kind == kPhO ? 1 : 3], K, sm);
                 }
             }
             __syncthreads();
             if (tracer) tr[2] = ds_globaltimer();
-            if (warp == kDsWarps - 1) pf_advance(p, pf, g, total_gemvs, lane);
-            if (pm.planes == 1) ds_run_gemv_rc<1>(pm, smem_raw, residual, warp, lane, item);
-            else ds_run_gemv_rc<2>(pm, smem_raw, residual, warp, lane, item);
+            if (planes == 1) ds_run_gemv_rc<1>(pm, smem_raw, residual, warp, lane, item, dist);
+            else ds_run_gemv_rc<2>(pm, smem_raw, residual, warp, lane, item, dist);
             g++;
-        } else if (kind == kPhAttn) {
-            ds_attn_partial<HD>(p, *ly, smem_raw, seq_len, pos);
-        } else if (kind == kPhMerge) {
-            ds_attn_merge<HD>(p, *ly);
-        } else {  // kPhSilu
-            ds_silu_phase(p, *ly, warp, lane);
+            // this warp is done with the phase: the head of the next GEMV phase (and of the one after it when the
+            // next one is short) is asked for now, to arrive while the CTA waits and stages
+            if (dist > 0 && g < total_gemvs) {
+                pf_head(pms[g % kPmSlots], dist + 1, warp, lane);
+                if (g + 1 < total_gemvs && (g & 3) == 1) pf_head(pms[(g + 1) % kPmSlots], dist, warp, lane);
+            }
+        } else {
+            ds_attn_phase<HD>(p, *ly, smem_raw, seq_len, pos, &last_flag_s);
         }
         if (tracer) tr[3] = ds_globaltimer();
         // ---- the next GEMV phase's first weight item goes in flight before the barrier in front of it
         const int nph = ph + 1;
-        if (nph < total_phases) {
-            const int nkind = nph < layer_phases ? nph % kPhPerLayer : -1;
-            if (nkind < 0 || ph_is_gemv(nkind)) {
-                pm_build(p, nkind < 0 ? nullptr : p.layers + nph / kPhPerLayer, nkind, pm);
-                pm_load_first(pm, warp, lane, item);
-                pf_retire(p, pf, g);
-            }
-        }
+        if (nph < total_phases && (nph >= layer_phases || nph % kPhPerLayer != kPhAttn))
+            pm_load_first(pms[g % kPmSlots], warp, lane, item);
     }
 }
 
@@ -764,9 +767,11 @@ __global__ void decode_step_wait_probe_kernel(DsParams p) {
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
+// Head of the workspace that must start at zero: barrier counter (+0), error word (+256), slice counters (+512).
+constexpr size_t kDsControlBytes = 4096;
+
 struct DsLayout {
-    size_t off_bar, off_err, off_q, off_k, off_v, off_parts, off_attn, off_xq_a, off_xs_a, off_gate, off_up, off_xq_f,
-        off_xlo_f, off_xs_f, total;
+    size_t off_bar, off_err, off_cnt, off_q, off_k, off_v, off_parts, off_attn, off_mid, total;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -782,19 +787,14 @@ static DsLayout ds_layout(const nve_b200_decode_model& m) {
     const size_t qd = static_cast<size_t>(m.num_heads) * m.head_dim, kvd = static_cast<size_t>(m.num_kv_heads) * m.head_dim;
     l.off_bar = take(8);
     l.off_err = take(4);
+    l.off_cnt = take(kDsControlBytes - 512);  // one int per pair of head pairs
     l.off_q = take(qd * 2);
     l.off_k = take(kvd * 2);
     l.off_v = take(kvd * 2);
     const size_t part = (2 + 2 + 2 * static_cast<size_t>(m.head_dim)) * sizeof(float);  // AdCtaPartial<hd, 2>
     l.off_parts = take(static_cast<size_t>(m.num_heads / 2) * kAdRanks * part);
     l.off_attn = take(qd * 2);
-    l.off_xq_a = take(qd);
-    l.off_xs_a = take(qd / 32 * 4);
-    l.off_gate = take(static_cast<size_t>(m.ffn) * 2);
-    l.off_up = take(static_cast<size_t>(m.ffn) * 2);
-    l.off_xq_f = take(m.ffn);
-    l.off_xlo_f = take(m.ffn);
-    l.off_xs_f = take(static_cast<size_t>(m.ffn) / 32 * 4);
+    l.off_mid = take(static_cast<size_t>(m.ffn) * 2);
     l.total = o;
     return l;
 }
@@ -803,6 +803,7 @@ static int ds_check_model(const nve_b200_decode_model& m) {
     if (m.hidden <= 0 || m.ffn <= 0 || m.num_heads <= 0 || m.num_kv_heads <= 0 || m.num_layers <= 0 || m.max_seq <= 0)
         return NVE_ERR_BAD_SHAPE;
     if (m.head_dim != 64 && m.head_dim != 128) return NVE_ERR_BAD_SHAPE;
+    if (static_cast<size_t>(m.num_heads) * sizeof(int) > kDsControlBytes - 512) return NVE_ERR_TOO_LARGE;
     if ((m.num_heads % m.num_kv_heads) != 0 || ((m.num_heads / m.num_kv_heads) % 2) != 0) return NVE_ERR_BAD_SHAPE;
     if ((m.hidden % 32) != 0 || (m.ffn % 32) != 0) return NVE_ERR_BAD_SHAPE;
     if (((m.num_heads * m.head_dim) % 8) != 0 || ((m.num_kv_heads * m.head_dim) % 8) != 0 || (m.ffn % 8) != 0 || (m.hidden % 8) != 0)
@@ -813,33 +814,30 @@ static int ds_check_model(const nve_b200_decode_model& m) {
     return NVE_OK;
 }
 
-static size_t ds_smem_bytes(const nve_b200_decode_model& m) {
+// Dynamic shared memory: activation planes of a GEMV phase or the attention state.
+static size_t ds_front_bytes(const nve_b200_decode_model& m) {
     const int kmax = std::max(m.hidden, std::max(m.ffn, m.num_heads * m.head_dim));
     const size_t S = (static_cast<size_t>(kmax) / 32 + 31) / 32;
     const size_t planes = S * 32 * (32 * 2 + 8);
     const size_t attn = 2 * (m.head_dim == 128 ? sizeof(AdShared<128, 2>) : sizeof(AdShared<64, 2>));
-    return std::max(planes, attn);
+    return align_up(std::max(planes, attn), 128);
 }
+constexpr size_t kDsSmemBudget = 200 * 1024;  // dynamic shared memory the kernel may ask for (static use comes on top)
 
 static void ds_fill_work(DsWork& w, void* workspace, const DsLayout& l) {
     unsigned char* b = static_cast<unsigned char*>(workspace);
     w.bar = reinterpret_cast<unsigned long long*>(b + l.off_bar);
     w.err = reinterpret_cast<int*>(b + l.off_err);
+    w.attn_cnt = reinterpret_cast<int*>(b + l.off_cnt);
     w.q = reinterpret_cast<uint16_t*>(b + l.off_q);
     w.k = reinterpret_cast<uint16_t*>(b + l.off_k);
     w.v = reinterpret_cast<uint16_t*>(b + l.off_v);
     w.parts = b + l.off_parts;
     w.attn = reinterpret_cast<uint16_t*>(b + l.off_attn);
-    w.xq_a = reinterpret_cast<int8_t*>(b + l.off_xq_a);
-    w.xs_a = reinterpret_cast<float*>(b + l.off_xs_a);
-    w.gate = reinterpret_cast<uint16_t*>(b + l.off_gate);
-    w.up = reinterpret_cast<uint16_t*>(b + l.off_up);
-    w.xq_f = reinterpret_cast<int8_t*>(b + l.off_xq_f);
-    w.xlo_f = reinterpret_cast<uint8_t*>(b + l.off_xlo_f);
-    w.xs_f = reinterpret_cast<float*>(b + l.off_xs_f);
+    w.mid = reinterpret_cast<uint16_t*>(b + l.off_mid);
 }
 
-static long long g_ds_prefetch_bytes = 48ll << 20;
+static int g_ds_prefetch_items = 0;
 static unsigned long long* g_ds_trace = nullptr;
 
 }  // namespace nve
@@ -856,15 +854,15 @@ extern "C" size_t nve_b200_decode_step_workspace_bytes(const nve_b200_decode_mod
 }
 
 extern "C" int nve_b200_decode_step_init(void* workspace, size_t workspace_bytes, nve_stream_t stream) {
-    if (workspace == nullptr || workspace_bytes < 512) return set_status(NVE_ERR_BAD_POINTER);
+    if (workspace == nullptr || workspace_bytes < kDsControlBytes) return set_status(NVE_ERR_BAD_POINTER);
     if (!aligned(workspace, 256)) return set_status(NVE_ERR_BAD_ALIGNMENT);
-    // barrier counter and error word start at zero; the activation buffers need no initial value
-    return set_cuda_status(cudaMemsetAsync(workspace, 0, 512, static_cast<cudaStream_t>(stream)));
+    // barrier counter, error word and slice counters start at zero; the activation buffers need no initial value
+    return set_cuda_status(cudaMemsetAsync(workspace, 0, kDsControlBytes, static_cast<cudaStream_t>(stream)));
 }
 
-extern "C" long long nve_b200_decode_step_set_prefetch(long long bytes) {
-    const long long old = g_ds_prefetch_bytes;
-    if (bytes >= 0) g_ds_prefetch_bytes = bytes;
+extern "C" int nve_b200_decode_step_set_prefetch(int items) {
+    const int old = g_ds_prefetch_items;
+    if (items >= 0) g_ds_prefetch_items = items > 64 ? 64 : items;
     return old;
 }
 
@@ -877,8 +875,8 @@ extern "C" int nve_b200_decode_step(const nve_b200_decode_model* model, const nv
     if (!aligned(workspace, 256) || !aligned(hidden, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
     const DsLayout l = ds_layout(*model);
     if (workspace_bytes < l.total) return set_status(NVE_ERR_TOO_LARGE);
-    const size_t smem = ds_smem_bytes(*model);
-    if (smem > static_cast<size_t>(kMaxGemvSmem)) return set_status(NVE_ERR_TOO_LARGE);
+    const size_t smem = ds_front_bytes(*model);
+    if (smem > kDsSmemBudget) return set_status(NVE_ERR_TOO_LARGE);
     DsParams p;
     p.m = *model;
     p.layers = layers_dev;
@@ -887,11 +885,11 @@ extern "C" int nve_b200_decode_step(const nve_b200_decode_model* model, const nv
     p.d_seq_len = d_seq_len;
     ds_fill_work(p.w, workspace, l);
     p.wait_ns = kDsWaitNs;
-    p.pf_bytes = g_ds_prefetch_bytes;
+    p.pf_items = g_ds_prefetch_items;
     p.trace = g_ds_trace;
     const void* kern = model->head_dim == 128 ? reinterpret_cast<const void*>(decode_step_kernel<128>)
                                               : reinterpret_cast<const void*>(decode_step_kernel<64>);
-    st = ensure_dynamic_smem(kern, kMaxGemvSmem);
+    st = ensure_dynamic_smem(kern, static_cast<int>(kDsSmemBudget));
     if (st != NVE_OK) return st;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count());
@@ -918,7 +916,7 @@ extern "C" int nve_b200_decode_step_error(void* workspace, int reset) {
     // the error word sits at the second 256-byte slot of the workspace (see ds_layout)
     cudaError_t e = cudaMemcpy(&v, b + 256, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { set_cuda_status(e); return -1; }
-    if (reset && v != 0) cudaMemset(workspace, 0, 512);
+    if (reset && v != 0) cudaMemset(workspace, 0, kDsControlBytes);
     return v;
 }
 

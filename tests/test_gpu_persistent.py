@@ -173,8 +173,8 @@ def test_bounded_wait_reports_timeout_instead_of_hanging(cuda):
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    ws = torch.zeros(1024, dtype=torch.uint8, device="cuda")
-    ws = ws[(-ws.data_ptr()) % 256:][:512]
+    ws = torch.zeros(4096 + 256, dtype=torch.uint8, device="cuda")
+    ws = ws[(-ws.data_ptr()) % 256:][:4096]
     ck.decode_step_init(ws)
     assert ck.decode_step_error(ws) == 0
     ck.decode_step_wait_probe(ws, 2_000_000)  # 2 ms
