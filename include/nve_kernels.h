@@ -387,8 +387,14 @@ NVE_API int nve_b200_decode_step_wait_probe(void* workspace, unsigned long long 
  * peers.  The *_allreduce GEMVs then compute out = [residual +] sum over ranks of (W_shard . x_shard) for a
  * K-sharded (row-parallel) projection in ONE kernel: each CTA pushes its partial rows as {value, epoch} slots
  * into every rank's buffer with plain 8-byte peer stores, then polls (bounded) its own buffer until the slots
- * of its rows carry the current epoch and adds them in rank order, so every rank holds bit-identical results.  All ranks must issue the same sequence of *_allreduce calls with the same N.
- * nve_b200_tp_error returns 0, or 1 + the rank whose flag a bounded wait gave up on. */
+ * of its rows carry the current epoch and adds them in rank order, so every rank holds bit-identical results.
+ * All ranks must issue the same sequence of *_allreduce calls (same N in the same order on every rank; N and K may
+ * differ from call to call: every all-reduce launch uses the full grid, so the per-CTA launch counters that number
+ * the epochs stay in step).  nve_b200_tp_error returns 0, or 1 + the rank whose slot a bounded wait (2^22 polls,
+ * >= 0.14 s) gave up on; the affected rows are then set to NaN.  Check it once per step; an eager (non-graph) caller
+ * should barrier the ranks after warm-up so that first-call module loading on one rank cannot outlast the wait.
+ * nve_b200_tp_destroy frees the buffer that every peer has mapped: call it only when ALL ranks are idle (no
+ * all-reduce kernel in flight anywhere) and have passed a host barrier; it closes the peer mappings first. */
 NVE_API int nve_b200_tp_create(int rank, int world, int max_rows, void* handle_out);
 NVE_API int nve_b200_tp_connect(const void* handles);
 NVE_API int nve_b200_tp_world(void);

@@ -95,15 +95,17 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
-// System-scope 8-byte accesses for slots that another GPU writes over NVLink (peer mappings): one store carries
-// value and epoch together, so the reader needs no separate flag.
-__device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, uint32_t a, uint32_t b) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+// System-scope 8-byte accesses for slots that another GPU writes over NVLink (peer mappings): value (low word) and
+// epoch (high word) travel in ONE aligned 64-bit access, which is single-copy atomic, so the reader needs no
+// separate flag and can never pair a new epoch with an old value.
+__device__ __forceinline__ void st_relaxed_sys_slot(uint2* p, uint32_t value, uint32_t epoch) {
+    const unsigned long long w = (static_cast<unsigned long long>(epoch) << 32) | value;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ uint2 ld_relaxed_sys_slot(const uint2* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
 }
 
 // Programmatic dependent launch: wait for the producer grid's memory / allow the consumer grid to start.

@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 for (int c = 1; c < CG; c++) y = __fadd_rn(y, sm.part[i * CG + c]);
                 if (tp_on) {  // push this rank's partial sum {value, epoch} to every rank; reduced after the last chunk
                     for (int r = 0; r < p.tp.world; r++)
-                        st_relaxed_sys_v2(p.tp.ll[r] + tp_plane + grow, __float_as_uint(y), tp_epoch);
+                        st_relaxed_sys_slot(p.tp.ll[r] + tp_plane + grow, __float_as_uint(y), tp_epoch);
                     continue;
                 }
                 void* out;
@@ -196,12 +196,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 float y = 0.0f;
                 for (int r = 0; r < p.tp.world; r++) {
                     const uint2* slot = mine + static_cast<size_t>(r) * p.tp.rows_cap + grow;
-                    uint2 v = ld_relaxed_sys_v2(slot);
+                    uint2 v = ld_relaxed_sys_slot(slot);
                     for (unsigned spin = 0; v.y != tp_epoch && spin < kTpSpinLimit; spin++) {
                         __nanosleep(32);
-                        v = ld_relaxed_sys_v2(slot);
+                        v = ld_relaxed_sys_slot(slot);
                     }
-                    if (v.y != tp_epoch) atomicExch(p.tp.err, 1 + r);  // bounded wait expired: report, do not hang
+                    // bounded wait expired: report which rank never arrived, do not hang, and poison the row so
+                    // that a finite-check on the hidden state trips instead of a stale partial sum passing silently
+                    if (v.y != tp_epoch) {
+                        atomicExch(p.tp.err, 1 + r);
+                        v.x = 0x7FC00000u;
+                    }
                     const float part = __uint_as_float(v.x);
                     y = (r == 0) ? part : __fadd_rn(y, part);
                 }
@@ -302,7 +307,9 @@ template <typename Kern> static int launch_gemv(Kern kern, const GemvParams& p, 
     }
     int grid = 2 * sm_count();
     const int tiles = (p.n_total + rows_per_item - 1) / rows_per_item;
-    if (grid > tiles) grid = tiles;
+    // The fused all-reduce numbers its launches with a per-CTA counter, so every all-reduce launch of a process must
+    // have the same grid whatever its shape: CTAs without tiles still run (and count the launch).
+    if (grid > tiles && p.tp.world <= 1) grid = tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kGemvThreads);

@@ -25,15 +25,12 @@ Tensor = torch.Tensor
 class _LayerScratch:
     """Per-layer scratch of src/decode_graph.rs:60-71, plus the int8 staging of the W4A8 route."""
 
-    normed: Tensor
     q: Tensor
     k: Tensor
     v: Tensor
     attn: Tensor
     gate: Tensor
     up: Tensor
-    xq_h: Tensor
-    xs_h: Tensor
     xq_a: Tensor
     xs_a: Tensor
     xq_f: Tensor
@@ -45,8 +42,13 @@ class StaticDecodeGraph:
     """One captured decode step over all layers of a GpuInferenceState."""
 
     def __init__(self, state: GpuInferenceState, hidden_size: int, ffn_size: int, importance: Sequence[float],
-                 allreduce: bool = False):
+                 allreduce: bool = False, lm_head=None):
+        """`lm_head` = (weights, final_norm, kind) appends the final RMSNorm and the lm_head GEMV that the reference
+        runs on the host (src/paged_model.rs:1424-1433): kind "w4a16" / "w4a8" with a GpuW4 (logits f32, one fused
+        launch) or "f16" with a dense [vocab, hidden] f16 tensor (RMSNorm launch + nve_matvec_f16, logits f16)."""
         self.state = state
+        self.lm_head = lm_head
+        self.logits = None
         self.allreduce = allreduce  # tensor parallel: `state` holds this rank's shards (ffn_size is the local FFN width)
         self.hidden_size = hidden_size
         self.ffn_size = ffn_size
@@ -58,15 +60,12 @@ class StaticDecodeGraph:
         self.scratch: List[_LayerScratch] = []
         # one scratch set is enough: layers run back to back on one stream
         s = _LayerScratch(
-            normed=torch.zeros((1, hidden_size), dtype=f16, device=dev),
             q=torch.zeros((nh, hd), dtype=f16, device=dev),
             k=torch.zeros((nkv, hd), dtype=f16, device=dev),
             v=torch.zeros((nkv, hd), dtype=f16, device=dev),
             attn=torch.zeros((1, nh * hd), dtype=f16, device=dev),
             gate=torch.zeros((1, ffn_size), dtype=f16, device=dev),
             up=torch.zeros((1, ffn_size), dtype=f16, device=dev),
-            xq_h=torch.zeros(hidden_size, dtype=torch.int8, device=dev),
-            xs_h=torch.zeros(hidden_size // 32, dtype=torch.float32, device=dev),
             xq_a=torch.zeros(nh * hd, dtype=torch.int8, device=dev),
             xs_a=torch.zeros(nh * hd // 32, dtype=torch.float32, device=dev),
             xq_f=torch.zeros(ffn_size, dtype=torch.int8, device=dev),
@@ -77,8 +76,28 @@ class StaticDecodeGraph:
         self.routes: List[bool] = [state.routing.use_w4a8(x) for x in self.importance]
         self.launches_per_replay = 0
         self.captured = False
+        if lm_head is not None:
+            w, _norm, kind = lm_head
+            if kind == "f16":
+                self.logits = torch.zeros((1, w.shape[0]), dtype=f16, device=dev)
+                self._normed = torch.zeros((1, hidden_size), dtype=f16, device=dev)
+            else:
+                self.logits = torch.zeros((1, w.n), dtype=torch.float32, device=dev)
 
     # ------------------------------------------------------------------ recording
+    def _record_lm_head(self) -> None:
+        w, norm, kind = self.lm_head
+        eps = self.state.norm_eps
+        if kind == "f16":
+            ck.fused_rms_norm_into(self.hidden_buf, norm, self._normed, eps)
+            ck.fused_matvec_into(self._normed, w, self.logits, w.shape[0], w.shape[1])
+        elif kind == "w4a8":
+            ck.rmsnorm_matvec_w4a8_multi(self.hidden_buf, norm, eps, [w.triple()], w.k, out_dtype=torch.float32,
+                                         outs=[self.logits])
+        else:
+            ck.rmsnorm_matvec_w4a16_multi(self.hidden_buf, norm, eps, w.awq_scales, [w.triple()], w.k,
+                                          out_dtype=torch.float32, outs=[self.logits])
+
     def _record_layer(self, li: int, d_pos: int, d_seqlen: int) -> None:
         from .gpu_layer import _layer_forward_fused
 
@@ -95,6 +114,8 @@ class StaticDecodeGraph:
             d_pos, d_seqlen = ck.graph_d_pos_ptr(), ck.graph_d_seqlen_ptr()
             for li in range(len(self.state.layer_weights)):
                 self._record_layer(li, d_pos, d_seqlen)
+            if self.lm_head is not None:
+                self._record_lm_head()
         finally:
             ck.graph_end_capture()
         self.launches_per_replay = ck.launch_count() - before

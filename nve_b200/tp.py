@@ -87,6 +87,8 @@ class TpContext:
         return int(_ffi.load().nve_b200_tp_error(int(reset)))
 
     def destroy(self) -> None:
+        """Free this rank's buffer.  Every peer has it mapped and stores into it from inside the all-reduce kernels, so
+        call this only after ALL ranks have synchronised their streams and passed a host barrier."""
         _ffi.load().nve_b200_tp_destroy()
 
 
@@ -124,3 +126,55 @@ def tp_layer_forward(hidden: torch.Tensor, li: int, state: GpuInferenceState, d_
     """One layer on this rank; o_proj and down_proj all-reduce inside their kernels."""
     return _layer_forward_fused(hidden, state.layer_weights[li], state, li, d_pos, d_seqlen, use_w4a8, out=out,
                                 scratch=scratch, allreduce=True)
+
+
+def tp_layer_forward_nccl(hidden: torch.Tensor, li: int, state: GpuInferenceState, d_pos: int, d_seqlen: int,
+                          use_w4a8: bool) -> torch.Tensor:
+    """The same layer with the NAMED collective: the row-parallel GEMVs write this rank's f32 partial sums and
+    `torch.distributed.all_reduce` (NCCL over NVLink) adds them; the residual is then added with the roundings of the
+    fused kernel (f16(sum), then f16(residual + that)).  This is the A/B baseline and the parity reference of the
+    all-reduce fused into the GEMV; it is not captured in a graph (eager launches + NCCL)."""
+    import torch.distributed as dist
+
+    w = state.layer_weights[li]
+    nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+    dev, f16, f32 = hidden.device, torch.float16, torch.float32
+    ffn = w.gate_proj.n
+    q = torch.empty((nh, hd), dtype=f16, device=dev)
+    k = torch.empty((nkv, hd), dtype=f16, device=dev)
+    v = torch.empty((nkv, hd), dtype=f16, device=dev)
+    attn = torch.empty((1, nh * hd), dtype=f16, device=dev)
+    gate = torch.empty((1, ffn), dtype=f16, device=dev)
+    up = torch.empty((1, ffn), dtype=f16, device=dev)
+    qkv_w = [w.q_proj.triple(), w.k_proj.triple(), w.v_proj.triple()]
+    qkv_o = [q.view(1, -1), k.view(1, -1), v.view(1, -1)]
+    kc, vc = state.kv_cache.k[li], state.kv_cache.v[li]
+    max_seq, eps, scale = state.kv_cache.max_seq, state.norm_eps, float(hd) ** -0.5
+
+    def reduce_add(res: torch.Tensor, part: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(part)
+        return (res.float() + part.to(f16).float()).to(f16)
+
+    if use_w4a8:
+        xq_a = torch.empty(nh * hd, dtype=torch.int8, device=dev)
+        xs_a = torch.empty(nh * hd // 32, dtype=f32, device=dev)
+        ck.rmsnorm_matvec_w4a8_multi(hidden, w.input_norm, eps, qkv_w, w.q_proj.k, outs=qkv_o)
+        ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv, hd,
+                             max_seq, scale, out_q=xq_a, out_scales=xs_a)
+        part = ck.matvec_w4a8_multi(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, out_dtype=f32)[0]
+        h1 = reduce_add(hidden, part)
+        ck.rmsnorm_matvec_w4a8_multi(h1, w.post_attn_norm, eps, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
+                                     outs=[gate, up])
+        xq_f, xs_f, _ = ck.silu_mul_quantize_q8(gate, up)
+        part = ck.matvec_w4a8_multi(xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, out_dtype=f32)[0]
+        return reduce_add(h1, part)
+    ck.rmsnorm_matvec_w4a16_multi(hidden, w.input_norm, eps, w.q_proj.awq_scales, qkv_w, w.q_proj.k, outs=qkv_o)
+    ck.attn_decode_fused(q, k, v, kc, vc, state.rope_cos, state.rope_sin, d_pos, d_seqlen, attn.view(nh, hd), nh, nkv, hd,
+                         max_seq, scale)
+    part = ck.matvec_w4a16_multi(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, out_dtype=f32)[0]
+    h1 = reduce_add(hidden, part)
+    ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
+                                  [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
+    ck.silu_mul_inplace(gate, up)
+    part = ck.matvec_w4a16_multi(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, out_dtype=f32)[0]
+    return reduce_add(h1, part)

@@ -328,6 +328,19 @@ def attn_decode(q, kc, vc, seq_len: int, scale: float) -> np.ndarray:
     return out
 
 
+def attn_decode_f32(q, kc, vc, seq_len: int, scale: float) -> np.ndarray:
+    """orc_attn_decode_f32: the reference's f32 loop order (timed baseline); same shapes as attn_decode."""
+    q = _c(q, np.float32)
+    kc = _c(kc, np.float32)
+    vc = _c(vc, np.float32)
+    nh, hd = q.shape
+    nkv, stride, _ = kc.shape
+    out = np.empty((nh, hd), np.float32)
+    lib().orc_attn_decode_f32(_p(q), _p(kc), _p(vc), C.c_int(nh), C.c_int(nkv), C.c_int(seq_len), C.c_int(stride),
+                              C.c_int(hd), C.c_float(scale), _p(out))
+    return out
+
+
 # --------------------------------------------------------------------------- routing
 def normalize_importance(scores) -> np.ndarray:
     s = _c(scores, np.float64)

@@ -388,21 +388,46 @@ void orc_q4_linear(const uint8_t* blocks, const float* X, long M, long N, long K
 /* ------------------------------------------------------------------------- */
 
 typedef void (*orc_row_fn)(void* ctx, long n0, long n1);
-typedef struct {
-    orc_row_fn fn;
-    void* ctx;
-    long n0, n1;
-} orc_job;
-
-static void* orc_job_main(void* p) {
-    orc_job* j = (orc_job*)p;
-    j->fn(j->ctx, j->n0, j->n1);
-    return NULL;
-}
-
 static int g_orc_threads = 1;
 void orc_set_threads(int n) { g_orc_threads = n < 1 ? 1 : (n > 256 ? 256 : n); }
 int orc_get_threads(void) { return g_orc_threads; }
+
+/* A persistent pool (the reference's rayon keeps its workers alive between calls too): workers sleep on a condition
+ * variable until a new job generation is published; the caller runs slice 0 itself and waits for the others. */
+static struct {
+    pthread_mutex_t mu;
+    pthread_cond_t go, done;
+    pthread_t th[256];
+    int workers;        /* threads created so far (worker w runs slice w + 1) */
+    unsigned long gen;  /* job generation */
+    int active;         /* slices of the current job that run on workers */
+    int pending;        /* of those, still running */
+    orc_row_fn fn;
+    void* ctx;
+    long N;
+    int T;
+    int ready;
+} g_pool = {PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER, PTHREAD_COND_INITIALIZER, {0}, 0, 0, 0, 0, 0, 0, 0, 0, 1};
+
+static void* orc_pool_main(void* arg) {
+    long w = (long)arg;
+    unsigned long seen = 0;
+    pthread_mutex_lock(&g_pool.mu);
+    for (;;) {
+        while (g_pool.gen == seen) pthread_cond_wait(&g_pool.go, &g_pool.mu);
+        seen = g_pool.gen;
+        if (w + 1 >= g_pool.T) continue; /* not part of this job */
+        orc_row_fn fn = g_pool.fn;
+        void* ctx = g_pool.ctx;
+        long N = g_pool.N;
+        int T = g_pool.T;
+        pthread_mutex_unlock(&g_pool.mu);
+        fn(ctx, N * (w + 1) / T, N * (w + 2) / T);
+        pthread_mutex_lock(&g_pool.mu);
+        if (--g_pool.pending == 0) pthread_cond_signal(&g_pool.done);
+    }
+    return NULL;
+}
 
 static void orc_parallel_rows(orc_row_fn fn, void* ctx, long N) {
     int T = g_orc_threads;
@@ -410,16 +435,25 @@ static void orc_parallel_rows(orc_row_fn fn, void* ctx, long N) {
         fn(ctx, 0, N);
         return;
     }
-    pthread_t th[256];
-    orc_job jobs[256];
-    for (int t = 0; t < T; t++) {
-        jobs[t].fn = fn;
-        jobs[t].ctx = ctx;
-        jobs[t].n0 = N * t / T;
-        jobs[t].n1 = N * (t + 1) / T;
-        pthread_create(&th[t], NULL, orc_job_main, &jobs[t]);
+    pthread_mutex_lock(&g_pool.mu);
+    while (g_pool.workers < T - 1) {
+        long w = g_pool.workers;
+        if (pthread_create(&g_pool.th[w], NULL, orc_pool_main, (void*)w) != 0) break;
+        g_pool.workers++;
     }
-    for (int t = 0; t < T; t++) pthread_join(th[t], NULL);
+    if (T > g_pool.workers + 1) T = g_pool.workers + 1;
+    g_pool.fn = fn;
+    g_pool.ctx = ctx;
+    g_pool.N = N;
+    g_pool.T = T;
+    g_pool.pending = T - 1;
+    g_pool.gen++;
+    pthread_cond_broadcast(&g_pool.go);
+    pthread_mutex_unlock(&g_pool.mu);
+    fn(ctx, 0, N / T);
+    pthread_mutex_lock(&g_pool.mu);
+    while (g_pool.pending > 0) pthread_cond_wait(&g_pool.done, &g_pool.mu);
+    pthread_mutex_unlock(&g_pool.mu);
 }
 
 /* Threaded form of matvec_f32 for the timed CPU baseline: rows in parallel as rayon does for
@@ -839,6 +873,69 @@ void orc_attn_decode(const float* q, const float* kc, const float* vc, int nh, i
             double a = 0.0;
             for (int t = 0; t < seq_len; t++) a += sc[t] * (double)vc[((long)kvh * stride + t) * hd + i];
             out[(long)h * hd + i] = (float)(sum > 0.0 ? a / sum : 0.0);
+        }
+    }
+    free(sc);
+}
+
+/* src/tensor.rs:932-953: f32 dot with the AVX2+FMA form the reference dispatches to on x86-64 (32 floats per
+ * iteration in four accumulators), scalar 8-way unrolled otherwise (:955-985). */
+static float orc_dot_f32(const float* a, const float* b, int n) {
+    int i = 0;
+    float sum = 0.0f;
+#if ORC_HAVE_AVX2
+    if (n >= 32) {
+        __m256 s0 = _mm256_setzero_ps(), s1 = s0, s2 = s0, s3 = s0;
+        for (; i + 32 <= n; i += 32) {
+            s0 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i), _mm256_loadu_ps(b + i), s0);
+            s1 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i + 8), _mm256_loadu_ps(b + i + 8), s1);
+            s2 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i + 16), _mm256_loadu_ps(b + i + 16), s2);
+            s3 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i + 24), _mm256_loadu_ps(b + i + 24), s3);
+        }
+        __m256 t = _mm256_add_ps(_mm256_add_ps(s0, s1), _mm256_add_ps(s2, s3));
+        float lanes[8];
+        _mm256_storeu_ps(lanes, t);
+        sum = ((lanes[0] + lanes[1]) + (lanes[2] + lanes[3])) + ((lanes[4] + lanes[5]) + (lanes[6] + lanes[7]));
+    }
+#endif
+    for (; i < n; i++) sum += a[i] * b[i];
+    return sum;
+}
+
+/* src/attention.rs:199-224 with the reference's own types and loop order (f32 dot, f32 softmax with max
+ * subtraction as src/ops.rs:152-163, t-outer / d-inner weighted V sum, one head after the other on one thread):
+ * the form timed by the CPU baseline.  orc_attn_decode above accumulates in f64 and is the one parity checks use. */
+void orc_attn_decode_f32(const float* q, const float* kc, const float* vc, int nh, int nkv, int seq_len, int stride,
+                         int hd, float scale, float* out) {
+    int groups = nh / nkv;
+    float* sc = (float*)malloc(sizeof(float) * (size_t)(seq_len > 0 ? seq_len : 1));
+    for (int h = 0; h < nh; h++) {
+        int kvh = h / groups;
+        const float* qh = q + (long)h * hd;
+        float mx = -INFINITY;
+        for (int t = 0; t < seq_len; t++) {
+            sc[t] = orc_dot_f32(qh, kc + ((long)kvh * stride + t) * hd, hd) * scale;
+            if (sc[t] > mx) mx = sc[t];
+        }
+        float sum = 0.0f;
+        for (int t = 0; t < seq_len; t++) {
+            sc[t] = expf(sc[t] - mx);
+            sum += sc[t];
+        }
+        float inv = 1.0f / sum;
+        for (int t = 0; t < seq_len; t++) sc[t] *= inv;
+        float* oh = out + (long)h * hd;
+        for (int i = 0; i < hd; i++) oh[i] = 0.0f;
+        for (int t = 0; t < seq_len; t++) {
+            const float* vt = vc + ((long)kvh * stride + t) * hd;
+            const float w = sc[t];
+            int i = 0;
+#if ORC_HAVE_AVX2
+            const __m256 wv = _mm256_set1_ps(w);
+            for (; i + 8 <= hd; i += 8)
+                _mm256_storeu_ps(oh + i, _mm256_add_ps(_mm256_loadu_ps(oh + i), _mm256_mul_ps(wv, _mm256_loadu_ps(vt + i))));
+#endif
+            for (; i < hd; i++) oh[i] += w * vt[i];
         }
     }
     free(sc);

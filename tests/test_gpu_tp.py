@@ -12,7 +12,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, dims):
     import torch
     import torch.distributed as dist
 
@@ -26,7 +26,7 @@ def _worker(rank, world, port, q):
         from nve_b200.gpu_layer import gpu_layer_forward_decode
         from nve_b200.tp import TpContext, build_tp_state, tp_layer_forward
 
-        shape = ModelShape(512, 1024, 8, 2, 64, 4)
+        shape = ModelShape(*dims)
         ctx_len, seed = 16, 123
         state, imp, plan = build_tp_state(shape, seed, ctx_len, rank, world, fill_kv=False)
         tp = TpContext(rank, world, max_rows=shape.hidden)
@@ -58,7 +58,10 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_tp2_matches_single_gpu_and_ranks_agree():
+# The second shape is Llama-3.2-1B's: its two row-parallel projections have different K shards (o_proj 1024,
+# down_proj 4096), hence different tile counts -- the all-reduce launches must still number their epochs in step.
+@pytest.mark.parametrize("dims", [(512, 1024, 8, 2, 64, 4), (2048, 8192, 32, 8, 64, 2)])
+def test_tp2_matches_single_gpu_and_ranks_agree(dims):
     import torch
     import torch.multiprocessing as mp
 
@@ -70,7 +73,7 @@ def test_tp2_matches_single_gpu_and_ranks_agree():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, dims)) for r in range(2)]
     for p in procs:
         p.start()
     res = {}
