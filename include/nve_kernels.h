@@ -123,7 +123,11 @@ NVE_API void nve_silu_mul_f16(uint16_t* gate, const uint16_t* up, int n, nve_str
 NVE_API void nve_d2d_copy(void* dst, const void* src, size_t bytes, nve_stream_t stream);
 
 /* cuda/nve_kernels.cu:1230-1299.  Process-global decode-graph manager: one capture stream, pinned
- * pos/seq_len scalars copied to device scalars by the first two nodes of the graph. */
+ * pos/seq_len scalars copied to device scalars by the first two nodes of the graph.
+ * nve_graph_launch writes pos / seq_len into the pinned words at once and the replay reads them when its first two
+ * nodes run: do not issue the next nve_graph_launch with other values before the previous replay has consumed them
+ * (synchronise the stream, or at least wait for an event recorded after the previous launch) -- two replays
+ * enqueued back to back can otherwise both read the later position.  The reference has the same property. */
 NVE_API void nve_graph_init(void);
 NVE_API void nve_graph_begin_capture(void);
 NVE_API void nve_graph_end_capture(void);
@@ -170,6 +174,13 @@ NVE_API int nve_b200_set_pdl(int enabled);
 /* Activation quantizer with selectable input type (NVE_DT_F16 or NVE_DT_BF16); arithmetic as
  * nve_quantize_f16_q8 (cuda/nve_kernels.cu:712-745). */
 NVE_API int nve_b200_quantize_q8(const void* x, int8_t* xq, float* scales, int K, int x_dtype, nve_stream_t stream);
+
+/* The same quantiser for the activations of an AWQ pre-scaled matrix (src/quantize.rs:271-304 scales column k of the
+ * weights by s[k] and the W4A16 kernels multiply x[k] by awq_inv[k] = 1/s[k]): x[k] * awq_inv[k] (f32 product) is what
+ * gets quantised.  The reference drops the multiplier on its W4A8 route (nve_matvec_w4a8 has no such argument,
+ * src/gpu_layer.rs:659); with this entry point the W4A8 route sees the activations the W4A16 route sees. */
+NVE_API int nve_b200_quantize_q8_awq(const void* x, const float* awq_inv, int8_t* xq, float* scales, int K, int x_dtype,
+                                     nve_stream_t stream);
 
 /* Fused RMSNorm -> 16-bit round -> int8 quantisation (the two launches at src/gpu_layer.rs:1032-1038,658
  * in one).  normed_out may be NULL when only the codes are needed. */
@@ -234,6 +245,11 @@ NVE_API int nve_b200_rmsnorm_matvec_w4a8_multi(const void* h, const void* norm_w
 NVE_API int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
                                                 const float* awq, const nve_b200_w4_matrix* mats, int num_mats, int K,
                                                 int out_dtype, nve_stream_t stream);
+/* nve_b200_rmsnorm_matvec_w4a8_multi with the AWQ multiplier folded into the quantiser (the normalised, 16-bit
+ * rounded value times awq_inv[k] is what gets quantised, as nve_b200_quantize_q8_awq does). */
+NVE_API int nve_b200_rmsnorm_matvec_w4a8_awq_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                   const float* awq_inv, const nve_b200_w4_matrix* mats, int num_mats,
+                                                   int K, int out_dtype, nve_stream_t stream);
 
 /* RoPE of q and the new k at position *d_pos, the KV-cache write of the new row and single-query GQA
  * attention over the first *d_seq_len positions, in one launch (src/gpu_layer.rs:697-735 /
@@ -308,7 +324,12 @@ NVE_API int nve_b200_gemm_error(int reset);
  *   - The first call on each device resolves the array's device address and caches it; make that call before
  *     any stream capture begins.
  *   - All calls share the array and it keeps the previous call's contents (nothing in it needs to start at
- *     zero); two of these GEMMs running concurrently on one GPU race on it -- keep them on one stream. */
+ *     zero); two of these GEMMs running concurrently on one GPU race on it -- keep them on one stream.
+ *   - The split over K is the one the workspace form would choose; it is not lowered to make a shape fit, so e.g.
+ *     the 8B down projection at M = 64 with bf16 input (4 MiB of partials + a 1.8 MB f16 copy) is refused although a
+ *     smaller split would fit: use the workspace form there.
+ *   - The cached address belongs to the device's current context: after cudaDeviceReset the library must be
+ *     reloaded before this entry point is used again on that device. */
 NVE_API int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
                                         int y_dtype, int M, int N, int K, nve_stream_t stream);
 

@@ -118,6 +118,7 @@ SIGNATURES = {
     "nve_b200_launch_count": (_ULL, []),
     "nve_b200_set_pdl": (_I, [_I]),
     "nve_b200_quantize_q8": (_I, [_P, _P, _P, _I, _I, _P]),
+    "nve_b200_quantize_q8_awq": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "nve_b200_rmsnorm_quantize_q8": (_I, [_P, _P, _P, _P, _P, _I, _F, _I, _P]),
     "nve_b200_rms_norm": (_I, [_P, _P, _P, _I, _F, _I, _P]),
     "nve_b200_silu_mul_quantize_q8": (_I, [_P, _P, _P, _P, _P, _I, _I, _P]),
@@ -128,6 +129,7 @@ SIGNATURES = {
     "nve_b200_matvec_w4a16_multi": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_matvec_w4a16_planes_multi": (_I, [_P, _P, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a8_multi": (_I, [_P, _P, _F, _I, C.POINTER(W4Matrix), _I, _I, _I, _P]),
+    "nve_b200_rmsnorm_matvec_w4a8_awq_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a16_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_attn_decode_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
     "nve_b200_w4a8_idot": (_I, [_P, _P, _P, _I, _I, _P]),

@@ -37,7 +37,8 @@ template <bool VEC> __device__ __forceinline__ void store_chunk(uint16_t* p, lon
 }
 
 template <int DT> __global__ void __launch_bounds__(kActThreads) quantize_q8_kernel(const uint16_t* x, int8_t* xq,
-                                                                                     float* scales, int K) {
+                                                                                     float* scales, int K,
+                                                                                     const float* awq_inv) {
     pdl_wait();
     const long long chunk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const bool active = chunk * 8 < K;
@@ -47,22 +48,31 @@ template <int DT> __global__ void __launch_bounds__(kActThreads) quantize_q8_ker
         load_chunk<true>(x, chunk, K, h);
 #pragma unroll
         for (int e = 0; e < 8; e++) v[e] = Act16<DT>::to_f32(h[e]);
+        if (awq_inv != nullptr) {  // activations of an AWQ pre-scaled matrix: x[k] * awq_inv[k] before the absmax
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], awq_inv[chunk * 8 + e]);
+        }
     }
     pdl_launch_dependents();
     quantize_quad(v, xq, scales, chunk, active);
 }
 
 // Scalar fallback for unaligned pointers: one thread per group.
-template <int DT> __global__ void quantize_q8_scalar_kernel(const uint16_t* x, int8_t* xq, float* scales, int K) {
+template <int DT> __global__ void quantize_q8_scalar_kernel(const uint16_t* x, int8_t* xq, float* scales, int K,
+                                                           const float* awq_inv) {
     const int g = blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= K / 32) return;
+    auto val = [&](int e) {
+        const float v = Act16<DT>::to_f32(x[g * 32 + e]);
+        return awq_inv != nullptr ? __fmul_rn(v, awq_inv[g * 32 + e]) : v;
+    };
     float amax = 0.0f;
-    for (int e = 0; e < 32; e++) amax = fmaxf(amax, fabsf(Act16<DT>::to_f32(x[g * 32 + e])));
+    for (int e = 0; e < 32; e++) amax = fmaxf(amax, fabsf(val(e)));
     const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, scale);
     scales[g] = scale;
     for (int e = 0; e < 32; e++) {
-        int q = __float2int_rn(__fmul_rn(Act16<DT>::to_f32(x[g * 32 + e]), inv));
+        int q = __float2int_rn(__fmul_rn(val(e), inv));
         xq[g * 32 + e] = static_cast<int8_t>(max(-127, min(127, q)));
     }
 }
@@ -218,7 +228,8 @@ static int launch_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int gr
     return 0;
 }
 
-template <int DT> static int quantize_q8_impl(const void* x, int8_t* xq, float* scales, int K, cudaStream_t st) {
+template <int DT>
+static int quantize_q8_impl(const void* x, int8_t* xq, float* scales, int K, cudaStream_t st, const float* awq_inv = nullptr) {
     if (!x || !xq || !scales) return set_status(NVE_ERR_BAD_POINTER);
     if (K <= 0 || (K % 32) != 0) return set_status(NVE_ERR_BAD_SHAPE);
     const uint16_t* x16 = static_cast<const uint16_t*>(x);
@@ -226,11 +237,11 @@ template <int DT> static int quantize_q8_impl(const void* x, int8_t* xq, float* 
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
         launch_cfg(cfg, attr, (K / 8 + kActThreads - 1) / kActThreads, st);
-        cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_q8_kernel<DT>, x16, xq, scales, K);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_q8_kernel<DT>, x16, xq, scales, K, awq_inv);
         count_launch();
         return set_cuda_status(e);
     }
-    quantize_q8_scalar_kernel<DT><<<(K / 32 + 127) / 128, 128, 0, st>>>(x16, xq, scales, K);
+    quantize_q8_scalar_kernel<DT><<<(K / 32 + 127) / 128, 128, 0, st>>>(x16, xq, scales, K, awq_inv);
     count_launch();
     return check_launch();
 }
@@ -314,6 +325,13 @@ extern "C" int nve_b200_quantize_q8(const void* x, int8_t* xq, float* scales, in
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return NVE_DISPATCH_16(x_dtype, quantize_q8_impl<NVE_DT_F16>(x, xq, scales, K, st),
                            quantize_q8_impl<NVE_DT_BF16>(x, xq, scales, K, st));
+}
+
+extern "C" int nve_b200_quantize_q8_awq(const void* x, const float* awq_inv, int8_t* xq, float* scales, int K, int x_dtype,
+                                        nve_stream_t stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return NVE_DISPATCH_16(x_dtype, quantize_q8_impl<NVE_DT_F16>(x, xq, scales, K, st, awq_inv),
+                           quantize_q8_impl<NVE_DT_BF16>(x, xq, scales, K, st, awq_inv));
 }
 
 extern "C" void nve_quantize_f16_q8(const uint16_t* x, int8_t* xq, float* scales, int K, nve_stream_t stream) {

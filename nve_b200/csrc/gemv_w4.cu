@@ -467,6 +467,23 @@ extern "C" int nve_b200_rmsnorm_matvec_w4a8_multi(const void* h, const void* nor
     return set_status(NVE_ERR_BAD_DTYPE);
 }
 
+extern "C" int nve_b200_rmsnorm_matvec_w4a8_awq_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                      const float* awq_inv, const nve_b200_w4_matrix* mats, int num_mats,
+                                                      int K, int out_dtype, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_params(p, mats, num_mats, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h;
+    p.norm_w = norm_weight;
+    p.eps = eps;
+    p.awq = awq_inv;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_out<1, NVE_DT_F16, 1>(p, num_mats, out_dtype, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_out<1, NVE_DT_BF16, 1>(p, num_mats, out_dtype, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
 extern "C" int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* norm_weight, float eps, int act_dtype,
                                                    const float* awq, const nve_b200_w4_matrix* mats, int num_mats, int K,
                                                    int out_dtype, nve_stream_t stream) {

@@ -340,11 +340,9 @@ template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_ac
                                 const float o = __fmul_rn(__fmul_rn(Act16<XDT>::to_f32(h[e]), r), Act16<XDT>::to_f32(hw[e]));
                                 v[e] = Act16<XDT>::to_f32(Act16<XDT>::from_f32(o));
                             }
-                            if constexpr (PLANES == 2) {
-                                if (p.awq != nullptr) {
+                            if (p.awq != nullptr) {  // W4A16 always; W4A8 only through the *_awq entry point
 #pragma unroll
-                                    for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
-                                }
+                                for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
                             }
                         }
                         if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);
@@ -394,11 +392,9 @@ template <int PLANES, int XDT, int PRO> __device__ __forceinline__ void stage_ac
 #pragma unroll
                     for (int e = 0; e < 8; e++) v[e] = Act16<XDT>::to_f32(h[e]);
                 }
-                if constexpr (PLANES == 2) {
-                    if (p.awq != nullptr) {
+                if (p.awq != nullptr) {
 #pragma unroll
-                        for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
-                    }
+                    for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.awq[c * 8 + e]);
                 }
             }
             if constexpr (PLANES == 1) stage_chunk_q8(sm, c, v, active);

@@ -328,6 +328,17 @@ def quantize_q8(x: Tensor) -> Tuple[Tensor, Tensor]:
     return xq, scales
 
 
+def quantize_q8_awq(x: Tensor, awq_inv: Tensor) -> Tuple[Tensor, Tensor]:
+    """int8 codes of x * awq_inv (per column), per group of 32: the W4A8 quantiser for AWQ pre-scaled weights."""
+    k = x.numel()
+    xq = torch.empty(k, dtype=torch.int8, device=x.device)
+    scales = torch.empty(k // 32, dtype=torch.float32, device=x.device)
+    _ffi.check("nve_b200_quantize_q8_awq",
+               _lib().nve_b200_quantize_q8_awq(_ptr(x, (torch.float16, torch.bfloat16), "x"), _ptr(awq_inv, torch.float32),
+                                               _ptr(xq), _ptr(scales), k, _dt(x), stream()))
+    return xq, scales
+
+
 def rms_norm(x: Tensor, weight: Tensor, eps: float, out: Optional[Tensor] = None) -> Tensor:
     out = torch.empty_like(x) if out is None else out
     _ffi.check("nve_b200_rms_norm", _lib().nve_b200_rms_norm(_ptr(x), _ptr(weight, x.dtype), _ptr(out, x.dtype),
@@ -450,6 +461,20 @@ def rmsnorm_matvec_w4a8_multi(h: Tensor, norm_weight: Tensor, eps: float, weight
                _lib().nve_b200_rmsnorm_matvec_w4a8_multi(_ptr(h, (torch.float16, torch.bfloat16), "h"),
                                                          _ptr(norm_weight, h.dtype, "norm_weight"), float(eps), _dt(h), arr,
                                                          len(weights), k, _TORCH_DT[out_dtype], stream()))
+    return list(outs)
+
+
+def rmsnorm_matvec_w4a8_awq_multi(h: Tensor, norm_weight: Tensor, eps: float, awq_inv: Tensor, weights: Sequence, k: int,
+                                  out_dtype=torch.float16, outs: Optional[Sequence[Tensor]] = None, residuals=None):
+    """rmsnorm_matvec_w4a8_multi with the AWQ multiplier folded into the activation quantiser."""
+    if outs is None:
+        outs = [torch.empty((1, n), dtype=out_dtype, device=h.device) for (_, _, n) in weights]
+    arr = _mats(weights, outs, residuals, out_dtype)
+    _ffi.check("nve_b200_rmsnorm_matvec_w4a8_awq_multi",
+               _lib().nve_b200_rmsnorm_matvec_w4a8_awq_multi(_ptr(h, (torch.float16, torch.bfloat16), "h"),
+                                                             _ptr(norm_weight, h.dtype, "norm_weight"), float(eps), _dt(h),
+                                                             _ptr(awq_inv, torch.float32), arr, len(weights), k,
+                                                             _TORCH_DT[out_dtype], stream()))
     return list(outs)
 
 

@@ -38,6 +38,31 @@ class GpuW4:
         return (self.nibbles, self.scales, self.n)
 
 
+def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None) -> Tensor:
+    """`GpuWeight::matmul_x` for W4 weights (src/gpu_layer.rs:220-239): x [M, K] -> [M, N].
+
+    The reference sends M == 1 to `fused_matvec_w4a16` and M > 1 through `dequant_w4a16` + a dense matmul (the whole
+    matrix materialised in f16, 4.6 bytes of traffic per weight).  Here M > 1 goes to the tcgen05 GEMM that reads the
+    packed weights once per slice of up to 64 rows of x (prefill-sized M is walked in such slices); the activation
+    multiplier `awq_scales`, which the GEMM has no argument for, is applied to x first as the GEMV does per element."""
+    if x.dim() != 2 or x.shape[1] != w.k:
+        raise ValueError(f"x must be [M, {w.k}]")
+    m = x.shape[0]
+    if m == 1:
+        return ck.fused_matvec_w4a16(x, w.nibbles, w.scales, w.awq_scales, w.n, w.k)
+    if w.awq_scales is not None:
+        x = (x.float() * w.awq_scales.view(1, -1)).to(x.dtype)
+    out = torch.empty((m, w.n), dtype=x.dtype, device=x.device)
+    step = 64
+    if scratch is None:
+        nbytes = ck.gemm_w4a16_scratch_bytes(min(m, step), w.n, w.k)
+        scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    for r0 in range(0, m, step):
+        rows = min(step, m - r0)
+        ck.gemm_w4a16(x[r0:r0 + rows], w.nibbles, w.scales, w.n, w.k, out=out[r0:r0 + rows], scratch=scratch)
+    return out
+
+
 @dataclass
 class GpuLayerWeights:
     """The W4 subset of src/gpu_layer.rs GpuLayerWeights (Llama-style block, no biases)."""

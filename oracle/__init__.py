@@ -195,6 +195,18 @@ def quantize_q8(x16, bf16: bool = False):
     return xq, sc
 
 
+def quantize_q8_awq(x16, awq_inv, bf16: bool = False):
+    """orc_quantize_q8_awq: int8 codes of x * awq_inv per group of 32."""
+    x16 = _c(x16, np.uint16)
+    awq_inv = _c(awq_inv, np.float32)
+    K = x16.size
+    assert K % 32 == 0 and awq_inv.size == K
+    xq = np.empty(K, np.int8)
+    sc = np.empty(K // 32, np.float32)
+    lib().orc_quantize_q8_awq(_p(x16), _p(awq_inv), _l(K), C.c_int(int(bf16)), _p(xq), _p(sc))
+    return xq, sc
+
+
 def w4a8_idot(xq, nibbles) -> np.ndarray:
     xq = _c(xq, np.int8)
     nibbles = _c(nibbles, np.uint8)

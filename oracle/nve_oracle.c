@@ -536,6 +536,30 @@ void orc_quantize_q8(const uint16_t* x16, long K, int is_bf16, int8_t* xq, float
     }
 }
 
+/* The same quantiser for activations of an AWQ pre-scaled matrix: x[k] * awq_inv[k] (one f32 product, the multiply
+ * the W4A16 kernels apply per element, cuda/nve_kernels.cu:354-355; awq_inv from src/quantize.rs:1107-1111) goes
+ * through the arithmetic of orc_quantize_q8.  The reference has no such W4A8 path (src/gpu_layer.rs:659 drops the
+ * multiplier): this restates the library's own extension. */
+void orc_quantize_q8_awq(const uint16_t* x16, const float* awq_inv, long K, int is_bf16, int8_t* xq, float* scales) {
+    for (long g = 0; g < K / 32; g++) {
+        float v[32];
+        float amax = 0.0f;
+        for (int e = 0; e < 32; e++) {
+            v[e] = act16_to_f32(x16[g * 32 + e], is_bf16) * awq_inv[g * 32 + e];
+            amax = fmaxf(amax, fabsf(v[e]));
+        }
+        float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        scales[g] = scale;
+        float inv = 1.0f / scale;
+        for (int e = 0; e < 32; e++) {
+            long q = lrintf(v[e] * inv);
+            if (q < -127) q = -127;
+            if (q > 127) q = 127;
+            xq[g * 32 + e] = (int8_t)q;
+        }
+    }
+}
+
 /* cuda/nve_kernels.cu:817-862: exact per-block integer dot I[n][b] = sum_e (q-8)*xq. */
 void orc_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, long N, long K, int32_t* I) {
     long nb = K / Q4_BLOCK;

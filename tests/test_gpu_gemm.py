@@ -104,3 +104,24 @@ def test_gemm_rejects_bad_arguments(cuda):
         ck.gemm_w4a16(x, nib, sc, 128, 64)  # M > 64
     with pytest.raises(_ffi.NveKernelError):
         ck.gemm_w4a16(x[:8, :32].contiguous(), nib, sc, 128, 32)  # K % 64 != 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 64, 130])
+@pytest.mark.parametrize("with_awq", [False, True])
+def test_matmul_x_matches_q4_linear(cuda, orc, M, with_awq):
+    """gpu_layer.matmul_x (the batch > 1 call site: GEMV at M == 1, the tcgen05 GEMM walked in 64-row slices above)
+    against the reference's CPU semantics q4_linear on the same 16-bit activations."""
+    from nve_b200.gpu_layer import GpuW4, matmul_x
+
+    torch = cuda
+    N, K = 768, 2048
+    W = orc.fill_normal(N * K, 931, 1, scale=0.02).reshape(N, K)
+    blocks = orc.quantize_q4(W)
+    nib, sc = orc.extract_for_gpu(blocks)
+    awq = (0.5 + np.abs(orc.fill_normal(K, 931, 3))).astype(np.float32) if with_awq else None
+    X16 = orc.to_act16(orc.fill_normal(M * K, 931, 2)).reshape(M, K)
+    w = GpuW4(dev(nib), dev(sc), None if awq is None else dev(awq), N, K)
+    y = matmul_x(dev(X16, torch.float16), w)
+    assert tuple(y.shape) == (M, N)
+    ref = orc.q4_linear(blocks, orc.from_act16(X16), awq_inv=awq)
+    assert rel_rms_err(y.float().cpu().numpy(), ref) < TOL

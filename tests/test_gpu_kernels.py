@@ -330,3 +330,64 @@ def test_matvec_f16_dense(cuda, orc):
     y = ck.fused_matvec(dev(x16, torch.float16), dev(W16, torch.float16), N, K)
     ref = orc.from_act16(W16).astype(np.float64) @ orc.from_act16(x16).astype(np.float64)
     assert rel_rms_err(y.float().cpu().numpy(), ref) < 2e-3
+
+
+# ------------------------------------------------------------------ AWQ multiplier folded into the W4A8 quantiser
+@pytest.mark.parametrize("bf", [False, True])
+def test_quantize_q8_awq_bit_exact_and_fused_prologue(cuda, orc, bf):
+    """codes / scales of x * awq_inv equal the oracle bit for bit; the fused RMSNorm + W4A8 GEMV with the multiplier
+    equals RMSNorm -> quantize_q8_awq -> W4A8 GEMV bit for bit."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    dt = torch.bfloat16 if bf else torch.float16
+    K, N = 4096, 512
+    x16 = orc.to_act16(orc.fill_normal(K, 611, 1) * 2.0, bf)
+    awq = (1.0 / (0.25 + np.abs(orc.fill_normal(K, 611, 2)))).astype(np.float32)  # 0.2 .. 4, a few large
+    awq[7] = 1.0e3
+    xq, xs = ck.quantize_q8_awq(dev(x16, dt), dev(awq))
+    eq, es = orc.quantize_q8_awq(x16, awq, bf)
+    assert np.array_equal(xq.cpu().numpy(), eq)
+    assert np.array_equal(xs.cpu().numpy(), es)
+    W = orc.fill_normal(N * K, 611, 3, scale=0.02).reshape(N, K)
+    nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+    mats = [(dev(nib), dev(sc), N)]
+    nw = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(K, 611, 4), bf), dt)
+    h = dev(x16, dt).view(1, -1)
+    normed = ck.rms_norm(h, nw, 1e-5)
+    q2, s2 = ck.quantize_q8_awq(normed, dev(awq))
+    sep = ck.matvec_w4a8_multi(q2, s2, mats, K, out_dtype=torch.float32)[0]
+    fused = ck.rmsnorm_matvec_w4a8_awq_multi(h, nw, 1e-5, dev(awq), mats, K, out_dtype=torch.float32)[0]
+    assert torch.equal(sep, fused)
+
+
+# ------------------------------------------------------------------ W4A16 fixed point under hostile dynamic ranges
+@pytest.mark.parametrize("case", ["outlier", "tiny", "awq_large"])
+def test_w4a16_fixed_point_hostile_ranges(cuda, orc, case):
+    """The W4A16 GEMV carries the activations as per-block 16-bit fixed point (step amax/32767).  Where that differs
+    most from per-element f16 -- one 1e4x outlier per block, values near the f16 subnormal range, a large AWQ
+    multiplier -- the result must still be within 1e-2 of the output RMS of the reference's f32 row dot
+    (q4_dot_row_scalar on the same 16-bit activations)."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    N, K = 1024, 4096
+    x = orc.fill_normal(K, 621, 1)
+    awq = None
+    if case == "outlier":
+        x = x * 1.0e-3
+        x[5::32] = 10.0  # one element 1e4 x its block-mates
+    elif case == "tiny":
+        x = x * 6.0e-5   # f16 subnormals and the smallest normals
+    else:
+        awq = (1.0 + np.abs(orc.fill_normal(K, 621, 3))).astype(np.float32)
+        awq[11::64] = 1.0e3
+    x16 = orc.to_act16(x)
+    W = orc.fill_normal(N * K, 621, 2, scale=0.02).reshape(N, K)
+    blocks = orc.quantize_q4(W)
+    nib, sc = orc.extract_for_gpu(blocks)
+    y = ck.matvec_w4a16_multi(dev(x16, torch.float16).view(1, -1), None if awq is None else dev(awq), [(dev(nib), dev(sc), N)], K,
+                              out_dtype=torch.float32)[0]
+    ref = orc.q4_matvec(blocks, orc.from_act16(x16), awq_inv=awq)
+    assert np.all(np.isfinite(y.cpu().numpy()))
+    assert rel_rms_err(y.cpu().numpy(), ref) < TOL

@@ -31,26 +31,34 @@ def _worker(rank, world, port, q, dims):
         state, imp, plan = build_tp_state(shape, seed, ctx_len, rank, world, fill_kv=False)
         tp = TpContext(rank, world, max_rows=shape.hidden)
         dist.barrier()
-        outs = []
+        # Layer by layer on the SAME input (the tensor-parallel trajectory): the two paths differ only in the order of
+        # the cross-rank f32 sums, and q/k/v are column-parallel, so the K/V caches stay bit-identical; a free-running
+        # comparison would mostly measure how a one-ulp difference is amplified by later int8 code flips.
+        full = imp_full = None
+        if rank == 0:
+            full, imp_full = build_state(shape, seed, ctx_len, fill_kv=False)
         h = ck.fill_normal(shape.hidden, seed, 42, dtype=torch.float16).view(1, -1)
+        worst = 0.0
         for pos in range(3):
             state.set_position(pos)
             for li in range(shape.num_layers):
-                h = tp_layer_forward(h, li, state, state.d_pos.data_ptr(), state.d_seqlen.data_ptr(),
-                                     state.routing.use_w4a8(imp[li]))
+                h_tp = tp_layer_forward(h, li, state, state.d_pos.data_ptr(), state.d_seqlen.data_ptr(),
+                                        state.routing.use_w4a8(imp[li]))
+                if rank == 0:
+                    h_s = gpu_layer_forward_decode(h, li, full, pos, False, imp_full[li])
+                    a, b = h_tp.double().view(-1), h_s.double().view(-1)
+                    worst = max(worst, float((a - b).abs().max() / b.pow(2).mean().sqrt()))
+                h = h_tp
             torch.cuda.synchronize()
-            outs.append(h.clone())
         err = tp.error()
-        result = {"rank": rank, "err": err, "h": outs[-1].view(torch.int16).cpu().numpy()}
+        result = {"rank": rank, "err": err, "h": h.view(torch.int16).cpu().numpy()}
         if rank == 0:
-            full, imp_full = build_state(shape, seed, ctx_len, fill_kv=False)
-            hf = ck.fill_normal(shape.hidden, seed, 42, dtype=torch.float16).view(1, -1)
-            for pos in range(3):
-                for li in range(shape.num_layers):
-                    hf = gpu_layer_forward_decode(hf, li, full, pos, False, imp_full[li])
-            torch.cuda.synchronize()
-            result["single"] = hf.float().cpu().numpy()
+            result["worst_layer_err"] = worst
             result["routes"] = [state.routing.use_w4a8(v) for v in imp]
+            # same inputs, column-parallel q/k/v: rank 0's KV heads hold the rows the single-GPU cache holds
+            kv_same = all(torch.equal(full.kv_cache.k[li][:plan.local_kv_heads], state.kv_cache.k[li]) for li in
+                          range(shape.num_layers))
+            result["kv_same"] = bool(kv_same)
         dist.barrier()
         tp.destroy()
         q.put(result)
@@ -86,6 +94,6 @@ def test_tp2_matches_single_gpu_and_ranks_agree(dims):
     assert np.array_equal(res[0]["h"], res[1]["h"])  # replicated state is bit-identical on every rank
     assert any(res[0]["routes"]) and not all(res[0]["routes"])  # both precisions exercised
     tp = res[0]["h"].view(np.float16).astype(np.float64).reshape(-1)
-    single = res[0]["single"].astype(np.float64).reshape(-1)
     assert np.all(np.isfinite(tp))
-    assert np.max(np.abs(tp - single)) / np.sqrt(np.mean(single**2)) < 1e-2
+    assert res[0]["kv_same"]
+    assert res[0]["worst_layer_err"] < 1e-2  # max|tp - single| / RMS(single), worst layer, same inputs

@@ -47,6 +47,32 @@ def test_noalloc_gemm_matches_workspace_gemm_twice(cuda, orc):
         assert torch.equal(got16, want.to(torch.float16))
 
 
+def test_noalloc_gemm_bf16_input_and_exact_limit(cuda, orc):
+    """bf16 activations (their f16 copy then shares the fixed array with the partial sums) and a shape whose workspace
+    is exactly the 4 MiB limit: both must equal the workspace form bit for bit."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    for (M, N, K, dt, bf) in ((16, 1024, 4096, torch.bfloat16, True), (64, 8192, 4096, torch.float16, False)):
+        W = orc.fill_normal(N * K, 921, 1, scale=0.02).reshape(N, K)
+        nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+        X16 = orc.to_act16(orc.fill_normal(M * K, 921, 2), bf).reshape(M, K)
+        dx, dn, ds = dev(X16, dt), dev(nib), dev(sc)
+        nbytes = ck.gemm_w4a16_scratch_bytes(M, N, K)
+        if not bf:
+            # 2 K slices x 64 x 8192 floats of partial sums = exactly the fixed 4 MiB array (the workspace form also
+            # reserves room for a 16-bit copy of the activations, which f16 input does not use)
+            assert nbytes - M * K * 2 == 4 * 1024 * 1024
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        want = ck.gemm_w4a16(dx, dn, ds, N, K, out_dtype=torch.float32, scratch=scratch)
+        for _call in range(2):
+            got = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+            ck.gemm_w4a16_noalloc(dx, dn, ds, N, K, got)
+            torch.cuda.synchronize()
+            assert ck.gemm_error() == 0
+            assert torch.equal(got, want)
+
+
 def test_noalloc_gemm_refuses_oversized_workspace(cuda):
     from nve_b200 import _ffi
     from nve_b200 import cuda_kernels as ck
