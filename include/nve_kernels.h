@@ -251,6 +251,27 @@ NVE_API int nve_b200_rmsnorm_matvec_w4a8_awq_multi(const void* h, const void* no
                                                    const float* awq_inv, const nve_b200_w4_matrix* mats, int num_mats,
                                                    int K, int out_dtype, nve_stream_t stream);
 
+/* RMSNorm + gate/up GEMV + SiLU*up in ONE launch (src/gpu_layer.rs:937-945 / :977-980 and the RMSNorm in front of
+ * them): a warp item holds gate row i and up row i, so the epilogue writes mid[i] = 16-bit(silu(16-bit gate_i) *
+ * 16-bit up_i) -- the bits of the GEMV with 16-bit outputs followed by nve_silu_mul_f16 -- and the gate / up vectors
+ * never reach memory.  gate->N == up->N (a multiple of 8); the `out` / `residual` members of the two matrices are
+ * ignored; mid_out [N] has the activation type.  awq_inv / awq may be NULL (see nve_b200_quantize_q8_awq for the
+ * W4A8 form). */
+NVE_API int nve_b200_rmsnorm_gateup_silu_w4a8(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                              const float* awq_inv, const nve_b200_w4_matrix* gate,
+                                              const nve_b200_w4_matrix* up, void* mid_out, int K, nve_stream_t stream);
+NVE_API int nve_b200_rmsnorm_gateup_silu_w4a16(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                               const float* awq, const nve_b200_w4_matrix* gate,
+                                               const nve_b200_w4_matrix* up, void* mid_out, int K, nve_stream_t stream);
+/* W4A8 GEMV whose int8 activation codes are produced in the kernel prologue from a 16-bit vector x (every CTA runs
+ * the arithmetic of nve_b200_quantize_q8 / _awq on it): nve_quantize_f16_q8 + nve_matvec_w4a8
+ * (src/gpu_layer.rs:946-947) in one launch, bit-identical to the two.  Output type = x_dtype; residual as in
+ * nve_b200_matvec_w4a8_multi.  The _allreduce form is the tensor-parallel one (see below). */
+NVE_API int nve_b200_quantize_matvec_w4a8_multi(const void* x, int x_dtype, const float* awq_inv,
+                                                const nve_b200_w4_matrix* mats, int num_mats, int K, nve_stream_t stream);
+NVE_API int nve_b200_quantize_matvec_w4a8_allreduce(const void* x, int x_dtype, const float* awq_inv,
+                                                    const nve_b200_w4_matrix* mat, int K, nve_stream_t stream);
+
 /* RoPE of q and the new k at position *d_pos, the KV-cache write of the new row and single-query GQA
  * attention over the first *d_seq_len positions, in one launch (src/gpu_layer.rs:697-735 /
  * src/decode_graph.rs:247-283).  q [nh,hd] and k_new/v_new [nkv,hd] are read, not modified; caches are

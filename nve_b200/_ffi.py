@@ -131,6 +131,10 @@ SIGNATURES = {
     "nve_b200_rmsnorm_matvec_w4a8_multi": (_I, [_P, _P, _F, _I, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a8_awq_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_matvec_w4a16_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
+    "nve_b200_rmsnorm_gateup_silu_w4a8": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
+    "nve_b200_rmsnorm_gateup_silu_w4a16": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
+    "nve_b200_quantize_matvec_w4a8_multi": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _P]),
+    "nve_b200_quantize_matvec_w4a8_allreduce": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _P]),
     "nve_b200_attn_decode_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
     "nve_b200_w4a8_idot": (_I, [_P, _P, _P, _I, _I, _P]),
     "nve_b200_dequant_w4a16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),

@@ -33,6 +33,7 @@
 
 namespace nve {
 
+
 constexpr unsigned kTpSpinLimit = 1u << 22;  // bounded wait for a peer's slot (local polls of >= 32 ns each)
 
 // One warp item: R rows x C consecutive column sets (R * C = 8 blocks per lane), all 16 loads in flight at once.
@@ -45,14 +46,24 @@ template <int R, int C> struct WItem {
 template <int R, int C>
 __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg, int lane, WItem<R, C>& t) {
     t.row0 = tile * R;
-    const uint8_t* nib;
-    const float* sc;
+    const uint8_t* nib0;
+    const float* sc0;
     int lrow, lend;
-    locate(p, t.row0, nib, sc, lrow, lend);
+    if (p.paired) {
+        nib0 = p.nib[0]; sc0 = p.sc[0]; lrow = tile * (R / 2); lend = p.row_end[0];
+    } else {
+        locate(p, t.row0, nib0, sc0, lrow, lend);
+    }
 #pragma unroll
     for (int r = 0; r < R; r++) {
+        const uint8_t* nib = nib0;
+        const float* sc = sc0;
+        int row = lrow + r;
+        if (p.paired && r >= R / 2) {  // second half of the tile: the up rows of the same indices
+            nib = p.nib[1]; sc = p.sc[1]; row = lrow + r - R / 2;
+        }
         // rows past the end of a matrix are clamped for the load and discarded at the store
-        const long long rb = static_cast<long long>(min(lrow + r, lend - 1)) * p.nb;
+        const long long rb = static_cast<long long>(min(row, lend - 1)) * p.nb;
 #pragma unroll
         for (int c = 0; c < C; c++) {
             const int b = (cg * C + c) * kWarp + lane;
@@ -149,6 +160,28 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
         if constexpr (!IDOT) {
             // add the column-group partials of every row of the chunk in ascending order, then store
             const int rows = chunk_tiles * R;
+            if (p.paired) {
+                // gate row and up row of one index sit in the same tile: out[j] = 16-bit silu(16-bit gate) * 16-bit up,
+                // the bits of the GEMV (16-bit outputs) followed by the SiLU*up kernel
+                constexpr int H = R / 2;
+                for (int i = threadIdx.x; i < chunk_tiles * H; i += kGemvThreads) {
+                    const int tl = i / H, j = i - tl * H;
+                    const int idx = (chunk0 + tl) * H + j;
+                    if (idx >= p.row_end[0]) continue;
+                    const float* pg = sm.part + (tl * R + j) * CG;
+                    const float* pu = sm.part + (tl * R + H + j) * CG;
+                    float yg = pg[0], yu = pu[0];
+                    for (int c = 1; c < CG; c++) {
+                        yg = __fadd_rn(yg, pg[c]);
+                        yu = __fadd_rn(yu, pu[c]);
+                    }
+                    if constexpr (ODT != NVE_DT_F32) {
+                        const float g = Act16<ODT>::to_f32(Act16<ODT>::from_f32(yg));
+                        const float u = Act16<ODT>::to_f32(Act16<ODT>::from_f32(yu));
+                        store_out<ODT>(p.out[0], idx, silu_mul_f32(g, u));
+                    }
+                }
+            } else
             for (int i = threadIdx.x; i < rows; i += kGemvThreads) {
                 const int grow = chunk0 * R + i;
                 if (grow >= p.n_total) continue;
@@ -332,7 +365,7 @@ static bool all_aligned(const GemvParams& p, int num_mats, int planes, int pro) 
         if (!aligned(p.nib[m], 16)) return false;
     if (pro == 1 && !aligned(p.norm_w, 16)) return false;
     if (planes == 1 && pro == 0) return aligned(p.xq, 16);
-    return aligned(p.x16, 16);
+    return aligned(p.x16, 16);  // PRO 1 and 2 and W4A16 read the 16-bit vector
 }
 
 template <int PLANES, int XDT, int ODT, int PRO> static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
@@ -384,6 +417,7 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.nb = K / kBlockK;
     p.S = (p.nb + kWarp - 1) / kWarp;
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.xlo = nullptr; p.awq = nullptr; p.idot = nullptr;
+    p.paired = 0;
     p.norm_w = nullptr; p.eps = 0.0f;
     p.tp.world = 0; p.tp.rank = 0; p.tp.rows_cap = 0; p.tp.err = nullptr;
     p.tp.counter = nullptr;
@@ -499,6 +533,82 @@ extern "C" int nve_b200_rmsnorm_matvec_w4a16_multi(const void* h, const void* no
     if (act_dtype == NVE_DT_F16) return dispatch_out<2, NVE_DT_F16, 1>(p, num_mats, out_dtype, cs);
     if (act_dtype == NVE_DT_BF16) return dispatch_out<2, NVE_DT_BF16, 1>(p, num_mats, out_dtype, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+static int attach_tp(GemvParams& p);
+
+// ---- gate/up with SiLU*up in the epilogue, down with the quantiser in the prologue (five launches per layer) ----
+// Only the 16-bit output type equal to the activation type is built (the form the decode step uses).
+template <int PLANES, int XDT, int PRO> static int dispatch_same_dt(const GemvParams& p, int num_mats, cudaStream_t st) {
+    return dispatch_aligned<PLANES, XDT, XDT, PRO>(p, num_mats, st);
+}
+
+static int fill_gateup(GemvParams& p, const nve_b200_w4_matrix* gate, const nve_b200_w4_matrix* up, void* mid_out, int K) {
+    if (!gate || !up || !mid_out) return NVE_ERR_BAD_POINTER;
+    if (gate->N != up->N || (gate->N % 8) != 0) return NVE_ERR_BAD_SHAPE;
+    nve_b200_w4_matrix m[2] = {*gate, *up};
+    m[0].out = mid_out; m[1].out = mid_out;  // the per-matrix outputs are not written in this form
+    m[0].residual = nullptr; m[1].residual = nullptr;
+    int st = fill_params(p, m, 2, K);
+    if (st != NVE_OK) return st;
+    p.paired = 1;
+    return NVE_OK;
+}
+
+extern "C" int nve_b200_rmsnorm_gateup_silu_w4a8(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                 const float* awq_inv, const nve_b200_w4_matrix* gate,
+                                                 const nve_b200_w4_matrix* up, void* mid_out, int K, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_gateup(p, gate, up, mid_out, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq_inv;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<1, NVE_DT_F16, 1>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<1, NVE_DT_BF16, 1>(p, 2, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+extern "C" int nve_b200_rmsnorm_gateup_silu_w4a16(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                  const float* awq, const nve_b200_w4_matrix* gate,
+                                                  const nve_b200_w4_matrix* up, void* mid_out, int K, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_gateup(p, gate, up, mid_out, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<2, NVE_DT_F16, 1>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<2, NVE_DT_BF16, 1>(p, 2, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+static int quantize_matvec_w4a8(const void* x, int x_dtype, const float* awq_inv, const nve_b200_w4_matrix* mats, int num_mats,
+                                int K, bool allreduce, cudaStream_t cs) {
+    GemvParams p;
+    int st = fill_params(p, mats, num_mats, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!x) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = x;
+    p.awq = awq_inv;
+    if (allreduce) {
+        if (!all_aligned(p, num_mats, 1, 2)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+        st = attach_tp(p);
+        if (st != NVE_OK) return set_status(st);
+    }
+    if (x_dtype == NVE_DT_F16) return dispatch_same_dt<1, NVE_DT_F16, 2>(p, num_mats, cs);
+    if (x_dtype == NVE_DT_BF16) return dispatch_same_dt<1, NVE_DT_BF16, 2>(p, num_mats, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+extern "C" int nve_b200_quantize_matvec_w4a8_multi(const void* x, int x_dtype, const float* awq_inv,
+                                                   const nve_b200_w4_matrix* mats, int num_mats, int K, nve_stream_t stream) {
+    return quantize_matvec_w4a8(x, x_dtype, awq_inv, mats, num_mats, K, false, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nve_b200_quantize_matvec_w4a8_allreduce(const void* x, int x_dtype, const float* awq_inv,
+                                                       const nve_b200_w4_matrix* mat, int K, nve_stream_t stream) {
+    return quantize_matvec_w4a8(x, x_dtype, awq_inv, mat, 1, K, true, static_cast<cudaStream_t>(stream));
 }
 
 // ---- tensor-parallel GEMVs: y = all-reduce over the ranks of (W_shard . x_shard), optional residual ----------

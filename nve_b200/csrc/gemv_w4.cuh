@@ -43,6 +43,8 @@ struct GemvParams {
     const void* norm_w; // RMSNorm weight of the fused prologue (16-bit, same type as x16)
     float eps;
     int32_t* idot;      // debug: per-block integer dots [n_total, nb]
+    int paired;         // gate/up with SiLU*up in the epilogue: a tile holds R/2 gate rows (matrix 0) and the R/2 up
+                        // rows (matrix 1) of the same indices; out[0] receives silu(gate) * up, [row_end[0]] values
     TpDev tp;           // all-reduce of the (single) output over the tensor-parallel ranks
 };
 
@@ -272,6 +274,7 @@ __device__ __forceinline__ void load_norm_regs(const GemvParams& p, NormRegs& nr
     }
 }
 // Stage the activations.  PRO = 0: the caller's vector (int8 codes for W4A8, 16-bit values for W4A16).
+// PRO = 2: the caller's 16-bit vector, quantised here (W4A8: the int8 codes of the stand-alone quantiser).
 // PRO = 1: RMSNorm of the caller's 16-bit vector first, in the library's fixed order (256 threads; thread t
 // adds x^2 over the 8-element chunks t, t+256, ... ; xor butterfly per warp; warp sums added in ascending
 // order; r = 1/sqrt(sum/n + eps); o = round16((x*r)*w)), then quantised exactly as the separate kernels do.

@@ -492,6 +492,37 @@ def rmsnorm_matvec_w4a16_multi(h: Tensor, norm_weight: Tensor, eps: float, awq: 
     return list(outs)
 
 
+def rmsnorm_gateup_silu(h: Tensor, norm_weight: Tensor, eps: float, awq: Optional[Tensor], gate, up, k: int, use_w4a8: bool,
+                        mid: Optional[Tensor] = None) -> Tensor:
+    """RMSNorm + gate/up GEMV + SiLU*up in one launch; gate / up are (nibbles, scales, n) triples; returns mid [1, n]."""
+    n = gate[2]
+    mid = torch.empty((1, n), dtype=h.dtype, device=h.device) if mid is None else mid
+    g = W4Matrix(_ptr(gate[0], torch.uint8), _ptr(gate[1], torch.float32), None, None, n)
+    u = W4Matrix(_ptr(up[0], torch.uint8), _ptr(up[1], torch.float32), None, None, up[2])
+    fn = "nve_b200_rmsnorm_gateup_silu_w4a8" if use_w4a8 else "nve_b200_rmsnorm_gateup_silu_w4a16"
+    _ffi.check(fn, getattr(_lib(), fn)(_ptr(h, (torch.float16, torch.bfloat16), "h"), _ptr(norm_weight, h.dtype), float(eps),
+                                       _dt(h), _ptr(awq, torch.float32), C.byref(g), C.byref(u), _ptr(mid, h.dtype), k,
+                                       stream()))
+    return mid
+
+
+def quantize_matvec_w4a8_multi(x: Tensor, awq_inv: Optional[Tensor], weights: Sequence, k: int,
+                               outs: Optional[Sequence[Tensor]] = None, residuals=None, allreduce: bool = False):
+    """int8 quantisation of the 16-bit vector x in the GEMV prologue + W4A8 GEMV (outputs of x's type)."""
+    if outs is None:
+        outs = [torch.empty((1, n), dtype=x.dtype, device=x.device) for (_, _, n) in weights]
+    arr = _mats(weights, outs, residuals, x.dtype)
+    if allreduce:
+        _ffi.check("nve_b200_quantize_matvec_w4a8_allreduce",
+                   _lib().nve_b200_quantize_matvec_w4a8_allreduce(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
+                                                                  _ptr(awq_inv, torch.float32), arr, k, stream()))
+    else:
+        _ffi.check("nve_b200_quantize_matvec_w4a8_multi",
+                   _lib().nve_b200_quantize_matvec_w4a8_multi(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
+                                                              _ptr(awq_inv, torch.float32), arr, len(weights), k, stream()))
+    return list(outs)
+
+
 def attn_decode_fused(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, cos_tab: Tensor,
                       sin_tab: Tensor, d_pos: int, d_seq_len: int, out: Tensor, num_heads: int, num_kv_heads: int,
                       head_dim: int, max_seq_len: int, scale: float, out_q: Optional[Tensor] = None,

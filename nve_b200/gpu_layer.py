@@ -140,6 +140,9 @@ class GpuInferenceState:
     rope_sin: Tensor
     routing: RoutingConfig = field(default_factory=RoutingConfig)
     fused: bool = True
+    # fused schedule only: SiLU*up in the gate/up epilogue and the quantiser in the down prologue (five launches per
+    # layer instead of six; same bits)
+    fuse_silu: bool = False
     # device scalars for position / valid length of the eager path
     d_pos: Optional[Tensor] = None
     d_seqlen: Optional[Tensor] = None
@@ -282,6 +285,12 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
                              hd, max_seq, scale, out_q=xq_a, out_scales=xs_a)
         gemv8 = ck.matvec_w4a8_allreduce if allreduce else ck.matvec_w4a8_multi
         gemv8(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        if state.fuse_silu:
+            ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, None, w.gate_proj.triple(), w.up_proj.triple(), w.gate_proj.k,
+                                   True, mid=gate)
+            ck.quantize_matvec_w4a8_multi(gate, None, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1],
+                                          allreduce=allreduce)
+            return h1
         ck.rmsnorm_matvec_w4a8_multi(h1, w.post_attn_norm, eps, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
                                      outs=[gate, up])
         ck.silu_mul_quantize_q8(gate, up, xq=xq_f, scales=xs_f)
@@ -292,6 +301,11 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
                              hd, max_seq, scale)
         gemv16 = ck.matvec_w4a16_allreduce if allreduce else ck.matvec_w4a16_multi
         gemv16(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        if state.fuse_silu:
+            ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales, w.gate_proj.triple(),
+                                   w.up_proj.triple(), w.gate_proj.k, False, mid=gate)
+            gemv16(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
+            return h1
         ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
                                       [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
         # the fixed-point form of silu(gate)*up is produced once here instead of by every CTA of the GEMV

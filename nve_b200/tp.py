@@ -15,6 +15,7 @@ order differs.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -118,6 +119,9 @@ def build_tp_state(shape: ModelShape, seed: int, context: int, rank: int, world:
     cos, sin = rope_tables(shape.head_dim, context, 10000.0, device)
     norm, routing = seeded_routing(shape.num_layers, seed)
     state = GpuInferenceState(lw, kv, plan.local_heads, plan.local_kv_heads, shape.head_dim, 1e-5, cos, sin, routing, True)
+    # With the FFN split over the ranks the quantiser in the down prologue handles only ffn / world values, so the
+    # five-launch layer (SiLU*up in the gate/up epilogue) saves a whole dependent launch; NVE_B200_FUSE_SILU=0 keeps six.
+    state.fuse_silu = os.environ.get("NVE_B200_FUSE_SILU", "1") != "0"
     return state, norm[:layers], plan
 
 

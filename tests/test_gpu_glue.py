@@ -376,3 +376,70 @@ def test_graph_replay_equals_eager_mixed_routing(cuda, orc):
     finally:
         graph.destroy()
     assert not ck.graph_ready()
+
+
+# ------------------------------------------------------------------ five launches per layer
+@pytest.mark.parametrize("route", ["w4a8", "w4a16"])
+@pytest.mark.parametrize("K,F", [(4096, 1024), (2048, 512), (1024, 264), (512, 96)])
+def test_gateup_silu_epilogue_equals_gemv_plus_silu(cuda, orc, route, K, F):
+    """RMSNorm + gate/up GEMV + SiLU*up in one launch == RMSNorm-fused gate/up GEMV followed by the SiLU*up kernel, bit
+    for bit (2, 4 and 8 rows per item; F = 264 and 96 leave ragged last tiles)."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    mats = []
+    for i in range(2):
+        W = orc.fill_normal(F * K, 771, i, scale=0.02).reshape(F, K)
+        nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+        mats.append((dev(nib), dev(sc), F))
+    h = dev(orc.to_act16(orc.fill_normal(K, 771, 9) * 3.0), torch.float16).view(1, -1)
+    w = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(K, 771, 10)), torch.float16)
+    if route == "w4a8":
+        gate, up = ck.rmsnorm_matvec_w4a8_multi(h, w, 1e-5, mats, K)
+    else:
+        gate, up = ck.rmsnorm_matvec_w4a16_multi(h, w, 1e-5, None, mats, K)
+    ck.silu_mul_inplace(gate, up)
+    mid = ck.rmsnorm_gateup_silu(h, w, 1e-5, None, mats[0], mats[1], K, route == "w4a8")
+    assert torch.equal(mid, gate)
+
+
+def test_quantizing_prologue_equals_quantiser_plus_gemv(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    N, K = 512, 14336
+    W = orc.fill_normal(N * K, 781, 1, scale=0.02).reshape(N, K)
+    nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+    mats = [(dev(nib), dev(sc), N)]
+    x = dev(orc.to_act16(orc.fill_normal(K, 781, 2)), torch.float16).view(1, -1)
+    res = dev(orc.to_act16(orc.fill_normal(N, 781, 3)), torch.float16).view(1, -1)
+    xq, xs = ck.quantize_f16_q8(x)
+    want = ck.matvec_w4a8_multi(xq, xs, mats, K, residuals=[res])[0]
+    got = ck.quantize_matvec_w4a8_multi(x, None, mats, K, residuals=[res])[0]
+    assert torch.equal(got, want)
+
+
+def test_five_launch_graph_equals_six_launch_graph(cuda, orc):
+    from nve_b200.decode_graph import StaticDecodeGraph
+
+    torch = cuda
+    hidden, ffn, nh, nkv, hd, layers, max_seq = 2048, 8192, 32, 8, 64, 4, 16
+    imp = [0.1, 0.9, 0.4, 1.0]
+    outs = []
+    for fuse in (False, True):
+        st = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 791, True)
+        st.fuse_silu = fuse
+        graph = StaticDecodeGraph(st, hidden, ffn, imp)
+        graph.capture()
+        assert graph.launches_per_replay == (5 if fuse else 6) * layers
+        try:
+            res = []
+            for pos in range(3):
+                h_in = dev(orc.to_act16(orc.fill_normal(hidden, 792, pos)), torch.float16).view(1, -1)
+                res.append(graph.replay(h_in, pos))
+                torch.cuda.synchronize()
+            outs.append(res)
+        finally:
+            graph.destroy()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
