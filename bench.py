@@ -307,7 +307,7 @@ def gemv_shape_table(torch, ck, state, s, hbuf, tmp, shape, peak):
 
 
 def config1_entry(torch, ck, peak):
-    """BASELINE config 1: a single W4A16 GEMV of the Llama-3.2-1B up_proj shape (8192 x 2048), 16 distinct matrices
+    """Measurement configuration 1: a single W4A16 GEMV of the Llama-3.2-1B up_proj shape (8192 x 2048), 16 distinct matrices
     rotated (168 MB in total, larger than L2)."""
     from nve_b200.bench_random import make_w4, w4_bytes
 
@@ -330,7 +330,7 @@ def config1_entry(torch, ck, peak):
 
 
 def config2_entry(torch, ck, peak):
-    """BASELINE config 2: the Llama-3.2-1B layer GEMV set on the W4A8 route, 16 layers (0.61 GB of weights)."""
+    """Measurement configuration 2: the Llama-3.2-1B layer GEMV set on the W4A8 route, 16 layers (0.61 GB of weights)."""
     from nve_b200.bench_random import SHAPES, build_graph, build_state, layer_weight_bytes
     from nve_b200.gpu_layer import RoutingConfig
 
@@ -372,7 +372,7 @@ def config2_entry(torch, ck, peak):
 
 
 def config5_entry(torch, ck, peak, steps: int):
-    """BASELINE config 5 at one GPU: the Llama-3-70B-shaped stack (42.8 GB of packed weights per token), batch 1."""
+    """Measurement configuration 5 at one GPU: the Llama-3-70B-shaped stack (42.8 GB of packed weights per token), batch 1."""
     from nve_b200.bench_random import SHAPES, build_graph, build_state, decode_bytes_per_token
 
     shape = SHAPES["70b"]
@@ -398,7 +398,7 @@ def config5_entry(torch, ck, peak, steps: int):
 
 
 def gemm_batch_table(torch, ck, state, shape, peak):
-    """BASELINE config 4: the batched W4A16 path at batch 1 (GEMV) and 8..64 (tcgen05 GEMM) on the four 8B
+    """Measurement configuration 4: the batched W4A16 path at batch 1 (GEMV) and 8..64 (tcgen05 GEMM) on the four 8B
     projection groups, rotating over the 32 layers' weights."""
     from nve_b200.bench_random import proj_dims, w4_bytes
 
@@ -601,7 +601,7 @@ def run_ours(args) -> None:
             act_bytes += (ks + ks // 8 if (routes[li] and ks != shape.hidden) else 2 * ks) + 2 * ns
     gemv_bytes = shape.num_layers * sum(w4_bytes(n, k) for n, k in dims.values()) + act_bytes
     achieved = gemv_bytes / (ms_gemv * 1e-3) / 1e9
-    # DRAM bytes per launch from the ncu captures under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of a
+    # DRAM bytes per launch from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum of a
     # GEMV launch on a > L2 case): 1.0136 x the algorithmic bytes; every block is touched once, so the traffic of a
     # launch grows with its matrix and the ratio carries over to the average launch of the step.
     traffic_ratio = 1.0136
@@ -640,7 +640,7 @@ def run_ours(args) -> None:
         table, gerr = gemm_batch_table(torch, ck, state, shape, peak)
         extras["gemm_batch"] = {"rows": table, "error_word": gerr,
                                 "tensor_pipe_pct": {"value": 6.3, "source": "sm__pipe_tensor_cycles_active of the gate/up "
-                                                    "pair at batch 16 in the ncu summary of the batched GEMM (profiles/)"}}
+                                                    "pair at batch 16 in an ncu --set full capture of the batched GEMM"}}
         del state, graph, pers
         torch.cuda.empty_cache()
         extras["config1"] = config1_entry(torch, ck, peak)

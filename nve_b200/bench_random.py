@@ -173,10 +173,64 @@ def _main() -> None:
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
     ap.add_argument("--batch", type=int, default=1, help="> 1: the tcgen05 batched W4A16 GEMM with this many rows of X")
+    ap.add_argument("--persistent", action="store_true",
+                    help="run whole decode steps of a --layers deep stack through the one-kernel form instead of one group")
+    ap.add_argument("--context", type=int, default=1024)
+    ap.add_argument("--trace", action="store_true",
+                    help="--persistent: print the per-phase time stamps of CTA 0 (barrier wait / staging / run, us)")
+    ap.add_argument("--prefetch", type=int, default=-1, help="--persistent: L2 prefetch distance in items per warp")
     a = ap.parse_args()
-    from .decode_graph import CapturedSequence
+    from .decode_graph import CapturedSequence, PersistentDecode
 
     ck.set_pdl(bool(a.pdl))
+    if a.persistent:
+        import dataclasses
+
+        shape = dataclasses.replace(SHAPES[a.model], num_layers=a.layers)
+        state, imp = build_state(shape, 1, a.context, max_seq=a.context)
+        if a.prefetch >= 0:
+            ck.decode_step_set_prefetch(a.prefetch)
+        pers = PersistentDecode(state, shape.hidden, shape.ffn, imp)
+        state.set_position(a.context - 1)
+        h0 = ck.fill_normal(shape.hidden, 1, 42, dtype=torch.float16).view(1, -1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(a.reps + 1):
+            if i == 1:
+                e0.record()
+            pers.hidden_buf.copy_(h0)
+            pers.step(state.d_pos.data_ptr(), state.d_seqlen.data_ptr())
+        e1.record()
+        torch.cuda.synchronize()
+        nbytes = decode_bytes_per_token(shape, a.context)
+        us = e0.elapsed_time(e1) * 1e3 / max(1, a.reps)
+        print(f"{a.model} persistent step, {a.layers} layers, context {a.context}: {us:.1f} us/step, "
+              f"{nbytes / us / 1e3:.1f} GB/s ({nbytes / 1e6:.1f} MB), error word {pers.error()}")
+        if a.trace:
+            from . import _ffi
+
+            phases = a.layers * 5
+            trace = torch.zeros(2 * phases * 4, dtype=torch.int64, device="cuda")
+            _ffi.load().nve_b200_decode_step_set_trace(trace.data_ptr())
+            for _ in range(2):
+                pers.hidden_buf.copy_(h0)
+                pers.step(state.d_pos.data_ptr(), state.d_seqlen.data_ptr())
+            torch.cuda.synchronize()
+            _ffi.load().nve_b200_decode_step_set_trace(None)
+            t = trace.cpu().view(2, phases, 4).numpy()
+            names = ["qkv", "attn", "o", "gateup", "down"]
+            print("per phase: barrier wait / activation staging / run (us); CTA 0, then the last CTA")
+            for cta in range(2):
+                for li in range(a.layers):
+                    row = []
+                    for k in range(5):
+                        s4 = t[cta, li * 5 + k]
+                        stg = (s4[2] - s4[1]) / 1e3 if s4[2] else 0.0
+                        run = (s4[3] - (s4[2] if s4[2] else s4[1])) / 1e3
+                        row.append(f"{names[k]} {(s4[1] - s4[0]) / 1e3:.1f}/{stg:.1f}/{run:.1f}")
+                    total = (t[cta, li * 5 + 4][3] - t[cta, li * 5][0]) / 1e3
+                    print(f"CTA {'0' if cta == 0 else 'last'} layer {li} ({'W4A8' if pers.routes[li] else 'W4A16'}) "
+                          f"{total:.1f} us: " + "  ".join(row))
+        return
     ns, k = gemv_groups(SHAPES[a.model])[a.group]
     ws = [[make_w4(n, k, 1, 100 * li + j) for j, n in enumerate(ns)] for li in range(a.layers)]
     x = ck.fill_normal(k, 1, 999, dtype=torch.float16)

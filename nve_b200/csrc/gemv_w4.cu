@@ -43,13 +43,13 @@ template <int R, int C> struct WItem {
     int row0;  // global first row
 };
 
-template <int R, int C>
+template <int R, int C, bool PAIR>
 __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg, int lane, WItem<R, C>& t) {
     t.row0 = tile * R;
     const uint8_t* nib0;
     const float* sc0;
     int lrow, lend;
-    if (p.paired) {
+    if constexpr (PAIR) {
         nib0 = p.nib[0]; sc0 = p.sc[0]; lrow = tile * (R / 2); lend = p.row_end[0];
     } else {
         locate(p, t.row0, nib0, sc0, lrow, lend);
@@ -59,7 +59,7 @@ __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg,
         const uint8_t* nib = nib0;
         const float* sc = sc0;
         int row = lrow + r;
-        if (p.paired && r >= R / 2) {  // second half of the tile: the up rows of the same indices
+        if (PAIR && r >= R / 2) {  // second half of the tile: the up rows of the same indices
             nib = p.nib[1]; sc = p.sc[1]; row = lrow + r - R / 2;
         }
         // rows past the end of a matrix are clamped for the load and discarded at the store
@@ -78,7 +78,7 @@ __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg,
     }
 }
 
-template <int PLANES, int XDT, int ODT, bool IDOT, int PRO, int R, int C>
+template <int PLANES, int XDT, int ODT, bool IDOT, int PRO, int R, int C, bool PAIR = false>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -97,8 +97,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     WItem<R, C> it;
     int chunk0 = tile_begin;
     int chunk_tiles = min(chunk_tiles_max, tile_end - chunk0);
-    int q = warp;  // item index inside the chunk: tile q / CG, column group q % CG
-    if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
+    // item index inside the chunk: q = tile * CG + column group; q advances by W per step, so (tile, column group) are
+    // carried along instead of divided out for every item
+    const int step_t = W / CG, step_c = W - step_t * CG;
+    const int tl0 = warp / CG, cg0 = warp - tl0 * CG;
+    int q = warp, tl = tl0, cg = cg0;
+    if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C, PAIR>(p, chunk0 + tl, cg, lane, it);
 
     NormRegs nr;
     if constexpr (PRO == 1) load_norm_regs(p, nr);  // static data: fetched before the dependency wait
@@ -118,7 +122,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     while (chunk_tiles > 0) {
         const int n_items = chunk_tiles * CG;
         while (q < n_items) {
-            const int tl = q / CG, cg = q - tl * CG;
             float a[R];
 #pragma unroll
             for (int c = 0; c < C; c++) {
@@ -149,18 +152,25 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
             }
             // issue the next item's loads before reducing this one
             const int qn = q + W;
-            if (qn < n_items) load_item<R, C>(p, chunk0 + qn / CG, qn % CG, lane, it);
+            int tln = tl + step_t, cgn = cg + step_c;
+            if (cgn >= CG) {
+                cgn -= CG;
+                tln++;
+            }
+            if (qn < n_items) load_item<R, C, PAIR>(p, chunk0 + tln, cgn, lane, it);
             if constexpr (!IDOT) {
                 warp_sum_multi<R>(a, lane);
                 if (multi_row_writer<R>(lane)) sm.part[(tl * R + multi_row_of<R>(lane)) * CG + cg] = a[0];
             }
             q = qn;
+            tl = tln;
+            cg = cgn;
         }
         __syncthreads();
         if constexpr (!IDOT) {
             // add the column-group partials of every row of the chunk in ascending order, then store
             const int rows = chunk_tiles * R;
-            if (p.paired) {
+            if constexpr (PAIR) {
                 // gate row and up row of one index sit in the same tile: out[j] = 16-bit silu(16-bit gate) * 16-bit up,
                 // the bits of the GEMV (16-bit outputs) followed by the SiLU*up kernel
                 constexpr int H = R / 2;
@@ -213,7 +223,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
         chunk_tiles = min(chunk_tiles_max, tile_end - chunk0);
         __syncthreads();
         q = warp;
-        if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C>(p, chunk0 + q / CG, q % CG, lane, it);
+        tl = tl0;
+        cg = cg0;
+        if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C, PAIR>(p, chunk0 + tl, cg, lane, it);
     }
 
     if constexpr (!IDOT) {
@@ -368,12 +380,13 @@ static bool all_aligned(const GemvParams& p, int num_mats, int planes, int pro) 
     return aligned(p.x16, 16);  // PRO 1 and 2 and W4A16 read the 16-bit vector
 }
 
-template <int PLANES, int XDT, int ODT, int PRO> static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
+template <int PLANES, int XDT, int ODT, int PRO, bool PAIR = false>
+static int dispatch_aligned(const GemvParams& p, int num_mats, cudaStream_t st) {
     if (all_aligned(p, num_mats, PLANES, PRO)) {
         // 8 blocks per lane and item: 2 rows x 4 column sets, or more rows when a row has fewer column sets
-        if (p.S >= 3) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 2, 4>, p, PLANES, 2, st);
-        if (p.S == 2) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 4, 2>, p, PLANES, 4, st);
-        return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 8, 1>, p, PLANES, 8, st);
+        if (p.S >= 3) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 2, 4, PAIR>, p, PLANES, 2, st);
+        if (p.S == 2) return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 4, 2, PAIR>, p, PLANES, 4, st);
+        return launch_gemv(gemv_w4_kernel<PLANES, XDT, ODT, false, PRO, 8, 1, PAIR>, p, PLANES, 8, st);
     }
     if constexpr (PRO != 0) {
         return set_status(NVE_ERR_BAD_ALIGNMENT);  // the fused prologue needs 16-byte aligned vectors
@@ -539,8 +552,9 @@ static int attach_tp(GemvParams& p);
 
 // ---- gate/up with SiLU*up in the epilogue, down with the quantiser in the prologue (five launches per layer) ----
 // Only the 16-bit output type equal to the activation type is built (the form the decode step uses).
-template <int PLANES, int XDT, int PRO> static int dispatch_same_dt(const GemvParams& p, int num_mats, cudaStream_t st) {
-    return dispatch_aligned<PLANES, XDT, XDT, PRO>(p, num_mats, st);
+template <int PLANES, int XDT, int PRO, bool PAIR = false>
+static int dispatch_same_dt(const GemvParams& p, int num_mats, cudaStream_t st) {
+    return dispatch_aligned<PLANES, XDT, XDT, PRO, PAIR>(p, num_mats, st);
 }
 
 static int fill_gateup(GemvParams& p, const nve_b200_w4_matrix* gate, const nve_b200_w4_matrix* up, void* mid_out, int K) {
@@ -564,8 +578,8 @@ extern "C" int nve_b200_rmsnorm_gateup_silu_w4a8(const void* h, const void* norm
     if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
     p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq_inv;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<1, NVE_DT_F16, 1>(p, 2, cs);
-    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<1, NVE_DT_BF16, 1>(p, 2, cs);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<1, NVE_DT_F16, 1, true>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<1, NVE_DT_BF16, 1, true>(p, 2, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
 }
 
@@ -578,8 +592,8 @@ extern "C" int nve_b200_rmsnorm_gateup_silu_w4a16(const void* h, const void* nor
     if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
     p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<2, NVE_DT_F16, 1>(p, 2, cs);
-    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<2, NVE_DT_BF16, 1>(p, 2, cs);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<2, NVE_DT_F16, 1, true>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<2, NVE_DT_BF16, 1, true>(p, 2, cs);
     return set_status(NVE_ERR_BAD_DTYPE);
 }
 

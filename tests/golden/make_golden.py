@@ -117,7 +117,7 @@ def main() -> None:
     scores = o.fill_uniform(32, SEED, 8).astype(np.float64)
     out.update(r_scores=scores, r_norm=o.normalize_importance(scores))
 
-    # ---- case 5: BASELINE config 1 (W4A16 GEMV, Llama-3.2-1B up_proj 8192 x 2048), digest + head only
+    # ---- case 5: measurement configuration 1 (W4A16 GEMV, Llama-3.2-1B up_proj 8192 x 2048), digest + head only
     Wc = o.fill_normal(8192 * 2048, SEED, 10, scale=0.02).reshape(8192, 2048)
     xc = o.fill_normal(2048, SEED, 11)
     cb = o.quantize_q4(Wc)

@@ -146,7 +146,7 @@ def test_w4a16_reference_entry_points(cuda, orc, golden):
 
 
 def test_config1_w4a16_up_proj(cuda, orc, golden):
-    """BASELINE config 1: x [1x2048], W [8192x2048] ~N(0,0.02) through the reference quantizer, y [1x8192]."""
+    """Measurement configuration 1: x [1x2048], W [8192x2048] ~N(0,0.02) through the reference quantizer, y [1x8192]."""
     import hashlib
 
     from nve_b200 import cuda_kernels as ck
@@ -232,7 +232,7 @@ def test_bad_shapes_are_rejected(cuda):
         ck.fused_matvec_w4a16(x, nib, sc, None, 4, 48)
 
 
-# ------------------------------------------------------------------ full-size properties (BASELINE 8B shapes)
+# ------------------------------------------------------------------ full-size properties (Llama-3.1-8B shapes)
 def test_full_size_properties_8b_gate(cuda, orc):
     """14336 x 4096 (8B gate/up): sampled rows against the oracle, exact homogeneity, zero input."""
     from nve_b200 import cuda_kernels as ck

@@ -47,7 +47,7 @@ def test_golden_glue(orc, golden):
 
 
 def test_golden_config1_digest(orc, golden):
-    """BASELINE config 1 (8192 x 2048 W4A16 GEMV) regenerated from the seed: digests of weights and outputs."""
+    """Measurement configuration 1 (8192 x 2048 W4A16 GEMV) regenerated from the seed: digests of weights and outputs."""
     seed = int(golden["seed"][0])
     W = orc.fill_normal(8192 * 2048, seed, 10, scale=0.02).reshape(8192, 2048)
     x16 = orc.to_act16(orc.fill_normal(2048, seed, 11))
