@@ -83,6 +83,21 @@ __device__ __forceinline__ float ld_stream_f32(const void* p) {
     return v;
 }
 
+// The same loads at a compile-time byte offset from a base address: the offset goes into the instruction's immediate
+// field, so the loads of one row of an item share one 64-bit address computation.
+template <int OFF> __device__ __forceinline__ uint4 ld_stream_u4_off(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ float ld_stream_f32_off(const void* p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1+%2];" : "=f"(v) : "l"(p), "n"(OFF));
+    return v;
+}
+
 // dp4a with an unsigned first operand (raw nibbles 0..15) and a signed second operand (int8 codes).
 __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
     int d;

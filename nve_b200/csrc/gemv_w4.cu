@@ -29,6 +29,8 @@
 //     in ascending order.
 //
 // Algorithmic bytes per launch: N*K/2 nibbles + N*K/8 scale bytes + activations + outputs.
+#include <type_traits>
+
 #include "gemv_w4.cuh"
 
 namespace nve {
@@ -43,7 +45,9 @@ template <int R, int C> struct WItem {
     int row0;  // global first row
 };
 
-template <int R, int C, bool PAIR>
+// EVEN: every row is a whole number of column groups of C full column sets (K % (1024 * C) == 0), so no lane and no
+// column set of an item is ever idle and the bounds checks drop out.
+template <int R, int C, bool PAIR, bool EVEN = false>
 __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg, int lane, WItem<R, C>& t) {
     t.row0 = tile * R;
     const uint8_t* nib0;
@@ -64,15 +68,35 @@ __device__ __forceinline__ void load_item(const GemvParams& p, int tile, int cg,
         }
         // rows past the end of a matrix are clamped for the load and discarded at the store
         const long long rb = static_cast<long long>(min(row, lend - 1)) * p.nb;
+        // a full column group of full column sets (always so with EVEN; otherwise e.g. 3 of the 4 groups of K = 14336)
+        if (EVEN || ((p.nb & (kWarp - 1)) == 0 && (cg + 1) * C <= p.S)) {
+            // one address per row; the C column sets of the item sit 512 (nibbles) / 128 (scales) bytes apart
+            const long long b0 = rb + cg * (C * kWarp) + lane;
+            const uint8_t* nrow = nib + b0 * 16;
+            const float* srow = sc + b0;
+            t.w[0][r] = ld_stream_u4_off<0>(nrow);
+            t.s[0][r] = ld_stream_f32_off<0>(srow);
+            if constexpr (C > 1) {
+                t.w[1][r] = ld_stream_u4_off<512>(nrow);
+                t.s[1][r] = ld_stream_f32_off<128>(srow);
+            }
+            if constexpr (C > 2) {
+                t.w[2][r] = ld_stream_u4_off<1024>(nrow);
+                t.s[2][r] = ld_stream_f32_off<256>(srow);
+                t.w[3][r] = ld_stream_u4_off<1536>(nrow);
+                t.s[3][r] = ld_stream_f32_off<384>(srow);
+            }
+        } else {
 #pragma unroll
-        for (int c = 0; c < C; c++) {
-            const int b = (cg * C + c) * kWarp + lane;
-            if (b < p.nb) {
-                t.w[c][r] = ld_stream_u4(nib + (rb + b) * 16);
-                t.s[c][r] = ld_stream_f32(sc + rb + b);
-            } else {
-                t.w[c][r] = make_uint4(0, 0, 0, 0);
-                t.s[c][r] = 0.0f;
+            for (int c = 0; c < C; c++) {
+                const int b = (cg * C + c) * kWarp + lane;
+                if (b < p.nb) {
+                    t.w[c][r] = ld_stream_u4(nib + (rb + b) * 16);
+                    t.s[c][r] = ld_stream_f32(sc + rb + b);
+                } else {
+                    t.w[c][r] = make_uint4(0, 0, 0, 0);
+                    t.s[c][r] = 0.0f;
+                }
             }
         }
     }
@@ -119,13 +143,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     // offset of the plane [parity][source = this rank] inside any rank's buffer
     const size_t tp_plane = (static_cast<size_t>(tp_epoch & 1u) * p.tp.world + p.tp.rank) * p.tp.rows_cap;
 
+    // The streaming loop is compiled twice: with and without the bounds checks of ragged rows (see load_item).
+    auto stream = [&](auto even_tag) {
+    constexpr bool EVEN = decltype(even_tag)::value;
     while (chunk_tiles > 0) {
         const int n_items = chunk_tiles * CG;
         while (q < n_items) {
             float a[R];
 #pragma unroll
             for (int c = 0; c < C; c++) {
-                const int bs = min((cg * C + c), S - 1) * kWarp + lane;  // < nbp; idle column sets carry zero weights
+                // < nbp; idle column sets carry zero weights
+                const int bs = (EVEN ? (cg * C + c) : min((cg * C + c), S - 1)) * kWarp + lane;
                 XTile<PLANES> x;
 #pragma unroll
                 for (int pl = 0; pl < PLANES; pl++) {
@@ -134,7 +162,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 }
                 x.xs = sm.xs[bs];
                 x.bias = sm.bias[bs];
-                const bool live = (cg * C + c) < S;
+                const bool live = EVEN || (cg * C + c) < S;
 #pragma unroll
                 for (int r = 0; r < R; r++) {
                     const int I = block_dot<PLANES>(it.w[c][r], x);
@@ -157,7 +185,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 cgn -= CG;
                 tln++;
             }
-            if (qn < n_items) load_item<R, C, PAIR>(p, chunk0 + tln, cgn, lane, it);
+            if (qn < n_items) load_item<R, C, PAIR, EVEN>(p, chunk0 + tln, cgn, lane, it);
             if constexpr (!IDOT) {
                 warp_sum_multi<R>(a, lane);
                 if (multi_row_writer<R>(lane)) sm.part[(tl * R + multi_row_of<R>(lane)) * CG + cg] = a[0];
@@ -191,7 +219,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                         store_out<ODT>(p.out[0], idx, silu_mul_f32(g, u));
                     }
                 }
-            } else
+            } else {
             for (int i = threadIdx.x; i < rows; i += kGemvThreads) {
                 const int grow = chunk0 * R + i;
                 if (grow >= p.n_total) continue;
@@ -217,6 +245,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
                 }
                 store_out<ODT>(out, lrow, y);
             }
+            }
         }
         // next chunk
         chunk0 += chunk_tiles;
@@ -225,8 +254,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
         q = warp;
         tl = tl0;
         cg = cg0;
-        if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C, PAIR>(p, chunk0 + tl, cg, lane, it);
+        if (chunk_tiles > 0 && q < chunk_tiles * CG) load_item<R, C, PAIR, EVEN>(p, chunk0 + tl, cg, lane, it);
     }
+
+    };
+    if ((p.nb % kWarp) == 0 && (S % C) == 0) stream(std::true_type{});
+    else stream(std::false_type{});
 
     if constexpr (!IDOT) {
         if (p.tp.world > 1) {
