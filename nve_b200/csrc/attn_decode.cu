@@ -92,14 +92,23 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     }
     pdl_wait();
 
+    // The position scalars are read again now that the producer has finished; q / k / v / the RoPE row are staged
+    // with the position read before the wait at the same time (one memory round trip instead of two) and staged again
+    // in the rare case that the scalars changed in between.
     int seq_len = p.d_seq_len != nullptr ? *reinterpret_cast<const volatile int*>(p.d_seq_len) : p.seq_len;
-    seq_len = max(0, min(seq_len, p.kv_stride));
     int pos = -1;
     if constexpr (FUSED) pos = *reinterpret_cast<const volatile int*>(p.d_pos);
+    if constexpr (FUSED) {
+        const bool spec_ok = pre_pos >= 0 && pre_pos < p.kv_stride;
+        attn_stage_q<HD, QH, FUSED>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pre_pos, spec_ok);
+    }
+    seq_len = max(0, min(seq_len, p.kv_stride));
     const bool pos_ok = FUSED && pos >= 0 && pos < p.kv_stride;
     const bool pre_ok = FUSED && pre_seq == seq_len && pre_pos == pos;
-
-    attn_stage_q<HD, QH, FUSED>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
+    if (!FUSED || pos != pre_pos) {  // uniform over the grid
+        if constexpr (FUSED) __syncthreads();
+        attn_stage_q<HD, QH, FUSED>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
+    }
     __syncthreads();
     pdl_launch_dependents();
 

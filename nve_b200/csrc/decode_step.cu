@@ -197,12 +197,40 @@ __device__ __forceinline__ void ds_load_item(const PhaseMats& pm, int tile, int 
         pf = m0 == m1;
     }
     const long long pf_rows = static_cast<long long>(pf_tiles) * kDsWarps * (pm.paired ? R / 2 : R);
+    // a full column group of full column sets: one address per row, the column sets at immediate offsets
+    const bool full = (pm.nb & (kWarp - 1)) == 0 && (cg + 1) * C <= pm.S;
 #pragma unroll
     for (int r = 0; r < R; r++) {
         const uint8_t* nib;
         const float* sc;
         long long rb;
         item_row(pm, tile, r, R, nib, sc, rb);
+        if (full) {
+            const long long b0 = rb + cg * (C * kWarp) + lane;
+            const uint8_t* nrow = nib + b0 * 16;
+            const float* srow = sc + b0;
+            t.w[0 * R + r] = ld_stream_u4_off<0>(nrow);
+            t.s[0 * R + r] = ld_stream_f32_off<0>(srow);
+            if constexpr (C > 1) {
+                t.w[1 * R + r] = ld_stream_u4_off<512>(nrow);
+                t.s[1 * R + r] = ld_stream_f32_off<128>(srow);
+            }
+            if constexpr (C > 2) {
+                t.w[2 * R + r] = ld_stream_u4_off<1024>(nrow);
+                t.s[2 * R + r] = ld_stream_f32_off<256>(srow);
+                t.w[3 * R + r] = ld_stream_u4_off<1536>(nrow);
+                t.s[3 * R + r] = ld_stream_f32_off<384>(srow);
+            }
+            if (pf && (lane & 7) == 0) {
+#pragma unroll
+                for (int c = 0; c < C; c++) l2_prefetch_line(nrow + pf_rows * pm.nb * 16 + c * 512);
+            }
+            if (pf && lane == 0) {
+#pragma unroll
+                for (int c = 0; c < C; c++) l2_prefetch_line(srow + pf_rows * pm.nb + c * 32);
+            }
+            continue;
+        }
 #pragma unroll
         for (int c = 0; c < C; c++) {
             const int b = (cg * C + c) * kWarp + lane;
