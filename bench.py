@@ -729,8 +729,6 @@ def main() -> None:
                     help="profiling aid: run only this many layers of the stack (default: all; changes the workload)")
     ap.add_argument("--model", default=MODEL, choices=["1b", "3b", "8b", "70b"],
                     help="shape of the synthetic stack; the default is the configuration the headline metric names")
-    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: all-reduce fused into the row-parallel GEMVs (default) or plain NCCL all-reduce")
     args = ap.parse_args()
     MODEL = args.model
     args.warmup = max(3, args.warmup) if args.impl == "ours" else max(1, args.warmup)

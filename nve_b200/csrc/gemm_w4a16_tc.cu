@@ -16,6 +16,11 @@
 // Weights are always dequantised to f16, the type the reference dequantises to; bf16 activations are converted
 // to f16 by a small pre-pass into the caller's scratch (bf16 weights would cost 2^-8 per weight and leave no
 // tolerance margin; tcgen05.mma kind::f16 takes both operands in one format).
+// Work split: the K range of every 128-row tile is cut into super-blocks of 256 weights per row, and the sequence
+// (tile 0, super-block 0), (tile 0, super-block 1), ... is dealt out in equal contiguous runs, one per CTA (one
+// CTA per SM: a CTA owns all 512 TMEM columns).  A run may start and end inside a tile; the part of a tile that a
+// CTA computes is a segment.  Whole-tile segments are stored to Y, the others as f32 partial tiles that a second
+// kernel adds in ascending K order.
 // Roles in a CTA of 640 threads:
 //   warps 0-15 producers, two teams of eight warps that take alternate super-blocks (256 weights per row), each
 //              with its own named barrier and its own cp.async ring of raw nibbles + scales (coalesced along K:
@@ -24,13 +29,15 @@
 //              super-block: (q-8)*scale with the f16 magic-number trick (exact q-8, one rounding in the multiply),
 //              tcgen05.st into the stage's columns, tcgen05.wait::st, one arrival per warp on the stage's "full"
 //              mbarrier.  One lane per group issues the TMA tile load of the stage's activations, which completes
-//              on the same barrier (expect_tx).
+//              on the same barrier (expect_tx).  The producers run through the CTA's whole run without regard to
+//              segment boundaries (only the global addresses change at a tile boundary).
 //   warps 16-19 issue tcgen05.mma (one lane each): warp 16+w takes K block w of every super-block into accumulator
-//              set w, tcgen05.commit -> "empty" mbarrier of the stage, and after its last K block -> the
-//              accumulator barrier.  Issuing costs a thread ~70 cycles per MMA and ~150 per commit whatever the
-//              shape, which is why four warps share it.  Warp 16 also allocates and frees the TMEM columns.
-//   warps 0-3  epilogue: tcgen05.ld (32 lanes x MB columns per warp, the four sets added in ascending order),
-//              convert, store Y (or f32 split-K partials to scratch, reduced in fixed order by a second kernel).
+//              set w, tcgen05.commit -> "empty" mbarrier of the stage, and after the last K block of a segment ->
+//              the accumulator barrier.  Issuing costs a thread ~70 cycles per MMA and ~150 per commit whatever the
+//              shape, which is why four warps share it.  The same warps are the epilogue: tcgen05.ld (warp w reads
+//              TMEM lanes 32w..32w+31, MB columns, the four sets added in ascending order), convert, store; the
+//              next segment's MMAs wait until all four warps have read.  Warp 16 also allocates and frees the
+//              TMEM columns.
 // K order is natural in both operands: one byte permute per raw word puts the two nibbles of consecutive
 // elements 16 bits apart, where a half2 wants them.
 // Every mbarrier wait is bounded in time; an expired wait latches an error code (nve_b200_gemm_error) and the
@@ -77,12 +84,20 @@ struct GemmParams {
     int Nm[3];             // rows of each matrix
     int tile_end[3];       // cumulative 128-row tiles
     int col0[3];           // first column of each matrix in the concatenated [M, N] view
-    float* partial;        // [ksplit, M, N] f32 when ksplit > 1 (N = all matrices side by side)
+    float* partial;        // [2 * grid][M][128] f32: slot 2c = first, slot 2c + 1 = last partial tile of CTA c
     int M, N, K;           // N = sum of Nm
     int nb;                // K / 32
     int kblocks;           // K / 64
-    int ksplit;
+    int sb_per_tile;       // super-blocks (4 K blocks) per tile
+    int units_per_cta;     // super-blocks in a CTA's contiguous run of the (tile, super-block) sequence
+    int total_units;       // tiles * sb_per_tile
 };
+
+// matrix and first row (inside that matrix) of a 128-row tile of the side-by-side tile sequence
+__device__ __forceinline__ void tile_locate(const GemmParams& p, int tile, int& mi, int& n0) {
+    mi = tile < p.tile_end[0] ? 0 : (tile < p.tile_end[1] ? 1 : 2);
+    n0 = (tile - (mi == 0 ? 0 : p.tile_end[mi - 1])) * kTileN;
+}
 
 __device__ __forceinline__ uint32_t s_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -259,28 +274,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kTeams * kRawStages * kTileN * 8);
     uint64_t* full = bars;                  // [kOpStages], one arrival per warp of the owning group
     uint64_t* empty = bars + kOpStages;     // [kOpStages], 1 arrival (tcgen05.commit)
-    uint64_t* accum = bars + 2 * kOpStages; // 1 arrival
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kOpStages + 1);
+    uint64_t* accum = bars + 2 * kOpStages; // one arrival per issuing warp: the segment's accumulators are complete
+    uint64_t* accfree = accum + 1;          // one arrival per issuing warp: the segment's accumulators have been read
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree + 1);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    // the tiles of the (up to three) matrices are laid side by side along blockIdx.x
-    const int tile = blockIdx.x;
-    const int mi = tile < p.tile_end[0] ? 0 : (tile < p.tile_end[1] ? 1 : 2);
-    const int n0 = (tile - (mi == 0 ? 0 : p.tile_end[mi - 1])) * kTileN;  // first row of the tile inside its matrix
-    const int Nloc = p.Nm[mi];
-    const int split = blockIdx.y;
-    const int kb_begin = static_cast<int>(static_cast<long long>(p.kblocks) * split / p.ksplit);
-    const int kb_end = static_cast<int>(static_cast<long long>(p.kblocks) * (split + 1) / p.ksplit);
-    const int nkb = kb_end - kb_begin;
+    // This CTA's work: units [u0, u0 + n_units) of the sequence (tile 0, super-block 0), (tile 0, super-block 1),
+    // ..., (tile 1, super-block 0), ...  The tiles of the (up to three) matrices follow one another.  A maximal
+    // run of units of one tile is a segment; it is whole when it covers all super-blocks of the tile.
+    const int SB = p.sb_per_tile;
+    const int u0 = blockIdx.x * p.units_per_cta;
+    const int n_units = min(p.units_per_cta, p.total_units - u0);
 
     if (tid == 0) {
         for (int i = 0; i < kOpStages; i++) {
             mb_init(&full[i], 5);  // the four warps of the group that owns the stage + the TMA issuer's expect_tx
             mb_init(&empty[i], 1);
         }
-        mb_init(accum, min(kMmaWarps, nkb));  // one tcgen05.commit per issuing warp that has work
+        mb_init(accum, kMmaWarps);
+        mb_init(accfree, kMmaWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -298,15 +312,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         // ------------------------------------------------------------------ producers
         // Raw loading is coalesced along K: 8 lanes copy the 128 contiguous nibble bytes (256 weights) of one row,
         // so a warp-wide cp.async touches 4 cache lines instead of 32.  16-byte chunks are XOR-swizzled by the row
-        // so that the later per-row reads are bank-conflict free.  All addresses are set up once; the loop only
-        // advances them (the kernel is bound by instruction issue, so loop overhead counts).
-        const int nsb = (nkb + kSuper - 1) / kSuper;
+        // so that the later per-row reads are bank-conflict free.  Addresses are set up once per tile; inside a
+        // tile the loop only advances them (the kernel is bound by instruction issue, so loop overhead counts).
         // The chain of one super-block (copy wait -> barrier -> ring wait -> load -> convert -> store -> fences ->
         // arrive) is over a thousand cycles of mostly latency; two teams run it out of phase on alternate
-        // super-blocks, each with its own named barrier and raw ring.
+        // units, each with its own named barrier and raw ring.
         const int team = tid / kTeamThreads;
         const int tt = tid - team * kTeamThreads;        // thread inside the team
-        const int nsb_team = (nsb - team + kTeams - 1) / kTeams;  // super-blocks team, team + kTeams, ...
+        const int nsb_team = n_units > team ? (n_units - team + kTeams - 1) / kTeams : 0;  // units team, team + kTeams, ...
         constexpr int kNibPer = 1024 / kTeamThreads;  // 128 rows x 8 chunks of 16 bytes
         constexpr int kScPer = 512 / kTeamThreads;    // 128 rows x 4 K blocks x 2 scales
         constexpr uint32_t kRawNStage = kTileN * 128, kRawSStage = kTileN * 8 * 4;
@@ -314,43 +327,75 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         const unsigned char* teamRawS = reinterpret_cast<const unsigned char*>(sRawS) + team * (kRawStages * kRawSStage);
         const uint8_t* gn[kNibPer];
         uint32_t sn[kNibPer];
-        int kn[kNibPer];  // K block of the super-block that the chunk belongs to
+        const float* gs[kScPer];
+        uint32_t ss[kScPer];
 #pragma unroll
         for (int j = 0; j < kNibPer; j++) {
             const int id = tt + kTeamThreads * j;
             const int rr = id >> 3, c = id & 7;
-            const int grow = min(n0 + rr, Nloc - 1);
-            gn[j] = p.nib[mi] + static_cast<long long>(grow) * (p.K / 2) + (kb_begin + team * kSuper) * 32 + c * 16;
             sn[j] = s_addr(teamRawN) + rr * 128 + ((c ^ (rr & 7)) << 4);
-            kn[j] = c >> 1;
         }
-        const float* gs[kScPer];
-        uint32_t ss[kScPer];
-        int ks[kScPer];
 #pragma unroll
         for (int j = 0; j < kScPer; j++) {
             const int id = tt + kTeamThreads * j;
             const int rr = id >> 2, kbi = id & 3;
-            const int grow = min(n0 + rr, Nloc - 1);
-            gs[j] = p.sc[mi] + static_cast<long long>(grow) * p.nb + (kb_begin + team * kSuper + kbi) * 2;
             ss[j] = s_addr(teamRawS) + (rr * 8 + kbi * 2) * 4;
-            ks[j] = kbi;
         }
-        int issue_left = nkb - team * kSuper;  // K blocks from the team's next super-block to issue onwards
+        // global addresses of this thread's chunks of super-block sbi of a tile
+        auto set_ptrs = [&](int tile, int sbi) {
+            int mi, n0;
+            tile_locate(p, tile, mi, n0);
+            const int Nloc = p.Nm[mi];
+            const uint8_t* nb0 = p.nib[mi] + sbi * (kSuper * 32);
+            const float* sc0 = p.sc[mi] + sbi * (kSuper * 2);
+#pragma unroll
+            for (int j = 0; j < kNibPer; j++) {
+                const int id = tt + kTeamThreads * j;
+                const int rr = id >> 3, c = id & 7;
+                const int grow = min(n0 + rr, Nloc - 1);
+                gn[j] = nb0 + static_cast<long long>(grow) * (p.K / 2) + c * 16;
+            }
+#pragma unroll
+            for (int j = 0; j < kScPer; j++) {
+                const int id = tt + kTeamThreads * j;
+                const int rr = id >> 2, kbi = id & 3;
+                const int grow = min(n0 + rr, Nloc - 1);
+                gs[j] = sc0 + static_cast<long long>(grow) * p.nb + kbi * 2;
+            }
+        };
+        // cursor of the raw copies: the team's next unit to fetch
+        int i_tile = (u0 + team) / SB;
+        int i_sbi = (u0 + team) - i_tile * SB;
+        int i_left = nsb_team;
+        if (i_left > 0) set_ptrs(i_tile, i_sbi);
         uint32_t issue_n = 0, issue_s = 0;     // byte offsets of the raw stage to fill
         auto issue_raw = [&]() {
-            if (issue_left > 0) {
+            if (i_left > 0) {
+                const int valid = p.kblocks - i_sbi * kSuper;  // K blocks of this super-block that exist (>= 1)
 #pragma unroll
                 for (int j = 0; j < kNibPer; j++) {
-                    if (kn[j] < issue_left) cp_async_16s(sn[j] + issue_n, gn[j]);
-                    gn[j] += kTeams * kSuper * 32;
+                    const int kn = ((tt + kTeamThreads * j) & 7) >> 1;  // K block of the super-block that the chunk belongs to
+                    if (kn < valid) cp_async_16s(sn[j] + issue_n, gn[j]);
                 }
 #pragma unroll
                 for (int j = 0; j < kScPer; j++) {
-                    if (ks[j] < issue_left) cp_async_8s(ss[j] + issue_s, gs[j]);
-                    gs[j] += kTeams * kSuper * 2;
+                    const int ks = (tt + kTeamThreads * j) & 3;
+                    if (ks < valid) cp_async_8s(ss[j] + issue_s, gs[j]);
                 }
-                issue_left -= kTeams * kSuper;
+                i_left--;
+                i_sbi += kTeams;
+                if (i_sbi >= SB) {  // the team's next unit lies in a later tile
+                    do {
+                        i_sbi -= SB;
+                        i_tile++;
+                    } while (i_sbi >= SB);
+                    if (i_left > 0) set_ptrs(i_tile, i_sbi);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kNibPer; j++) gn[j] += kTeams * kSuper * 32;
+#pragma unroll
+                    for (int j = 0; j < kScPer; j++) gs[j] += kTeams * kSuper * 2;
+                }
                 issue_n = issue_n == (kRawStages - 1) * kRawNStage ? 0 : issue_n + kRawNStage;
                 issue_s = issue_s == (kRawStages - 1) * kRawSStage ? 0 : issue_s + kRawSStage;
             }
@@ -368,8 +413,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kAccCols;
         const bool tma_lane = (warp & 3) == 0 && lane == 0;
         pdl_wait();  // activations come from the previous kernel; weights do not
-        int left = nkb - team * kSuper - kBurst * g;  // K blocks that exist from this group's burst of the current super-block onwards
-        int kx = (kb_begin + team * kSuper + kBurst * g) * kKBlock;  // K coordinate of that burst
+        int d_sbi = (u0 + team) % SB;  // super-block (inside its tile) of the unit being dequantised
 
         // read offsets of this group's quantisation blocks inside a raw row / scale row
         uint32_t roff[2 * kBurst];
@@ -379,7 +423,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
         const DequantConsts dc = make_dequant_consts();
         bool ok = true;
-        int slot = team % kSlots, use = team / kSlots;  // operand-ring slot of the super-block and how often it was used
+        int slot = team % kSlots, use = team / kSlots;  // operand-ring slot of the unit and how often it was used
         uint32_t raw_n = 0, raw_s = 0;  // byte offsets of the raw stage to read
         for (int it = 0; it < nsb_team; it++) {
             cp_async_wait<1>();                               // this thread's copies of the super-block have landed
@@ -387,7 +431,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             else asm volatile("bar.sync 3, %0;" ::"n"(kTeamThreads) : "memory");
             // every thread of the team has finished the previous super-block, whose raw stage is refilled now
             issue_raw();
-            const int nvalid = min(kBurst, left);      // K blocks of the burst that exist
+            // K blocks of the burst that exist (fewer than kBurst only in the last super-block of a K that is not
+            // a multiple of 256, which the host allows only when a CTA's run is exactly one tile)
+            const int nvalid = max(0, min(kBurst, p.kblocks - d_sbi * kSuper - kBurst * g));
+            const int kx = (d_sbi * kSuper + kBurst * g) * kKBlock;  // K coordinate of the burst
             const int so0 = slot * kSuper + kBurst * g;  // operand stage of the first K block of the burst
             // a warp that gave up keeps attending the producer barrier above (the others would wait for it for ever)
             // and does nothing else
@@ -449,8 +496,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     }
                 }
             }
-            left -= kTeams * kSuper;
-            kx += kTeams * kSuper * kKBlock;
+            d_sbi += kTeams;
+            while (d_sbi >= SB) d_sbi -= SB;
             raw_n = raw_n == (kRawStages - 1) * kRawNStage ? 0 : raw_n + kRawNStage;
             raw_s = raw_s == (kRawStages - 1) * kRawSStage ? 0 : raw_s + kRawSStage;
             slot += kTeams;
@@ -461,20 +508,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         }
         cp_async_wait<0>();
         pdl_launch_dependents();
-
-        // ------------------------------------------------------------------ epilogue (warps 0-3)
-        if (warp < 4) {
-            bool done = ok && mb_wait(accum, 0);
-            if (!done || *reinterpret_cast<volatile int*>(abort_flag)) {
-                atomicCAS(&g_gemm_device_error, 0, 3);
-                atomicExch(abort_flag, 1);
-                done = false;
+    } else {
+        // ------------------------------------------------------------------ MMA issuers and epilogue (last four warps)
+        // Warp w issues K block w of every unit into accumulator set w (one lane: waits, fences, MMAs and commits
+        // are single-thread operations).  At the end of a segment the four warps wait for all four sets, and
+        // warp w reads TMEM lanes 32w .. 32w+31 (the lanes a warp with this index may touch) of every set, adds
+        // them in ascending order and stores the tile -- to Y when the segment is whole, else as an f32 partial
+        // tile that the reduce kernel sums.  The next segment's MMAs start once all four warps have read.
+        constexpr uint32_t idesc = make_idesc(MB, false, false);  // both operands f16 (bf16 activations are converted first)
+        const int w = warp - kProducerWarps;
+        pdl_wait();  // the stores below must not overtake the previous kernel's reads of Y / the partials
+        int j = 0, seg = 0;
+        int tile = u0 / SB;
+        int sbi = u0 - tile * SB;
+        bool ok = true;
+        while (j < n_units) {
+            const int seg_units = min(SB - sbi, n_units - j);
+            if (lane == 0) {
+                if (seg > 0) ok = mb_wait(accfree, static_cast<unsigned>(seg - 1) & 1u);
+                bool issued = false;
+                for (int q = 0; q < seg_units && ok; q++) {
+                    if ((sbi + q) * kSuper + w >= p.kblocks) break;  // K block beyond the end of a ragged K
+                    const int jj = j + q;
+                    const int so = (jj % kSlots) * kSuper + w;
+                    ok = mb_wait(&full[so], static_cast<unsigned>(jj / kSlots) & 1u);
+                    if (!ok || *reinterpret_cast<volatile int*>(abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_tmem = tmem_base + kAccCols + so * kStageCols;
+                    const uint64_t bdesc = make_desc_k_sw128(s_addr(sB + so * kBBytes));
+#pragma unroll
+                    for (int kk = 0; kk < kKBlock / 16; kk++) {
+                        // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
+                        umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (q > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
+                    issued = true;
+                }
+                if (ok) {
+                    // this warp's accumulator set is complete (a warp without a K block of its own just arrives)
+                    if (issued) umma_commit(accum);
+                    else mb_arrive(accum);
+                    ok = mb_wait(accum, static_cast<unsigned>(seg) & 1u);
+                }
+                if (!ok || *reinterpret_cast<volatile int*>(abort_flag)) {
+                    atomicCAS(&g_gemm_device_error, 0, 2);
+                    atomicExch(abort_flag, 1);
+                    ok = false;
+                }
             }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (done) {
-                const int n = n0 + warp * 32 + lane;  // this thread's output feature
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-                const int used = min(kAccSets, nkb);  // accumulator sets that received an MMA
+            {
+                int mi, n0;
+                tile_locate(p, tile, mi, n0);
+                const int Nloc = p.Nm[mi];
+                const bool whole = seg_units == SB;
+                const int n = n0 + w * 32 + lane;  // this thread's output feature
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16);
+                const int used = min(kAccSets, min((sbi + seg_units) * kSuper, p.kblocks) - sbi * kSuper);  // sets that received an MMA
+                float* part = p.partial + (static_cast<long long>(2 * blockIdx.x + (seg > 0 ? 1 : 0)) * p.M) * kTileN + w * 32 + lane;
 #pragma unroll
                 for (int cb = 0; cb < MB; cb += 8) {
                     float y[8];
@@ -485,50 +581,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                                      : "r"(taddr + a * MB + cb));
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int j = 0; j < 8; j++) y[j] = a == 0 ? __uint_as_float(v[j]) : __fadd_rn(y[j], __uint_as_float(v[j]));
+                        for (int e = 0; e < 8; e++) y[e] = a == 0 ? __uint_as_float(v[e]) : __fadd_rn(y[e], __uint_as_float(v[e]));
                     }
-                    if (n < Nloc) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const int m = cb + j;
-                            if (m < p.M) {
-                                if (p.ksplit > 1) p.partial[(static_cast<long long>(split) * p.M + m) * p.N + p.col0[mi] + n] = y[j];
-                                else store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y[j]);
-                            }
+                    for (int e = 0; e < 8; e++) {
+                        const int m = cb + e;
+                        if (m < p.M) {
+                            if (!whole) part[m * kTileN] = y[e];
+                            else if (n < Nloc) store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y[e]);
                         }
                     }
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        }
-    } else {
-        // ------------------------------------------------------------------ MMA issuers (last four warps)
-        // One lane per warp runs the loop: waits, fences, MMAs and commits are all single-thread operations.
-        constexpr uint32_t idesc = make_idesc(MB, false, false);  // both operands f16 (bf16 activations are converted first)
-        const int w = warp - kProducerWarps;               // K block of the super-block and accumulator set
-        if (lane == 0) {
-            bool issued = false;
-            for (int sb = 0; sb * kSuper + w < nkb; sb++) {
-                const int so = (sb % kSlots) * kSuper + w;
-                const bool ready = mb_wait(&full[so], static_cast<unsigned>(sb / kSlots) & 1u);
-                if (!ready || *reinterpret_cast<volatile int*>(abort_flag)) {
-                    atomicCAS(&g_gemm_device_error, 0, 2);
-                    atomicExch(abort_flag, 1);
-                    break;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_tmem = tmem_base + kAccCols + so * kStageCols;
-                const uint64_t bdesc = make_desc_k_sw128(s_addr(sB + so * kBBytes));
-#pragma unroll
-                for (int kk = 0; kk < kKBlock / 16; kk++) {
-                    // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
-                    umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
-                issued = true;
+            __syncwarp();
+            if (lane == 0) mb_arrive(accfree);
+            j += seg_units;
+            sbi += seg_units;
+            if (sbi >= SB) {
+                sbi = 0;
+                tile++;
             }
-            // this warp's accumulator set is complete (on an abandoned run the epilogue is not waiting any more)
-            if (issued) umma_commit(accum);
+            seg++;
         }
         __syncwarp();
     }
@@ -541,40 +615,75 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     }
 }
 
-// Sum the split-K partials in ascending split order, convert and scatter to the matrices' outputs.
-template <int ODT> __global__ void gemm_splitk_reduce_kernel(const GemmParams p) {
+// Tiles that more than one CTA worked on: sum their partial tiles in ascending CTA (= ascending K) order, convert
+// and store.  One block per tile; a tile that a single CTA covered was stored by that CTA.
+template <int ODT> __global__ void __launch_bounds__(512) gemm_partial_reduce_kernel(const GemmParams p) {
     pdl_wait();
-    const long long mn = static_cast<long long>(p.M) * p.N;
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= mn) return;
-    float y = p.partial[i];
-    for (int s = 1; s < p.ksplit; s++) y = __fadd_rn(y, p.partial[static_cast<long long>(s) * mn + i]);
-    const int m = static_cast<int>(i / p.N), c = static_cast<int>(i - static_cast<long long>(m) * p.N);
-    const int mi = c < p.col0[1] ? 0 : (c < p.col0[2] ? 1 : 2);
-    store_out<ODT>(p.Y[mi], static_cast<long long>(m) * p.Nm[mi] + (c - p.col0[mi]), y);
+    const int t = blockIdx.x;
+    const int SB = p.sb_per_tile, U = p.units_per_cta;
+    const int first = (t * SB) / U, last = ((t + 1) * SB - 1) / U;
+    if (first == last) return;
+    int mi, n0;
+    tile_locate(p, t, mi, n0);
+    const int Nloc = p.Nm[mi];
+    const int n = n0 + threadIdx.x;
+    if (n >= Nloc) return;
+    for (int m = threadIdx.y; m < p.M; m += blockDim.y) {
+        float y = 0.0f;
+        for (int c = first; c <= last; c++) {
+            // the CTA's first segment when its run starts inside this tile, else its last one
+            const int slot = 2 * c + (c * U >= t * SB ? 0 : 1);
+            const float v = p.partial[(static_cast<long long>(slot) * p.M + m) * kTileN + threadIdx.x];
+            y = c == first ? v : __fadd_rn(y, v);
+        }
+        store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y);
+    }
 }
 
 static size_t gemm_smem_bytes(int mb) {
     const size_t need = 1024 + static_cast<size_t>(op_slots(mb) * kSuper) * (mb * 128) + static_cast<size_t>(kTeams * kRawStages) * kTileN * (128 + 32) +
-                        (2 * kMaxOpStages + 1) * 8 + 16;
+                        (2 * kMaxOpStages + 2) * 8 + 16;
     // A CTA allocates all 512 TMEM columns, so a second CTA on the same SM would only sit in tcgen05.alloc until the
     // first one ends: ask for more than half of the SM's shared memory to keep it off the SM instead.
     const size_t half_sm = 120 * 1024;
     return need > half_sm ? need : half_sm;
 }
 
-static int choose_ksplit_tiles(int tiles, int K, bool have_scratch);
-static int choose_ksplit(int N, int K, bool have_scratch) {
-    return choose_ksplit_tiles((N + kTileN - 1) / kTileN, K, have_scratch);
+// How the (tile, super-block) sequence is cut into one contiguous run per CTA.  With a workspace the runs are equal
+// (total / SM count, rounded up; at least two super-blocks = 512 weights per row), whatever the tile count: few
+// tiles are split over K so that every SM streams weights, and a tile count that is not a multiple of the SM count
+// (gate/up of an 8B model: 224 tiles on 148 SMs) costs total / SMs instead of two full waves.  Runs that cut a
+// tile leave f32 partial tiles in the workspace (two slots per CTA: its first and its last segment); the reduce
+// kernel adds them in ascending K order, so the result is reproducible for a given SM count.  Without a workspace,
+// or with K not a multiple of 256, a CTA takes exactly one tile.
+struct GemmPlan {
+    int sb;      // super-blocks per tile
+    int U;       // units per CTA
+    int grid;
+    size_t partial_bytes;  // 0 when every run consists of whole tiles
+};
+static size_t plan_partial_bytes(int total, int sb, int U, int M) {
+    if (U % sb == 0) return 0;
+    const int grid = (total + U - 1) / U;
+    return static_cast<size_t>(2) * grid * M * kTileN * sizeof(float);
 }
-static int choose_ksplit_tiles(int tiles, int K, bool have_scratch) {
-    if (!have_scratch) return 1;
-    int ks = sm_count() / tiles;
+static GemmPlan plan_gemm(int tiles, int K, int M, bool have_scratch, size_t avail) {
+    GemmPlan g;
     const int kblocks = K / kKBlock;
-    if (ks > kblocks / 8) ks = kblocks / 8;  // at least 8 K blocks (512 elements) per split
-    if (ks > 8) ks = 8;
-    if (ks < 1) ks = 1;
-    return ks;
+    g.sb = (kblocks + kSuper - 1) / kSuper;
+    const long long total = static_cast<long long>(tiles) * g.sb;
+    g.U = g.sb;
+    if (have_scratch && (kblocks % kSuper) == 0 && total < 0x3FFFFFFF) {
+        const int sms = sm_count();
+        int U = static_cast<int>((total + sms - 1) / sms);
+        if (U < 2) U = g.sb < 2 ? g.sb : 2;
+        // a workspace too small for the partial tiles: longer runs (fewer CTAs) until they fit; whole tiles need none
+        while (plan_partial_bytes(static_cast<int>(total), g.sb, U, M) > avail) U++;
+        g.U = U;
+    }
+    g.grid = static_cast<int>((total + g.U - 1) / g.U);
+    g.partial_bytes = plan_partial_bytes(static_cast<int>(total), g.sb, g.U, M);
+    return g;
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link-time dependency on libcuda).
@@ -616,7 +725,7 @@ template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStrea
     int s = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(smem));
     if (s != NVE_OK) return s;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.tile_end[2], p.ksplit);
+    cfg.gridDim = dim3((p.total_units + p.units_per_cta - 1) / p.units_per_cta);
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -630,9 +739,8 @@ template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStrea
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p, xmap);
     count_launch();
     if (e != cudaSuccess) return set_cuda_status(e);
-    if (p.ksplit > 1) {
-        const long long mn = static_cast<long long>(p.M) * p.N;
-        gemm_splitk_reduce_kernel<ODT><<<static_cast<unsigned>((mn + 255) / 256), 256, 0, st>>>(p);
+    if (p.units_per_cta % p.sb_per_tile != 0) {
+        gemm_partial_reduce_kernel<ODT><<<p.tile_end[2], dim3(kTileN, 4), 0, st>>>(p);
         count_launch();
         return check_launch();
     }
@@ -664,8 +772,8 @@ __global__ void bf16_to_f16_kernel(const uint4* in, uint4* out, long long n8) {
 
 static size_t x16_region_bytes(int M, int K) { return (static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255); }
 
-// Shared by both entry points.  Scratch layout: [f16 copy of bf16 activations (x16_region_bytes)][split-K partials].
-// bf16 activations need the first region; split-K uses what is left.
+// Shared by both entry points.  Scratch layout: [f16 copy of bf16 activations (x16_region_bytes)][partial tiles].
+// bf16 activations need the first region; the partial tiles of split runs use what is left.
 struct GemmMat {
     const uint8_t* nib;
     const float* sc;
@@ -708,9 +816,10 @@ static int run_gemm_multi(const void* X, int x_dtype, const GemmMat* mats, int n
     p.M = M; p.N = cols; p.K = K;
     p.nb = K / 32;
     p.kblocks = K / kKBlock;
-    int ks = choose_ksplit_tiles(tiles, K, sp != nullptr);
-    while (ks > 1 && static_cast<size_t>(ks) * M * cols * sizeof(float) > scratch_bytes) ks--;
-    p.ksplit = ks;
+    const GemmPlan plan = plan_gemm(tiles, K, M, sp != nullptr, sp != nullptr ? scratch_bytes : 0);
+    p.sb_per_tile = plan.sb;
+    p.units_per_cta = plan.U;
+    p.total_units = tiles * plan.sb;
     p.partial = reinterpret_cast<float*>(sp);
     if (y_dtype == NVE_DT_F32) return gemm_mb<NVE_DT_F32>(p, st);
     return y_dtype == NVE_DT_F16 ? gemm_mb<NVE_DT_F16>(p, st) : gemm_mb<NVE_DT_BF16>(p, st);
@@ -728,8 +837,7 @@ using namespace nve;
 
 extern "C" size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0 || (K % kKBlock) != 0) return 0;
-    const int ks = choose_ksplit(N, K, true);
-    return x16_region_bytes(M, K) + (ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0);
+    return x16_region_bytes(M, K) + plan_gemm((N + kTileN - 1) / kTileN, K, M, true, ~static_cast<size_t>(0)).partial_bytes;
 }
 
 extern "C" size_t nve_b200_gemm_w4a16_multi_scratch_bytes(int M, const int* Ns, int num_mats, int K) {
@@ -740,8 +848,8 @@ extern "C" size_t nve_b200_gemm_w4a16_multi_scratch_bytes(int M, const int* Ns, 
         tiles += (Ns[m] + kTileN - 1) / kTileN;
         cols += Ns[m];
     }
-    const int ks = choose_ksplit_tiles(static_cast<int>(tiles), K, true);
-    return x16_region_bytes(M, K) + (ks > 1 ? static_cast<size_t>(ks) * M * cols * sizeof(float) : 0);
+    if (tiles > 0x00FFFFFF) return 0;
+    return x16_region_bytes(M, K) + plan_gemm(static_cast<int>(tiles), K, M, true, ~static_cast<size_t>(0)).partial_bytes;
 }
 
 extern "C" int nve_b200_gemm_w4a16_multi(const void* X, int x_dtype, const nve_b200_w4_matrix* mats, int num_mats, int y_dtype,
@@ -792,11 +900,11 @@ extern "C" int nve_b200_gemm_error(int reset) {
 // Who needs it: the reference's batch > 1 call site (GpuWeight::matmul_x) receives only the activations and the
 // weight tensors -- it has no workspace to hand down -- and it can run while a CUDA graph is being recorded,
 // where cudaMalloc is illegal; a serving thread that must not touch the allocator is in the same position.
-// For those callers the split-K partial sums live in a fixed array inside the library image instead of a
+// For those callers the partial tiles of split runs live in a fixed array inside the library image instead of a
 // caller-provided buffer.
 //
 // Cost and limits: the array is kStaticScratchFloats * 4 bytes (4 MiB) of device memory on every GPU that loads
-// the library, until the process exits.  A call whose split-K partials (nve_b200_gemm_w4a16_scratch_bytes) exceed
+// the library, until the process exits.  A call whose partial tiles (nve_b200_gemm_w4a16_scratch_bytes) exceed
 // it is rejected with NVE_ERR_TOO_LARGE.  All calls share the one array: two such GEMMs that overlap on the same
 // GPU (different streams) race on it; issue them on one stream.  The array keeps whatever the previous call
 // left in it; nothing in it has to start at zero, because every partial a call reads was written by that same
@@ -840,9 +948,8 @@ extern "C" int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uin
     if (x_dtype != NVE_DT_F16 && x_dtype != NVE_DT_BF16) return set_status(NVE_ERR_BAD_DTYPE);
     if (y_dtype != x_dtype && y_dtype != NVE_DT_F32) return set_status(NVE_ERR_BAD_DTYPE);
     if (!aligned(X, 16) || !aligned(nibbles, 16) || !aligned(scales, 8)) return set_status(NVE_ERR_BAD_ALIGNMENT);
-    const int ks = choose_ksplit(N, K, true);
     const size_t need = (x_dtype == NVE_DT_BF16 ? x16_region_bytes(M, K) : 0) +
-                        (ks > 1 ? static_cast<size_t>(ks) * M * N * sizeof(float) : 0);
+                        plan_gemm((N + kTileN - 1) / kTileN, K, M, true, ~static_cast<size_t>(0)).partial_bytes;
     if (need > kStaticScratchFloats * sizeof(float)) return set_status(NVE_ERR_TOO_LARGE);
     float* scratch = nullptr;
     int st = static_scratch_address(&scratch);

@@ -19,7 +19,9 @@ def _case(orc, M, N, K, seed, bf):
 
 
 @pytest.mark.parametrize("M,N,K", [(16, 128, 64), (16, 128, 512), (1, 256, 1024), (8, 384, 2048), (32, 1024, 4096),
-                                    (64, 512, 4096), (33, 200, 1024), (64, 4096, 4096), (16, 2048, 14336)])
+                                    (64, 512, 4096), (33, 200, 1024), (64, 4096, 4096), (16, 2048, 14336),
+                                    # more tiles than SMs: a CTA's run crosses tile boundaries (partial first and last segments)
+                                    (16, 25600, 512), (32, 20480, 1024), (8, 19000, 768)])
 @pytest.mark.parametrize("bf", [False, True])
 def test_gemm_w4a16_tensor_core(cuda, orc, M, N, K, bf):
     from nve_b200 import cuda_kernels as ck
@@ -40,7 +42,7 @@ def test_gemm_w4a16_tensor_core(cuda, orc, M, N, K, bf):
     assert torch.equal(y16, y32.to(dt))
     if not bf:
         assert rel_rms_err(y16.float().cpu().numpy(), ref) < TOL
-    # split-K through caller-provided scratch gives the same result within f32 reassociation
+    # with a caller-provided workspace tiles are cut over K between CTAs: same result within f32 reassociation
     nbytes = ck.gemm_w4a16_scratch_bytes(M, N, K)
     if nbytes:
         scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
@@ -64,10 +66,11 @@ def test_gemm_matches_gemv_rows(cuda, orc):
         assert rel_rms_err(Y[m], y) < 3e-3
 
 
-@pytest.mark.parametrize("M,Ns,K", [(16, (4096, 1024, 1024), 4096), (8, (256, 128), 512), (64, (1024, 1000, 40), 1024)])
+@pytest.mark.parametrize("M,Ns,K", [(16, (4096, 1024, 1024), 4096), (8, (256, 128), 512), (64, (1024, 1000, 40), 1024),
+                                     (8, (12800, 12864), 512)])
 def test_gemm_multi_matrix_equals_single_calls(cuda, orc, M, Ns, K):
-    """q/k/v (or gate/up) in one launch: same numbers as one call per matrix without split-K, and within f32
-    reassociation of them with split-K over the combined tile count."""
+    """q/k/v (or gate/up) in one launch: same numbers as one call per matrix without a workspace, and within f32
+    reassociation of them when the workspace lets the runs of the CTAs cut tiles (also across the matrices)."""
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda

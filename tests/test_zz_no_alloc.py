@@ -2,7 +2,7 @@
 
 Some callers of the batched GEMM have nowhere to get a workspace from: the reference's batch > 1 call site only
 holds activation and weight tensors, and it may run while a CUDA graph is being captured, when device allocation
-is forbidden.  For them the library keeps the split-K partial sums in a fixed array of its own.  This file checks,
+is forbidden.  For them the library keeps the partial sums of tiles that several CTAs share in a fixed array of its own.  This file checks,
 through the C ABI, that the entry point gives the same result as the ordinary one (which takes a caller-provided
 workspace) on two calls in a row -- the second with different inputs, so stale partials from the first call
 would show -- and that a shape whose partials exceed the fixed array is refused.  It is collected last so that a
@@ -26,7 +26,7 @@ def test_noalloc_gemm_matches_workspace_gemm_twice(cuda, orc):
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    M, N, K = 32, 1024, 4096  # 8 weight tiles -> split-K over 8 slices: the workspace is really used
+    M, N, K = 32, 1024, 4096  # 8 weight tiles, each cut over K between 8 CTAs: the workspace is really used
     assert ck.gemm_w4a16_scratch_bytes(M, N, K) > 0
     for call, seed in enumerate((911, 912)):
         nib, sc, X16 = _inputs(orc, M, N, K, seed)
@@ -53,14 +53,14 @@ def test_noalloc_gemm_bf16_input_and_exact_limit(cuda, orc):
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    for (M, N, K, dt, bf) in ((16, 1024, 4096, torch.bfloat16, True), (64, 8192, 4096, torch.float16, False)):
+    for (M, N, K, dt, bf) in ((16, 1024, 4096, torch.bfloat16, True), (64, 1024, 4096, torch.float16, False)):
         W = orc.fill_normal(N * K, 921, 1, scale=0.02).reshape(N, K)
         nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
         X16 = orc.to_act16(orc.fill_normal(M * K, 921, 2), bf).reshape(M, K)
         dx, dn, ds = dev(X16, dt), dev(nib), dev(sc)
         nbytes = ck.gemm_w4a16_scratch_bytes(M, N, K)
         if not bf:
-            # 2 K slices x 64 x 8192 floats of partial sums = exactly the fixed 4 MiB array (the workspace form also
+            # 64 CTAs x 2 partial tiles x 64 x 128 floats = exactly the fixed 4 MiB array (the workspace form also
             # reserves room for a 16-bit copy of the activations, which f16 input does not use)
             assert nbytes - M * K * 2 == 4 * 1024 * 1024
         scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
@@ -78,7 +78,7 @@ def test_noalloc_gemm_refuses_oversized_workspace(cuda):
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    M, N, K = 64, 9472, 4096  # 74 tiles -> 2 K slices -> 2 * 64 * 9472 floats = 4.6 MiB > the fixed 4 MiB
+    M, N, K = 64, 2048, 4096  # 128 CTAs x 2 partial tiles x 64 x 128 floats = 8 MiB > the fixed 4 MiB
     assert ck.gemm_w4a16_scratch_bytes(M, N, K) > 4 * 1024 * 1024
     x = torch.zeros((M, K), dtype=torch.float16, device="cuda")
     nib = torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda")
