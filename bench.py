@@ -425,11 +425,12 @@ def gemm_batch_table(torch, ck, state, shape, peak):
                         ck.gemm_w4a16_multi(x, trip, K, outs=outs, scratch=scratch)
 
             us, launches = time_sequence(torch, rec, reps=10)
-            us /= launches
+            calls = len(state.layer_weights)
+            us /= calls  # per GEMM call: a call whose CTAs cut tiles is two launches (GEMM + partial-tile reduce)
             nbytes = w4_bytes(sum(ns), K)
             gbs = nbytes / us / 1e3
             row[gname] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
-                          "tflops": round(2.0 * m * sum(ns) * K / us / 1e6, 2)}
+                          "tflops": round(2.0 * m * sum(ns) * K / us / 1e6, 2), "launches_per_call": launches // calls}
         table[str(m)] = row
     err = ck.gemm_error()
     return table, err

@@ -42,6 +42,14 @@
 // elements 16 bits apart, where a half2 wants them.
 // Every mbarrier wait is bounded in time; an expired wait latches an error code (nve_b200_gemm_error) and the
 // CTA leaves through the normal path, freeing its TMEM columns.
+// What bounds the kernel (ncu, 28672 x 4096 at batch 16): 3.8 instructions per weight, of which 1.75 are the
+// dequantisation itself (PRMT, SHF, 4 x (LOP3, HADD2, HMUL2) per 8 weights) and about a third is executed by
+// waiting threads (mbarrier polling); issue slots 40 % busy, about 5 warps active per scheduler of which 0.7 are
+// eligible per cycle.  A CTA needs ~6 us for start-up and tail (barrier setup, TMEM allocation, first bytes from
+// DRAM, last MMAs and epilogue) and ~1 us per unit (128 rows x 256 weights) with all SMs busy, 0.8 us alone on the
+// GPU -- a latency-bound pipeline at about a third of the HBM rate.  A variant with TMA-fed raw rings, dedicated
+// loader warps and units issued by four warps side by side measured the same per-unit time, as did runs without
+// the dequantisation arithmetic (-14 %), without the MMAs (-16 %) and without the TMEM stores (0 %).
 #include <cuda.h>
 
 #include <mutex>
@@ -65,6 +73,9 @@ __host__ __device__ constexpr int acc_sets(int) { return kMmaWarps; }
 // super-blocks of operand stages in flight: what is left of the 512 columns, in units of 4 stages x 32 columns
 __host__ __device__ constexpr int op_slots(int mb) { return (kTmemCols - acc_sets(mb) * mb) / (kSuper * kStageCols); }
 constexpr int kMaxOpStages = 12;
+// Barriers are indexed by the unit number modulo kBarUnits (x 4 K blocks), not by the operand slot: see the kernel.
+constexpr int kBarUnits = 6;
+constexpr int kBarStages = kBarUnits * kSuper;
 constexpr int kTeams = 2;          // producer teams; team t takes super-blocks t, t+2, ... on its own barrier and raw ring
 constexpr int kGroups = 2;         // groups of four warps per team (thread = weight row = TMEM lane)
 constexpr int kBurst = kSuper / kGroups;  // K blocks a group dequantises per super-block
@@ -130,14 +141,45 @@ __device__ __forceinline__ bool mb_try(uint32_t addr, unsigned parity) {
         : "memory");
     return done != 0;
 }
-// Bounded by wall time: false after kGemmWaitLimitNs without the phase completing.
+// The same test without the suspend-time hint.
+__device__ __forceinline__ bool mb_test(uint32_t addr, unsigned parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded by wall time: false after kGemmWaitLimitNs without the phase completing.  The clock is read once per 64
+// tries.  A parity wait is only meaningful when the previous phase of the barrier is known to be complete; every
+// wait in this kernel is made by a thread that, in program order, has already dealt with that previous phase (see
+// the barrier ring in the kernel).
 __device__ __forceinline__ bool mb_wait(uint64_t* bar, unsigned parity) {
     const uint32_t addr = s_addr(bar);
-    if (mb_try(addr, parity)) return true;
+    for (int i = 0; i < 64; i++)
+        if (mb_try(addr, parity)) return true;
     unsigned long long t0, t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     do {
-        if (mb_try(addr, parity)) return true;
+        for (int i = 0; i < 64; i++)
+            if (mb_try(addr, parity)) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    } while (t - t0 < kGemmWaitLimitNs);
+    return false;
+}
+// mb_wait that polls without the hint, for the waits whose end is the critical path of the CTA (segment ends).
+__device__ __forceinline__ bool mb_wait_spin(uint64_t* bar, unsigned parity) {
+    const uint32_t addr = s_addr(bar);
+    for (int i = 0; i < 256; i++)
+        if (mb_test(addr, parity)) return true;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    do {
+        for (int i = 0; i < 64; i++)
+            if (mb_test(addr, parity)) return true;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     } while (t - t0 < kGemmWaitLimitNs);
     return false;
@@ -267,14 +309,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     constexpr int kSlots = op_slots(MB);
     constexpr int kOpStages = kSlots * kSuper;  // dequantised operand stages (A in TMEM, B in shared memory)
     static_assert(kAccCols + kOpStages * kStageCols <= kTmemCols && kSlots >= 2 && kOpStages <= kMaxOpStages, "TMEM budget");
+    static_assert(kBarUnits % kSlots == 0 && kBarUnits % kTeams == 0, "the barrier ring must be a multiple of the operand ring and of the team count");
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sB = smem;
     unsigned char* sRawN = sB + kOpStages * kBBytes;            // [kTeams][kRawStages][128 rows][128 B], 16-byte chunks XOR-swizzled
     float* sRawS = reinterpret_cast<float*>(sRawN + kTeams * kRawStages * kTileN * 128);  // [kTeams][kRawStages][128 rows][8 scales]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sRawS + kTeams * kRawStages * kTileN * 8);
-    uint64_t* full = bars;                  // [kOpStages], one arrival per warp of the owning group
-    uint64_t* empty = bars + kOpStages;     // [kOpStages], 1 arrival (tcgen05.commit)
-    uint64_t* accum = bars + 2 * kOpStages; // one arrival per issuing warp: the segment's accumulators are complete
+    // A parity wait is only meaningful when the waiter knows that the barrier's previous phase is complete.  The
+    // operand ring has two or three slots, but units alternate between two dequantiser teams: with one barrier
+    // per slot, consecutive phases of an "empty" barrier would be awaited by different teams, which are not ordered
+    // with each other.  The barriers of a unit are therefore indexed by the unit number modulo kBarUnits = 6 (a
+    // multiple of both ring depths and of the team count): the thread that awaits phase k of a barrier has, in
+    // program order, already awaited its phase k - 1, and so has every thread that arrives on it.
+    uint64_t* full = bars;                  // [kBarStages], one arrival per warp of the owning group + the activation tile's bytes
+    uint64_t* empty = bars + kBarStages;    // [kBarStages], 1 arrival (tcgen05.commit)
+    uint64_t* accum = bars + 2 * kBarStages; // one arrival per issuing warp: the segment's accumulators are complete
     uint64_t* accfree = accum + 1;          // one arrival per issuing warp: the segment's accumulators have been read
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree + 1);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
@@ -289,7 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
     const int n_units = min(p.units_per_cta, p.total_units - u0);
 
     if (tid == 0) {
-        for (int i = 0; i < kOpStages; i++) {
+        for (int i = 0; i < kBarStages; i++) {
             mb_init(&full[i], 5);  // the four warps of the group that owns the stage + the TMA issuer's expect_tx
             mb_init(&empty[i], 1);
         }
@@ -423,7 +472,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
 
         const DequantConsts dc = make_dequant_consts();
         bool ok = true;
-        int slot = team % kSlots, use = team / kSlots;  // operand-ring slot of the unit and how often it was used
+        int slot = team % kSlots;  // operand-ring slot of the unit
         uint32_t raw_n = 0, raw_s = 0;  // byte offsets of the raw stage to read
         for (int it = 0; it < nsb_team; it++) {
             cp_async_wait<1>();                               // this thread's copies of the super-block have landed
@@ -436,15 +485,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             const int nvalid = max(0, min(kBurst, p.kblocks - d_sbi * kSuper - kBurst * g));
             const int kx = (d_sbi * kSuper + kBurst * g) * kKBlock;  // K coordinate of the burst
             const int so0 = slot * kSuper + kBurst * g;  // operand stage of the first K block of the burst
+            const int jj = team + kTeams * it;           // index of the unit in the CTA's run
+            const int fb0 = (jj % kBarUnits) * kSuper + kBurst * g;  // its "full" barriers
+            const int pj = jj - kSlots;                  // the unit whose MMAs read these operand stages last
             // a warp that gave up keeps attending the producer barrier above (the others would wait for it for ever)
             // and does nothing else
             if (ok && nvalid > 0) {
-                if (use > 0) {
+                if (pj >= 0) {
                     // one lane polls for the warp: many threads spinning on one mbarrier word serialise
                     bool w = true;
-                    const unsigned par = static_cast<unsigned>(use - 1) & 1u;
+                    const unsigned par = static_cast<unsigned>(pj / kBarUnits) & 1u;
+                    const int eb0 = (pj % kBarUnits) * kSuper + kBurst * g;
                     if (lane == 0)
-                        for (int b2 = 0; b2 < nvalid && w; b2++) w = mb_wait(&empty[so0 + b2], par);
+                        for (int b2 = 0; b2 < nvalid && w; b2++) w = mb_wait(&empty[eb0 + b2], par);
                     w = __shfl_sync(0xffffffffu, w, 0);
                     if (!w) {
                         if (lane == 0) {
@@ -458,8 +511,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                 if (ok) {
                     if (tma_lane) {
                         for (int b2 = 0; b2 < nvalid; b2++) {
-                            mb_expect_tx(&full[so0 + b2], kBBytes);
-                            tma_load_2d(s_addr(sB + (so0 + b2) * kBBytes), &xmap, kx + b2 * kKBlock, 0, s_addr(&full[so0 + b2]));
+                            mb_expect_tx(&full[fb0 + b2], kBBytes);
+                            tma_load_2d(s_addr(sB + (so0 + b2) * kBBytes), &xmap, kx + b2 * kKBlock, 0, s_addr(&full[fb0 + b2]));
                         }
                     }
                     float scv[2 * kBurst];
@@ -492,7 +545,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {  // one arrival per warp
-                        for (int b2 = 0; b2 < nvalid; b2++) mb_arrive(&full[so0 + b2]);
+                        for (int b2 = 0; b2 < nvalid; b2++) mb_arrive(&full[fb0 + b2]);
                     }
                 }
             }
@@ -500,11 +553,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
             while (d_sbi >= SB) d_sbi -= SB;
             raw_n = raw_n == (kRawStages - 1) * kRawNStage ? 0 : raw_n + kRawNStage;
             raw_s = raw_s == (kRawStages - 1) * kRawSStage ? 0 : raw_s + kRawSStage;
-            slot += kTeams;
-            if (slot >= kSlots) {
-                slot -= kSlots;
-                use++;
-            }
+            slot = (slot + kTeams) % kSlots;
         }
         cp_async_wait<0>();
         pdl_launch_dependents();
@@ -525,13 +574,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
         while (j < n_units) {
             const int seg_units = min(SB - sbi, n_units - j);
             if (lane == 0) {
-                if (seg > 0) ok = mb_wait(accfree, static_cast<unsigned>(seg - 1) & 1u);
+                if (seg > 0) ok = mb_wait_spin(accfree, static_cast<unsigned>(seg - 1) & 1u);
                 bool issued = false;
                 for (int q = 0; q < seg_units && ok; q++) {
                     if ((sbi + q) * kSuper + w >= p.kblocks) break;  // K block beyond the end of a ragged K
                     const int jj = j + q;
                     const int so = (jj % kSlots) * kSuper + w;
-                    ok = mb_wait(&full[so], static_cast<unsigned>(jj / kSlots) & 1u);
+                    const int ub = (jj % kBarUnits) * kSuper + w;  // the barriers of this K block of the unit
+                    ok = mb_wait(&full[ub], static_cast<unsigned>(jj / kBarUnits) & 1u);
                     if (!ok || *reinterpret_cast<volatile int*>(abort_flag)) {
                         ok = false;
                         break;
@@ -544,14 +594,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                         // 16 elements further along K: 8 TMEM columns for A, 32 bytes (+2 in 16-byte units) for B
                         umma_f16_ts(tmem_base + w * MB, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (q > 0 || kk > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty[so]);  // stage reusable once these MMAs have read it
+                    umma_commit(&empty[ub]);  // stage reusable once these MMAs have read it
                     issued = true;
                 }
                 if (ok) {
                     // this warp's accumulator set is complete (a warp without a K block of its own just arrives)
                     if (issued) umma_commit(accum);
                     else mb_arrive(accum);
-                    ok = mb_wait(accum, static_cast<unsigned>(seg) & 1u);
+                    ok = mb_wait_spin(accum, static_cast<unsigned>(seg) & 1u);
                 }
                 if (!ok || *reinterpret_cast<volatile int*>(abort_flag)) {
                     atomicCAS(&g_gemm_device_error, 0, 2);
@@ -573,15 +623,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w4a16_tc_kernel(const Ge
                 float* part = p.partial + (static_cast<long long>(2 * blockIdx.x + (seg > 0 ? 1 : 0)) * p.M) * kTileN + w * 32 + lane;
 #pragma unroll
                 for (int cb = 0; cb < MB; cb += 8) {
-                    float y[8];
-                    for (int a = 0; a < used; a++) {
-                        uint32_t v[8];
-                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                                     : "r"(taddr + a * MB + cb));
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    // the four sets' loads go out together and are waited for once (a set that received no MMA --
+                    // only when the whole K is shorter than four K blocks -- is read and ignored)
+                    uint32_t v[kAccSets][8];
 #pragma unroll
-                        for (int e = 0; e < 8; e++) y[e] = a == 0 ? __uint_as_float(v[e]) : __fadd_rn(y[e], __uint_as_float(v[e]));
+                    for (int a = 0; a < kAccSets; a++)
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                     : "=r"(v[a][0]), "=r"(v[a][1]), "=r"(v[a][2]), "=r"(v[a][3]), "=r"(v[a][4]), "=r"(v[a][5]),
+                                       "=r"(v[a][6]), "=r"(v[a][7])
+                                     : "r"(taddr + a * MB + cb));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    float y[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        y[e] = __uint_as_float(v[0][e]);
+#pragma unroll
+                        for (int a = 1; a < kAccSets; a++)
+                            if (a < used) y[e] = __fadd_rn(y[e], __uint_as_float(v[a][e]));
                     }
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
@@ -627,22 +685,26 @@ template <int ODT> __global__ void __launch_bounds__(512) gemm_partial_reduce_ke
     tile_locate(p, t, mi, n0);
     const int Nloc = p.Nm[mi];
     const int n = n0 + threadIdx.x;
-    if (n >= Nloc) return;
-    for (int m = threadIdx.y; m < p.M; m += blockDim.y) {
-        float y = 0.0f;
-        for (int c = first; c <= last; c++) {
-            // the CTA's first segment when its run starts inside this tile, else its last one
-            const int slot = 2 * c + (c * U >= t * SB ? 0 : 1);
-            const float v = p.partial[(static_cast<long long>(slot) * p.M + m) * kTileN + threadIdx.x];
-            y = c == first ? v : __fadd_rn(y, v);
-        }
-        store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y);
+    const int m = blockIdx.y * blockDim.y + threadIdx.y;
+    if (n >= Nloc || m >= p.M) return;
+    // the CTA's first segment when its run starts inside this tile, else its last one
+    auto part = [&](int c) {
+        const int slot = 2 * c + (c * U >= t * SB ? 0 : 1);
+        return __ldcg(p.partial + (static_cast<long long>(slot) * p.M + m) * kTileN + threadIdx.x);
+    };
+    float y = part(first);
+    int c = first + 1;
+    for (; c + 3 <= last; c += 4) {  // four loads in flight, added in ascending order
+        const float v0 = part(c), v1 = part(c + 1), v2 = part(c + 2), v3 = part(c + 3);
+        y = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(y, v0), v1), v2), v3);
     }
+    for (; c <= last; c++) y = __fadd_rn(y, part(c));
+    store_out<ODT>(p.Y[mi], static_cast<long long>(m) * Nloc + n, y);
 }
 
 static size_t gemm_smem_bytes(int mb) {
     const size_t need = 1024 + static_cast<size_t>(op_slots(mb) * kSuper) * (mb * 128) + static_cast<size_t>(kTeams * kRawStages) * kTileN * (128 + 32) +
-                        (2 * kMaxOpStages + 2) * 8 + 16;
+                        (2 * kBarStages + 2) * 8 + 16;
     // A CTA allocates all 512 TMEM columns, so a second CTA on the same SM would only sit in tcgen05.alloc until the
     // first one ends: ask for more than half of the SM's shared memory to keep it off the SM instead.
     const size_t half_sm = 120 * 1024;
@@ -677,6 +739,9 @@ static GemmPlan plan_gemm(int tiles, int K, int M, bool have_scratch, size_t ava
         const int sms = sm_count();
         int U = static_cast<int>((total + sms - 1) / sms);
         if (U < 2) U = g.sb < 2 ? g.sb : 2;
+        // More tiles than SMs and a wide batch: the partial tiles (2 x M x 128 floats per CTA, written and read back)
+        // and the longer epilogues cost more than the uneven waves do (measured at M = 64 on 224 tiles); whole tiles.
+        if (M > 32 && tiles >= sms) U = g.sb;
         // a workspace too small for the partial tiles: longer runs (fewer CTAs) until they fit; whole tiles need none
         while (plan_partial_bytes(static_cast<int>(total), g.sb, U, M) > avail) U++;
         g.U = U;
@@ -740,7 +805,7 @@ template <int MB, int ODT> static int launch_gemm(const GemmParams& p, cudaStrea
     count_launch();
     if (e != cudaSuccess) return set_cuda_status(e);
     if (p.units_per_cta % p.sb_per_tile != 0) {
-        gemm_partial_reduce_kernel<ODT><<<p.tile_end[2], dim3(kTileN, 4), 0, st>>>(p);
+        gemm_partial_reduce_kernel<ODT><<<dim3(p.tile_end[2], (p.M + 3) / 4), dim3(kTileN, 4), 0, st>>>(p);
         count_launch();
         return check_launch();
     }
