@@ -317,17 +317,20 @@ NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long s
  * scales 8-byte aligned.  Weights are rounded to f16 as (q-8)*scale like the reference's dequantisation;
  * accumulation is f32 in tensor memory.
  * `scratch` (may be NULL for f16 activations) holds, in this order, an f16 copy of bf16 activations (exact up to
- * +-65504, saturating beyond) and the f32 split-K partials that let small N fill all SMs; its size comes from
- * nve_b200_gemm_w4a16_scratch_bytes.  bf16 activations without enough scratch for their copy are refused with
- * NVE_ERR_TOO_LARGE; a scratch too small for split-K only lowers the split.
+ * +-65504, saturating beyond) and f32 partial tiles: with a workspace the (tile, 256-weight K slice) units are dealt
+ * to the SMs in equal contiguous runs, so that few tiles still fill all SMs and a tile count that is not a multiple
+ * of the SM count is balanced; tiles that several CTAs share are summed in ascending K order by a second kernel
+ * (reproducible for a given SM count).  Its size comes from nve_b200_gemm_w4a16_scratch_bytes.  bf16 activations
+ * without enough scratch for their copy are refused with NVE_ERR_TOO_LARGE; a scratch too small for the partial
+ * tiles only lengthens the runs (fewer CTAs), down to one whole tile per CTA, which needs none.
  * nve_b200_gemm_error returns the code latched by an expired bounded wait. */
 NVE_API size_t nve_b200_gemm_w4a16_scratch_bytes(int M, int N, int K);
 NVE_API int nve_b200_gemm_w4a16(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,
                                 int y_dtype, int M, int N, int K, void* scratch, size_t scratch_bytes,
                                 nve_stream_t stream);
 /* The same GEMM over 1..3 matrices that share X (q/k/v, gate/up) in one launch: mats[i].{nibbles, scales, out, N},
- * out [M, N_i] row-major, residual must be NULL.  Their 128-row tiles are laid side by side over the grid and
- * split-K is chosen for the total, which is what lets the narrow k and v projections fill the GPU. */
+ * out [M, N_i] row-major, residual must be NULL.  Their 128-row tiles follow one another in one unit sequence and the
+ * runs are chosen for the total, which is what lets the narrow k and v projections fill the GPU. */
 NVE_API size_t nve_b200_gemm_w4a16_multi_scratch_bytes(int M, const int* Ns, int num_mats, int K);
 NVE_API int nve_b200_gemm_w4a16_multi(const void* X, int x_dtype, const nve_b200_w4_matrix* mats, int num_mats,
                                       int y_dtype, int M, int K, void* scratch, size_t scratch_bytes,
@@ -337,18 +340,18 @@ NVE_API int nve_b200_gemm_error(int reset);
 /* Allocation-free form of nve_b200_gemm_w4a16.  No counterpart in the reference: it exists for callers that have
  * no workspace to pass and may not allocate one -- the reference's batch > 1 call site (GpuWeight::matmul_x,
  * src/gpu_layer.rs:220-239) only receives activations and weights and can run under CUDA-graph capture, where
- * cudaMalloc is illegal; a latency-critical serving thread is in the same position.  The split-K partial sums go
+ * cudaMalloc is illegal; a latency-critical serving thread is in the same position.  The partial tiles go
  * to a fixed 4 MiB array inside the library image (held on every GPU that loads the library until the process
  * exits) instead of a caller buffer.  Same arguments and results as nve_b200_gemm_w4a16 otherwise.
- *   - A shape whose workspace (split-K partial sums, plus the f16 copy of bf16 activations) exceeds 4 MiB is
+ *   - A shape whose workspace (partial tiles, plus the f16 copy of bf16 activations) exceeds 4 MiB is
  *     refused: NVE_ERR_TOO_LARGE.
  *   - The first call on each device resolves the array's device address and caches it; make that call before
  *     any stream capture begins.
  *   - All calls share the array and it keeps the previous call's contents (nothing in it needs to start at
  *     zero); two of these GEMMs running concurrently on one GPU race on it -- keep them on one stream.
- *   - The split over K is the one the workspace form would choose; it is not lowered to make a shape fit, so e.g.
- *     the 8B down projection at M = 64 with bf16 input (4 MiB of partials + a 1.8 MB f16 copy) is refused although a
- *     smaller split would fit: use the workspace form there.
+ *   - The work split is the one the workspace form would choose; it is not changed to make a shape fit, so e.g.
+ *     the 8B down projection at M = 64 (138 CTAs x 2 partial tiles x 64 x 128 floats = 9 MB) is refused although
+ *     longer runs would fit: use the workspace form there.
  *   - The cached address belongs to the device's current context: after cudaDeviceReset the library must be
  *     reloaded before this entry point is used again on that device. */
 NVE_API int nve_b200_gemm_w4a16_noalloc(const void* X, int x_dtype, const uint8_t* nibbles, const float* scales, void* Y,

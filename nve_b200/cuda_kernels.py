@@ -618,7 +618,7 @@ def gemm_w4a16_scratch_bytes(m: int, n: int, k: int) -> int:
 def gemm_w4a16(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out_dtype=None, out: Optional[Tensor] = None,
                scratch: Optional[Tensor] = None) -> Tensor:
     """Batched W4A16 GEMM on the tensor cores: x [M, K] (f16/bf16), M <= 64 -> [M, n].  `scratch` (uint8/float
-    tensor of gemm_w4a16_scratch_bytes) enables split-K for small n; bf16 activations need it for their f16 copy
+    tensor of gemm_w4a16_scratch_bytes) lets the CTAs share tiles over K (few tiles fill all SMs, uneven tile counts are balanced); bf16 activations need it for their f16 copy
     (allocated here when not given)."""
     m = x.shape[0]
     out_dtype = x.dtype if out_dtype is None else out_dtype
@@ -660,7 +660,7 @@ def gemm_w4a16_multi(x: Tensor, weights: Sequence, k: int, out_dtype=None, outs:
 
 def gemm_w4a16_noalloc(x: Tensor, nibbles: Tensor, scales: Tensor, n: int, k: int, out: Tensor) -> Tensor:
     """Batched W4A16 GEMM for callers that cannot allocate: the caller passes input and output tensors only, the
-    split-K workspace is a fixed 4 MiB array inside the library (shapes needing more raise NVE_ERR_TOO_LARGE).
+    workspace for partial tiles is a fixed 4 MiB array inside the library (shapes needing more raise NVE_ERR_TOO_LARGE).
     Calls share that array: keep them on one stream.  Make the first call on a device outside stream capture."""
     _ffi.check("nve_b200_gemm_w4a16_noalloc",
                _lib().nve_b200_gemm_w4a16_noalloc(_ptr(x, (torch.float16, torch.bfloat16), "x"), _dt(x),
