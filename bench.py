@@ -275,7 +275,12 @@ def gemv_shape_table(torch, ck, state, s, hbuf, tmp, shape, peak):
                             ck.rmsnorm_matvec_w4a16_multi(hbuf, w.input_norm, eps, None, mats, K, outs=[qv, kv_, vv])
                     elif gname == "gateup":
                         mats = [w.gate_proj.triple(), w.up_proj.triple()]
-                        if route == "w4a8":
+                        if state.fuse_silu:  # the step's own launch: + SiLU*up + conversion for the down projection
+                            q = ({"xq": s.xq_f, "xs": s.xs_f, "counters": s.pq_cnt} if route == "w4a8" else
+                                 {"xlo": s.xlo_f, "xhi": s.xq_f, "xs": s.xs_f, "counters": s.pq_cnt})
+                            ck.rmsnorm_gateup_silu(hbuf, w.post_attn_norm, eps, None, mats[0], mats[1], K, route == "w4a8",
+                                                   mid=s.gate, quant=q)
+                        elif route == "w4a8":
                             ck.rmsnorm_matvec_w4a8_multi(hbuf, w.post_attn_norm, eps, mats, K, outs=[s.gate, s.up])
                         else:
                             ck.rmsnorm_matvec_w4a16_multi(hbuf, w.post_attn_norm, eps, None, mats, K, outs=[s.gate, s.up])
@@ -573,12 +578,20 @@ def run_ours(args) -> None:
             if routes[li]:
                 ck.rmsnorm_matvec_w4a8_multi(hbuf, w.input_norm, eps, qkv, w.q_proj.k, outs=[qv, kv_, vv])
                 ck.matvec_w4a8_multi(s.xq_a, s.xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[hbuf], residuals=[hbuf])
-                ck.rmsnorm_matvec_w4a8_multi(hbuf, w.post_attn_norm, eps, gu, w.gate_proj.k, outs=[s.gate, s.up])
+                if state.fuse_silu:  # the step's own gate/up launch: SiLU*up + conversion for down in the epilogue
+                    ck.rmsnorm_gateup_silu(hbuf, w.post_attn_norm, eps, None, gu[0], gu[1], w.gate_proj.k, True, mid=s.gate,
+                                           quant={"xq": s.xq_f, "xs": s.xs_f, "counters": s.pq_cnt})
+                else:
+                    ck.rmsnorm_matvec_w4a8_multi(hbuf, w.post_attn_norm, eps, gu, w.gate_proj.k, outs=[s.gate, s.up])
                 ck.matvec_w4a8_multi(s.xq_f, s.xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[hbuf], residuals=[hbuf])
             else:
                 ck.rmsnorm_matvec_w4a16_multi(hbuf, w.input_norm, eps, None, qkv, w.q_proj.k, outs=[qv, kv_, vv])
                 ck.matvec_w4a16_multi(s.attn, None, [w.o_proj.triple()], w.o_proj.k, outs=[hbuf], residuals=[hbuf])
-                ck.rmsnorm_matvec_w4a16_multi(hbuf, w.post_attn_norm, eps, None, gu, w.gate_proj.k, outs=[s.gate, s.up])
+                if state.fuse_silu:
+                    ck.rmsnorm_gateup_silu(hbuf, w.post_attn_norm, eps, None, gu[0], gu[1], w.gate_proj.k, False, mid=s.gate,
+                                           quant={"xlo": s.xlo_f, "xhi": s.xq_f, "xs": s.xs_f, "counters": s.pq_cnt})
+                else:
+                    ck.rmsnorm_matvec_w4a16_multi(hbuf, w.post_attn_norm, eps, None, gu, w.gate_proj.k, outs=[s.gate, s.up])
                 # as in the step: the SiLU kernel has left the fixed-point planes of its result in the scratch buffers
                 ck.matvec_w4a16_planes_multi(s.xlo_f, s.xq_f, s.xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[hbuf],
                                              residuals=[hbuf])
@@ -681,7 +694,7 @@ def run_ours(args) -> None:
         config["workload"] += f" -- TRUNCATED to {args.layers} layers"
     config.update({"activations": "f16 (the reference ABI's activation type)", "kv_cache": "f16", "parallelism": "tp1",
                    "l2_policy": f"inputs larger than L2: {total_bytes / 1e9:.2f} GB streamed per step",
-                   "launches_per_step": launches_per_step, "graph": "one CUDA graph per token, six launches per layer",
+                   "launches_per_step": launches_per_step, "graph": f"one CUDA graph per token, {launches_per_step // shape.num_layers} launches per layer",
                    "programmatic_dependent_launch": pdl})
     line = {
         "metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,

@@ -263,6 +263,25 @@ NVE_API int nve_b200_rmsnorm_gateup_silu_w4a8(const void* h, const void* norm_we
 NVE_API int nve_b200_rmsnorm_gateup_silu_w4a16(const void* h, const void* norm_weight, float eps, int act_dtype,
                                                const float* awq, const nve_b200_w4_matrix* gate,
                                                const nve_b200_w4_matrix* up, void* mid_out, int K, nve_stream_t stream);
+/* The same launch, which in addition leaves mid converted for the down projection, so that neither a SiLU*up
+ * kernel nor a quantiser runs between the gate/up and the down GEMV (src/gpu_layer.rs:937-947 in two launches):
+ *   _q8_w4a8:   mid_q [N] int8 codes + mid_scales [N/32], the bits of nve_quantize_f16_q8 on mid;
+ *   _x16_w4a16: the 16-bit fixed-point planes mid_lo / mid_hi [N] + mid_scales [N/32] that
+ *               nve_b200_matvec_w4a16_planes_multi reads (down_awq, optional, multiplies mid first, as the W4A16
+ *               GEMV's own staging does).
+ * A CTA writes a contiguous range of mid; the CTA whose store completes a 32-wide group converts that group
+ * (group_counters [N/32] u32 count the values written per group: zero them once, every launch adds 32 to each; a
+ * buffer belongs to one mid vector and to launches that are ordered on one stream).  N % 32 == 0; mid_out 16-byte,
+ * mid_q / mid_lo / mid_hi 8-byte aligned. */
+NVE_API int nve_b200_rmsnorm_gateup_silu_q8_w4a8(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                 const float* awq_inv, const nve_b200_w4_matrix* gate,
+                                                 const nve_b200_w4_matrix* up, void* mid_out, int K, int8_t* mid_q,
+                                                 float* mid_scales, unsigned* group_counters, nve_stream_t stream);
+NVE_API int nve_b200_rmsnorm_gateup_silu_x16_w4a16(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                   const float* awq, const nve_b200_w4_matrix* gate,
+                                                   const nve_b200_w4_matrix* up, void* mid_out, int K, uint8_t* mid_lo,
+                                                   int8_t* mid_hi, float* mid_scales, const float* down_awq,
+                                                   unsigned* group_counters, nve_stream_t stream);
 /* W4A8 GEMV whose int8 activation codes are produced in the kernel prologue from a 16-bit vector x (every CTA runs
  * the arithmetic of nve_b200_quantize_q8 / _awq on it): nve_quantize_f16_q8 + nve_matvec_w4a8
  * (src/gpu_layer.rs:946-947) in one launch, bit-identical to the two.  Output type = x_dtype; residual as in

@@ -133,6 +133,9 @@ SIGNATURES = {
     "nve_b200_rmsnorm_matvec_w4a16_multi": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), _I, _I, _I, _P]),
     "nve_b200_rmsnorm_gateup_silu_w4a8": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
     "nve_b200_rmsnorm_gateup_silu_w4a16": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
+    "nve_b200_rmsnorm_gateup_silu_q8_w4a8": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P, _P, _P, _P]),
+    "nve_b200_rmsnorm_gateup_silu_x16_w4a16": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P, _P, _P,
+                                                    _P, _P, _P]),
     "nve_b200_quantize_matvec_w4a8_multi": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _P]),
     "nve_b200_quantize_matvec_w4a8_allreduce": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _P]),
     "nve_b200_attn_decode_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),

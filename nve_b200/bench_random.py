@@ -11,6 +11,7 @@ median so that the top half of the layers runs W4A16 and the rest W4A8.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -133,6 +134,9 @@ def build_state(shape: ModelShape, seed: int, context: int, max_seq: Optional[in
     cos, sin = rope_tables(shape.head_dim, max_seq, 10000.0, device)
     norm, routing = seeded_routing(shape.num_layers, seed)
     state = GpuInferenceState(lw, kv, shape.num_heads, shape.num_kv_heads, shape.head_dim, 1e-5, cos, sin, routing, fused)
+    # five launches per layer (SiLU*up and the conversion for the down projection inside the gate/up launch) unless
+    # NVE_B200_FUSE_SILU=0 asks for the six-launch schedule; both produce the same bits
+    state.fuse_silu = os.environ.get("NVE_B200_FUSE_SILU", "1") != "0"
     return state, norm[:layers]
 
 

@@ -261,6 +261,57 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_w4_kernel(const GemvPara
     if ((p.nb % kWarp) == 0 && (S % C) == 0) stream(std::true_type{});
     else stream(std::false_type{});
 
+    if constexpr (PAIR && !IDOT && ODT != NVE_DT_F32) {
+        if (p.pq_mode != 0) {
+            // ---- conversion of completed 32-wide groups of out[] for the down projection.  A CTA writes a contiguous
+            // range of out[]; after its last store it adds, per group it touched, the number of values it wrote to
+            // that group's counter.  Whoever brings a counter to a multiple of 32 wrote last: every value of the
+            // group is visible (fence before the count, fence after it), and that CTA converts the group with the
+            // arithmetic of the stand-alone activation kernels (same bits as SiLU*up + quantise).
+            constexpr int H = R / 2;
+            __threadfence();
+            __syncthreads();
+            if (warp == 0) {
+                const int lo = tile_begin * H, hi = min(tile_end * H, p.row_end[0]);
+                if (hi > lo) {
+                    const int g_first = lo >> 5, g_last = (hi - 1) >> 5;
+                    const int tq = lane & 3;
+                    for (int gb = g_first; gb <= g_last; gb += 8) {
+                        const int g = gb + (lane >> 2);
+                        int mine = 0;
+                        if (tq == 0 && g <= g_last) {
+                            const unsigned n = static_cast<unsigned>(min(hi, (g + 1) * 32) - max(lo, g * 32));
+                            const unsigned old = atomicAdd(p.pq_cnt + g, n);
+                            mine = ((old + n) & 31u) == 0u;
+                        }
+                        mine = __shfl_sync(0xffffffffu, mine, lane & ~3);
+                        if (__any_sync(0xffffffffu, mine)) {
+                            __threadfence();
+                            const long long chunk = static_cast<long long>(g) * 4 + tq;  // 8 values of the group
+                            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                            if (mine) {
+                                const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.out[0]) + chunk);
+                                uint16_t h[8];
+                                unpack8(raw, h);
+#pragma unroll
+                                for (int e = 0; e < 8; e++) v[e] = Act16<ODT>::to_f32(h[e]);
+                            }
+                            if (p.pq_mode == 1) {
+                                quantize_quad(v, p.pq_xq, p.pq_xs, chunk, mine != 0);
+                            } else {
+                                if (mine && p.pq_awq != nullptr) {
+#pragma unroll
+                                    for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], p.pq_awq[chunk * 8 + e]);
+                                }
+                                x16_quad(v, p.pq_xlo, p.pq_xq, p.pq_xs, chunk, mine != 0);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
     if constexpr (!IDOT) {
         if (p.tp.world > 1) {
             // ---- fused all-reduce: every rank has pushed (or is pushing) its partial rows into this rank's buffer;
@@ -464,6 +515,12 @@ static int fill_params(GemvParams& p, const nve_b200_w4_matrix* mats, int num_ma
     p.S = (p.nb + kWarp - 1) / kWarp;
     p.xq = nullptr; p.xs = nullptr; p.x16 = nullptr; p.xlo = nullptr; p.awq = nullptr; p.idot = nullptr;
     p.paired = 0;
+    p.pq_mode = 0;
+    p.pq_cnt = nullptr;
+    p.pq_xq = nullptr;
+    p.pq_xlo = nullptr;
+    p.pq_xs = nullptr;
+    p.pq_awq = nullptr;
     p.norm_w = nullptr; p.eps = 0.0f;
     p.tp.world = 0; p.tp.rank = 0; p.tp.rows_cap = 0; p.tp.err = nullptr;
     p.tp.counter = nullptr;
@@ -624,6 +681,55 @@ extern "C" int nve_b200_rmsnorm_gateup_silu_w4a16(const void* h, const void* nor
     if (st != NVE_OK) return set_status(st);
     if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
     p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<2, NVE_DT_F16, 1, true>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<2, NVE_DT_BF16, 1, true>(p, 2, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+// The paired form that also leaves silu(gate)*up converted for the down projection (see the end of the kernel).
+static int attach_pair_quant(GemvParams& p, int mode, unsigned* counters, int8_t* xq, uint8_t* xlo, float* xs, const float* awq) {
+    if (!counters || !xq || !xs || (mode == 2 && !xlo)) return NVE_ERR_BAD_POINTER;
+    if ((p.row_end[0] % 32) != 0) return NVE_ERR_BAD_SHAPE;
+    if (!aligned(p.out[0], 16) || !aligned(xq, 8) || (xlo && !aligned(xlo, 8))) return NVE_ERR_BAD_ALIGNMENT;
+    p.pq_mode = mode;
+    p.pq_cnt = counters;
+    p.pq_xq = xq;
+    p.pq_xlo = xlo;
+    p.pq_xs = xs;
+    p.pq_awq = awq;
+    return NVE_OK;
+}
+
+extern "C" int nve_b200_rmsnorm_gateup_silu_q8_w4a8(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                    const float* awq_inv, const nve_b200_w4_matrix* gate,
+                                                    const nve_b200_w4_matrix* up, void* mid_out, int K, int8_t* mid_q,
+                                                    float* mid_scales, unsigned* group_counters, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_gateup(p, gate, up, mid_out, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq_inv;
+    st = attach_pair_quant(p, 1, group_counters, mid_q, nullptr, mid_scales, nullptr);
+    if (st != NVE_OK) return set_status(st);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (act_dtype == NVE_DT_F16) return dispatch_same_dt<1, NVE_DT_F16, 1, true>(p, 2, cs);
+    if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<1, NVE_DT_BF16, 1, true>(p, 2, cs);
+    return set_status(NVE_ERR_BAD_DTYPE);
+}
+
+extern "C" int nve_b200_rmsnorm_gateup_silu_x16_w4a16(const void* h, const void* norm_weight, float eps, int act_dtype,
+                                                      const float* awq, const nve_b200_w4_matrix* gate,
+                                                      const nve_b200_w4_matrix* up, void* mid_out, int K, uint8_t* mid_lo,
+                                                      int8_t* mid_hi, float* mid_scales, const float* down_awq,
+                                                      unsigned* group_counters, nve_stream_t stream) {
+    GemvParams p;
+    int st = fill_gateup(p, gate, up, mid_out, K);
+    if (st != NVE_OK) return set_status(st);
+    if (!h || !norm_weight) return set_status(NVE_ERR_BAD_POINTER);
+    p.x16 = h; p.norm_w = norm_weight; p.eps = eps; p.awq = awq;
+    st = attach_pair_quant(p, 2, group_counters, mid_hi, mid_lo, mid_scales, down_awq);
+    if (st != NVE_OK) return set_status(st);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (act_dtype == NVE_DT_F16) return dispatch_same_dt<2, NVE_DT_F16, 1, true>(p, 2, cs);
     if (act_dtype == NVE_DT_BF16) return dispatch_same_dt<2, NVE_DT_BF16, 1, true>(p, 2, cs);

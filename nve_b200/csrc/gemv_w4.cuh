@@ -45,6 +45,16 @@ struct GemvParams {
     int32_t* idot;      // debug: per-block integer dots [n_total, nb]
     int paired;         // gate/up with SiLU*up in the epilogue: a tile holds R/2 gate rows (matrix 0) and the R/2 up
                         // rows (matrix 1) of the same indices; out[0] receives silu(gate) * up, [row_end[0]] values
+    // paired form only: the CTA that completes a 32-wide group of silu(gate)*up values converts the group for the
+    // down projection (pq_mode 1: int8 codes + scale, 2: 16-bit fixed-point planes + scale), so that no separate
+    // activation kernel and no per-CTA quantiser prologue is needed.  pq_cnt[g] counts the values written to group g
+    // (32 per launch, never reset).
+    int pq_mode;
+    unsigned* pq_cnt;
+    int8_t* pq_xq;      // int8 codes (mode 1) / high-byte plane (mode 2)
+    uint8_t* pq_xlo;    // low-byte plane (mode 2)
+    float* pq_xs;       // per-group scales
+    const float* pq_awq; // optional per-column multiplier of the down projection (mode 2)
     TpDev tp;           // all-reduce of the (single) output over the tensor-parallel ranks
 };
 

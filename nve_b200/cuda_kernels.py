@@ -493,16 +493,31 @@ def rmsnorm_matvec_w4a16_multi(h: Tensor, norm_weight: Tensor, eps: float, awq: 
 
 
 def rmsnorm_gateup_silu(h: Tensor, norm_weight: Tensor, eps: float, awq: Optional[Tensor], gate, up, k: int, use_w4a8: bool,
-                        mid: Optional[Tensor] = None) -> Tensor:
-    """RMSNorm + gate/up GEMV + SiLU*up in one launch; gate / up are (nibbles, scales, n) triples; returns mid [1, n]."""
+                        mid: Optional[Tensor] = None, quant: Optional[dict] = None) -> Tensor:
+    """RMSNorm + gate/up GEMV + SiLU*up in one launch; gate / up are (nibbles, scales, n) triples; returns mid [1, n].
+
+    `quant` also leaves mid converted for the down projection (the CTA that completes a 32-wide group converts it):
+    W4A8 route {"xq": int8 [n], "xs": f32 [n/32], "counters": int32 [n/32]}; W4A16 route {"xlo": uint8 [n], "xhi": int8
+    [n], "xs": ..., "counters": ..., "down_awq": optional f32 [n]}.  `counters` is zeroed once by the caller and then
+    only ever passed to launches for this mid vector."""
     n = gate[2]
     mid = torch.empty((1, n), dtype=h.dtype, device=h.device) if mid is None else mid
     g = W4Matrix(_ptr(gate[0], torch.uint8), _ptr(gate[1], torch.float32), None, None, n)
     u = W4Matrix(_ptr(up[0], torch.uint8), _ptr(up[1], torch.float32), None, None, up[2])
-    fn = "nve_b200_rmsnorm_gateup_silu_w4a8" if use_w4a8 else "nve_b200_rmsnorm_gateup_silu_w4a16"
-    _ffi.check(fn, getattr(_lib(), fn)(_ptr(h, (torch.float16, torch.bfloat16), "h"), _ptr(norm_weight, h.dtype), float(eps),
-                                       _dt(h), _ptr(awq, torch.float32), C.byref(g), C.byref(u), _ptr(mid, h.dtype), k,
-                                       stream()))
+    head = (_ptr(h, (torch.float16, torch.bfloat16), "h"), _ptr(norm_weight, h.dtype), float(eps), _dt(h),
+            _ptr(awq, torch.float32), C.byref(g), C.byref(u), _ptr(mid, h.dtype), k)
+    if quant is None:
+        fn = "nve_b200_rmsnorm_gateup_silu_w4a8" if use_w4a8 else "nve_b200_rmsnorm_gateup_silu_w4a16"
+        _ffi.check(fn, getattr(_lib(), fn)(*head, stream()))
+    elif use_w4a8:
+        fn = "nve_b200_rmsnorm_gateup_silu_q8_w4a8"
+        _ffi.check(fn, getattr(_lib(), fn)(*head, _ptr(quant["xq"], _Q8, "xq"), _ptr(quant["xs"], torch.float32, "xs"),
+                                           _ptr(quant["counters"], torch.int32, "counters"), stream()))
+    else:
+        fn = "nve_b200_rmsnorm_gateup_silu_x16_w4a16"
+        _ffi.check(fn, getattr(_lib(), fn)(*head, _ptr(quant["xlo"], torch.uint8, "xlo"), _ptr(quant["xhi"], _Q8, "xhi"),
+                                           _ptr(quant["xs"], torch.float32, "xs"), _ptr(quant.get("down_awq"), torch.float32),
+                                           _ptr(quant["counters"], torch.int32, "counters"), stream()))
     return mid
 
 

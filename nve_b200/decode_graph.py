@@ -36,6 +36,7 @@ class _LayerScratch:
     xq_f: Tensor
     xs_f: Tensor
     xlo_f: Tensor
+    pq_cnt: Tensor  # per 32-wide group of the FFN activation: values written so far (five-launch layer)
 
 
 class StaticDecodeGraph:
@@ -71,6 +72,7 @@ class StaticDecodeGraph:
             xq_f=torch.zeros(ffn_size, dtype=torch.int8, device=dev),
             xs_f=torch.zeros(ffn_size // 32, dtype=torch.float32, device=dev),
             xlo_f=torch.zeros(ffn_size, dtype=torch.uint8, device=dev),
+            pq_cnt=torch.zeros(max(1, ffn_size // 32), dtype=torch.int32, device=dev),
         )
         self.s = s
         self.routes: List[bool] = [state.routing.use_w4a8(x) for x in self.importance]
@@ -142,9 +144,9 @@ class StaticDecodeGraph:
 
 class PersistentDecode:
     """The same decode step as `StaticDecodeGraph`, run by ONE persistent kernel (nve_b200_decode_step) instead of
-    six launches per layer.  The launch is recorded into the library's graph like the layer sequence is, so
+    five or six launches per layer.  The launch is recorded into the library's graph like the layer sequence is, so
     `replay` / `replay_resident` drive it through the same pinned position scalars; the hidden state it leaves is
-    bit-identical to the six-launch graph.  `lm_head` = (GpuW4, final_norm weight, use_w4a8) adds the device-side
+    bit-identical to the graph of separate launches.  `lm_head` = (GpuW4, final_norm weight, use_w4a8) adds the device-side
     final RMSNorm + lm_head GEMV; logits land in `self.logits` (f32)."""
 
     def __init__(self, state: GpuInferenceState, hidden_size: int, ffn_size: int, importance: Sequence[float],

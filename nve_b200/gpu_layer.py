@@ -9,7 +9,8 @@ Two schedules compute the same thing:
   * ``fused=False`` issues exactly the reference's sequence of kernels (one launch per reference call);
   * ``fused=True`` uses the fused entry points (RMSNorm inside the q/k/v and gate/up GEMV prologue, RoPE +
     KV write + attention + quantise in one kernel, SiLU*up->quantise, residual add in the GEMV epilogue):
-    six launches per layer.  Both give bit-identical hidden states.
+    six launches per layer, or five with ``state.fuse_silu`` (SiLU*up and the conversion for the down projection
+    inside the gate/up launch).  All give bit-identical hidden states.
 """
 from __future__ import annotations
 
@@ -140,8 +141,8 @@ class GpuInferenceState:
     rope_sin: Tensor
     routing: RoutingConfig = field(default_factory=RoutingConfig)
     fused: bool = True
-    # fused schedule only: SiLU*up in the gate/up epilogue and the quantiser in the down prologue (five launches per
-    # layer instead of six; same bits)
+    # fused schedule only: SiLU*up in the gate/up epilogue, which also converts the result for the down projection
+    # (five launches per layer instead of six; same bits)
     fuse_silu: bool = False
     # device scalars for position / valid length of the eager path
     d_pos: Optional[Tensor] = None
@@ -265,8 +266,10 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
     ffn = w.gate_proj.n
     s = scratch
 
-    def buf(name, shape, dtype=f16):
-        return getattr(s, name) if s is not None else torch.empty(shape, dtype=dtype, device=dev)
+    def buf(name, shape, dtype=f16, zero=False):
+        if s is not None:
+            return getattr(s, name)
+        return (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=dev)
 
     q, k, v = buf("q", (nh, hd)), buf("k", (nkv, hd)), buf("v", (nkv, hd))
     attn = buf("attn", (1, nh * hd))
@@ -286,10 +289,11 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
         gemv8 = ck.matvec_w4a8_allreduce if allreduce else ck.matvec_w4a8_multi
         gemv8(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
         if state.fuse_silu:
+            # SiLU*up in the gate/up epilogue; the CTA that completes a 32-wide group of it writes the group's int8 codes
+            cnt = buf("pq_cnt", (ffn // 32,), torch.int32, zero=True)
             ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, None, w.gate_proj.triple(), w.up_proj.triple(), w.gate_proj.k,
-                                   True, mid=gate)
-            ck.quantize_matvec_w4a8_multi(gate, None, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1],
-                                          allreduce=allreduce)
+                                   True, mid=gate, quant={"xq": xq_f, "xs": xs_f, "counters": cnt})
+            gemv8(xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
             return h1
         ck.rmsnorm_matvec_w4a8_multi(h1, w.post_attn_norm, eps, [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k,
                                      outs=[gate, up])
@@ -301,18 +305,22 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
                              hd, max_seq, scale)
         gemv16 = ck.matvec_w4a16_allreduce if allreduce else ck.matvec_w4a16_multi
         gemv16(attn, w.o_proj.awq_scales, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
+        xlo_f = buf("xlo_f", (ffn,), torch.uint8)
+        down16 = ck.matvec_w4a16_planes_allreduce if allreduce else ck.matvec_w4a16_planes_multi
         if state.fuse_silu:
+            # ... or the group's 16-bit fixed-point planes, as the stand-alone SiLU kernel below would
+            cnt = buf("pq_cnt", (ffn // 32,), torch.int32, zero=True)
             ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales, w.gate_proj.triple(),
-                                   w.up_proj.triple(), w.gate_proj.k, False, mid=gate)
-            gemv16(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
+                                   w.up_proj.triple(), w.gate_proj.k, False, mid=gate,
+                                   quant={"xlo": xlo_f, "xhi": xq_f, "xs": xs_f, "counters": cnt,
+                                          "down_awq": w.down_proj.awq_scales})
+            down16(xlo_f, xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
             return h1
         ck.rmsnorm_matvec_w4a16_multi(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales,
                                       [w.gate_proj.triple(), w.up_proj.triple()], w.gate_proj.k, outs=[gate, up])
         # the fixed-point form of silu(gate)*up is produced once here instead of by every CTA of the GEMV
-        xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
-        xlo_f = buf("xlo_f", (ffn,), torch.uint8)
         ck.silu_mul_x16(gate, up, w.down_proj.awq_scales, x_lo=xlo_f, x_hi=xq_f, scales=xs_f)
-        down16 = ck.matvec_w4a16_planes_allreduce if allreduce else ck.matvec_w4a16_planes_multi
         down16(xlo_f, xq_f, xs_f, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
     return h1
 

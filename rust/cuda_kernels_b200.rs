@@ -101,6 +101,15 @@ extern "C" {
     pub fn nve_b200_rmsnorm_gateup_silu_w4a16(h: *const CVoid, norm_weight: *const CVoid, eps: f32, act_dtype: i32,
                                               awq: *const f32, gate: *const NveB200W4Matrix, up: *const NveB200W4Matrix,
                                               mid_out: *mut CVoid, k: i32, stream: Stream) -> i32;
+    pub fn nve_b200_rmsnorm_gateup_silu_q8_w4a8(h: *const CVoid, norm_weight: *const CVoid, eps: f32, act_dtype: i32,
+                                                awq_inv: *const f32, gate: *const NveB200W4Matrix, up: *const NveB200W4Matrix,
+                                                mid_out: *mut CVoid, k: i32, mid_q: *mut i8, mid_scales: *mut f32,
+                                                group_counters: *mut u32, stream: Stream) -> i32;
+    pub fn nve_b200_rmsnorm_gateup_silu_x16_w4a16(h: *const CVoid, norm_weight: *const CVoid, eps: f32, act_dtype: i32,
+                                                  awq: *const f32, gate: *const NveB200W4Matrix, up: *const NveB200W4Matrix,
+                                                  mid_out: *mut CVoid, k: i32, mid_lo: *mut u8, mid_hi: *mut i8,
+                                                  mid_scales: *mut f32, down_awq: *const f32, group_counters: *mut u32,
+                                                  stream: Stream) -> i32;
     pub fn nve_b200_quantize_matvec_w4a8_multi(x: *const CVoid, x_dtype: i32, awq_inv: *const f32,
                                                mats: *const NveB200W4Matrix, num_mats: i32, k: i32, stream: Stream) -> i32;
 

@@ -403,6 +403,51 @@ def test_gateup_silu_epilogue_equals_gemv_plus_silu(cuda, orc, route, K, F):
     assert torch.equal(mid, gate)
 
 
+@pytest.mark.parametrize("route", ["w4a8", "w4a16"])
+@pytest.mark.parametrize("K,F", [(4096, 14336), (2048, 512), (1024, 288), (512, 96)])
+def test_gateup_silu_group_conversion_equals_activation_kernels(cuda, orc, route, K, F):
+    """The quantising form of the fused gate/up launch leaves, besides mid, exactly what the stand-alone SiLU*up +
+    quantise kernels leave for the down projection (int8 codes / 16-bit fixed-point planes + scales), on three launches
+    in a row with different inputs over the same group counters (stale or double conversions would show)."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    mats = []
+    for i in range(2):
+        W = orc.fill_normal(F * K, 775, i, scale=0.02).reshape(F, K)
+        nib, sc = orc.extract_for_gpu(orc.quantize_q4(W))
+        mats.append((dev(nib), dev(sc), F))
+    w = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(K, 775, 10)), torch.float16)
+    awq = dev((1.0 + 0.25 * np.abs(orc.fill_normal(F, 775, 11))).astype(np.float32)) if route == "w4a16" else None
+    cnt = torch.zeros(F // 32, dtype=torch.int32, device="cuda")
+    xq = torch.full((F,), 99, dtype=torch.int8, device="cuda")
+    xlo = torch.full((F,), 99, dtype=torch.uint8, device="cuda")
+    xs = torch.full((F // 32,), -1.0, dtype=torch.float32, device="cuda")
+    for call in range(3):
+        h = dev(orc.to_act16(orc.fill_normal(K, 775, 20 + call) * (3.0 + call)), torch.float16).view(1, -1)
+        if route == "w4a8":
+            gate, up = ck.rmsnorm_matvec_w4a8_multi(h, w, 1e-5, mats, K)
+            want_q = torch.empty((F,), dtype=torch.int8, device="cuda")
+            want_s = torch.empty((F // 32,), dtype=torch.float32, device="cuda")
+            want_mid = ck.silu_mul_quantize_q8(gate, up, want_mid=True, xq=want_q, scales=want_s)[2]
+            mid = ck.rmsnorm_gateup_silu(h, w, 1e-5, None, mats[0], mats[1], K, True,
+                                         quant={"xq": xq, "xs": xs, "counters": cnt})
+            torch.cuda.synchronize()
+            assert torch.equal(xq, want_q) and torch.equal(xs, want_s), f"call {call}"
+        else:
+            gate, up = ck.rmsnorm_matvec_w4a16_multi(h, w, 1e-5, None, mats, K)
+            want_lo = torch.empty((F,), dtype=torch.uint8, device="cuda")
+            want_hi = torch.empty((F,), dtype=torch.int8, device="cuda")
+            want_s = torch.empty((F // 32,), dtype=torch.float32, device="cuda")
+            want_mid = ck.silu_mul_x16(gate, up, awq, want_mid=True, x_lo=want_lo, x_hi=want_hi, scales=want_s)[3]
+            mid = ck.rmsnorm_gateup_silu(h, w, 1e-5, None, mats[0], mats[1], K, False,
+                                         quant={"xlo": xlo, "xhi": xq, "xs": xs, "counters": cnt, "down_awq": awq})
+            torch.cuda.synchronize()
+            assert torch.equal(xlo, want_lo) and torch.equal(xq, want_hi) and torch.equal(xs, want_s), f"call {call}"
+        assert int(cnt.min()) == 32 * (call + 1) and int(cnt.max()) == 32 * (call + 1)
+        assert torch.equal(mid, want_mid)
+
+
 def test_quantizing_prologue_equals_quantiser_plus_gemv(cuda, orc):
     from nve_b200 import cuda_kernels as ck
 
