@@ -48,7 +48,7 @@ struct GemvParams {
     // paired form only: the CTA that completes a 32-wide group of silu(gate)*up values converts the group for the
     // down projection (pq_mode 1: int8 codes + scale, 2: 16-bit fixed-point planes + scale), so that no separate
     // activation kernel and no per-CTA quantiser prologue is needed.  pq_cnt[g] counts the values written to group g
-    // (32 per launch, never reset).
+    // (32 per launch, never reset; the test is on the count modulo 32, so the wrap of the 32-bit counter is harmless).
     int pq_mode;
     unsigned* pq_cnt;
     int8_t* pq_xq;      // int8 codes (mode 1) / high-byte plane (mode 2)

@@ -144,6 +144,11 @@ class GpuInferenceState:
     # fused schedule only: SiLU*up in the gate/up epilogue, which also converts the result for the down projection
     # (five launches per layer instead of six; same bits)
     fuse_silu: bool = False
+    # with fuse_silu: where SiLU*up is converted for the down projection -- False: by the gate/up CTA that completes a
+    # 32-wide group (best at one GPU, where every down CTA would otherwise convert the whole FFN vector itself);
+    # True: in the prologue of the down GEMV (best under tensor parallelism, where the FFN shard is short and the
+    # fence + count + convert tail of the gate/up launch costs more than it saves)
+    convert_in_down_prologue: bool = False
     # device scalars for position / valid length of the eager path
     d_pos: Optional[Tensor] = None
     d_seqlen: Optional[Tensor] = None
@@ -288,6 +293,12 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
                              hd, max_seq, scale, out_q=xq_a, out_scales=xs_a)
         gemv8 = ck.matvec_w4a8_allreduce if allreduce else ck.matvec_w4a8_multi
         gemv8(xq_a, xs_a, [w.o_proj.triple()], w.o_proj.k, outs=[h1], residuals=[hidden])
+        if state.fuse_silu and state.convert_in_down_prologue:
+            ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, None, w.gate_proj.triple(), w.up_proj.triple(), w.gate_proj.k,
+                                   True, mid=gate)
+            ck.quantize_matvec_w4a8_multi(gate, None, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1],
+                                          allreduce=allreduce)
+            return h1
         if state.fuse_silu:
             # SiLU*up in the gate/up epilogue; the CTA that completes a 32-wide group of it writes the group's int8 codes
             cnt = buf("pq_cnt", (ffn // 32,), torch.int32, zero=True)
@@ -308,6 +319,11 @@ def _layer_forward_fused(hidden: Tensor, w: GpuLayerWeights, state: GpuInference
         xq_f, xs_f = buf("xq_f", (ffn,), torch.int8), buf("xs_f", (ffn // 32,), torch.float32)
         xlo_f = buf("xlo_f", (ffn,), torch.uint8)
         down16 = ck.matvec_w4a16_planes_allreduce if allreduce else ck.matvec_w4a16_planes_multi
+        if state.fuse_silu and state.convert_in_down_prologue:
+            ck.rmsnorm_gateup_silu(h1, w.post_attn_norm, eps, w.gate_proj.awq_scales, w.gate_proj.triple(),
+                                   w.up_proj.triple(), w.gate_proj.k, False, mid=gate)
+            gemv16(gate, w.down_proj.awq_scales, [w.down_proj.triple()], w.down_proj.k, outs=[h1], residuals=[h1])
+            return h1
         if state.fuse_silu:
             # ... or the group's 16-bit fixed-point planes, as the stand-alone SiLU kernel below would
             cnt = buf("pq_cnt", (ffn // 32,), torch.int32, zero=True)

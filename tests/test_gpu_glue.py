@@ -471,9 +471,11 @@ def test_five_launch_graph_equals_six_launch_graph(cuda, orc):
     hidden, ffn, nh, nkv, hd, layers, max_seq = 2048, 8192, 32, 8, 64, 4, 16
     imp = [0.1, 0.9, 0.4, 1.0]
     outs = []
-    for fuse in (False, True):
+    # six launches; five with the conversion at the tail of the gate/up launch; five with it in the down prologue
+    for fuse, in_prologue in ((False, False), (True, False), (True, True)):
         st = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 791, True)
         st.fuse_silu = fuse
+        st.convert_in_down_prologue = in_prologue
         graph = StaticDecodeGraph(st, hidden, ffn, imp)
         graph.capture()
         assert graph.launches_per_replay == (5 if fuse else 6) * layers
@@ -486,5 +488,6 @@ def test_five_launch_graph_equals_six_launch_graph(cuda, orc):
             outs.append(res)
         finally:
             graph.destroy()
-    for a, b in zip(*outs):
-        assert torch.equal(a, b)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
