@@ -441,6 +441,30 @@ def gemm_batch_table(torch, ck, state, shape, peak):
     return table, err
 
 
+def prefill_entry(torch, ck, state, shape, S: int = 256):
+    """A prompt block of S positions through all layers with gpu_layer_forward_prefill (tcgen05 GEMM projections in
+    64-row slices, one-launch RMSNorm rows / KV rows / causal attention).  Eager launches, allocations included: the
+    reference has no graph for prefill either (src/gpu_layer.rs:1086-1160)."""
+    from nve_b200.gpu_layer import gpu_layer_forward_prefill
+
+    x = ck.fill_normal(S * shape.hidden, SEED, 9500, dtype=torch.float16).view(S, shape.hidden)
+    layers = len(state.layer_weights)
+
+    def run(_i):
+        h = x
+        for li in range(layers):
+            h = gpu_layer_forward_prefill(h, li, state, 0)
+        return h
+
+    out = run(0)
+    torch.cuda.synchronize()
+    finite = bool(torch.isfinite(out.float()).all())
+    ms = time_events(torch, run, 3)
+    return {"workload": f"prompt block of {S} positions through all {layers} layers (positions 0..{S - 1}, 16-bit route)",
+            "ms": round(ms, 3), "prompt_tok_s": round(S / (ms * 1e-3), 1), "output_finite": finite,
+            "gemm_error": ck.gemm_error()}
+
+
 def lm_head_entries(torch, ck, state, shape, importance, h0, pos):
     """The same step with the final RMSNorm + lm_head on the device (the reference leaves them on the host): W4
     lm_head (328 MB per token) and dense f16 lm_head (1051 MB per token)."""
@@ -667,6 +691,7 @@ def run_ours(args) -> None:
                                      "bit_identical_to_graph": same, "error_word": pers.error()}
         pers.destroy()
         extras["lm_head"] = lm_head_entries(torch, ck, state, shape, importance, h0, pos)
+        extras["prefill"] = prefill_entry(torch, ck, state, shape)
         table, gerr = gemm_batch_table(torch, ck, state, shape, peak)
         extras["gemm_batch"] = {"rows": table, "error_word": gerr,
                                 "tensor_pipe_pct": {"value": 6.4, "source": "sm__pipe_tensor_cycles_active of the gate/up "

@@ -207,6 +207,27 @@ NVE_API int nve_b200_silu_mul_x16(const void* gate, const void* up, void* mid_ou
 
 /* silu(gate)*up and residual add with selectable 16-bit type. */
 NVE_API int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_stream_t stream);
+
+/* ---- prefill (a block of S new positions of one sequence; src/gpu_layer.rs:777-890, :1086-1160) --------------
+ * The projections of a block go through nve_b200_gemm_w4a16 / _multi (M = S, in slices of 64 rows); these three
+ * entry points are the glue around them.
+ * nve_b200_rms_norm_rows: RMSNorm of every row of x [rows, n] with one weight vector, one launch (the reference runs
+ *   its kernel once per token, src/gpu_layer.rs:137); each row is bit-identical to nve_b200_rms_norm on it.
+ * nve_b200_kv_cache_write_rows: cache[kvh, start_pos + s, :] = new[s, kvh, :] for K and V (k_new / v_new
+ *   [rows, num_kv_heads, head_dim], caches [num_kv_heads, max_seq_len, head_dim]); replaces the transpose + append of
+ *   src/gpu_layer.rs:814-818.
+ * nve_b200_attn_prefill_causal: row r of q [rows, num_heads * head_dim] attends to positions [0, start_pos + r] of the
+ *   caches (which already hold the block); out has q's layout.  Replaces the unfused masked SDPA of
+ *   src/gpu_layer.rs:846-885; every row equals a nve_flash_decode_f16 call of length start_pos + r + 1 bit for bit
+ *   (the decode kernel with the row as second grid dimension).  head_dim 64 or 128; q and caches 16-byte aligned. */
+NVE_API int nve_b200_rms_norm_rows(const void* x, const void* weight, void* out, int rows, int n, float eps, int dtype,
+                                   nve_stream_t stream);
+NVE_API int nve_b200_kv_cache_write_rows(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new,
+                                         uint16_t* v_cache, int rows, int start_pos, int num_kv_heads, int head_dim,
+                                         int max_seq_len, nve_stream_t stream);
+NVE_API int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                                         uint16_t* out, int rows, int start_pos, int num_heads, int num_kv_heads,
+                                         int head_dim, int max_seq_len, float scale, nve_stream_t stream);
 NVE_API int nve_b200_add_inplace(void* dst, const void* src, int n, int dtype, nve_stream_t stream);
 
 /* One matrix of a fused multi-matrix GEMV (all share the activation vector and K). */

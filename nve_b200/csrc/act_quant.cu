@@ -104,6 +104,9 @@ template <int DT, bool VEC> __device__ __forceinline__ float sum_squares(const u
 template <int DT, bool VEC, bool QUANT>
 __global__ void __launch_bounds__(kActThreads) rmsnorm_kernel(const uint16_t* x, const uint16_t* w, uint16_t* out,
                                                               int8_t* xq, float* scales, int n, float eps) {
+    // one CTA per row of n values (a single row in every form but nve_b200_rms_norm_rows)
+    x += static_cast<long long>(blockIdx.x) * n;
+    if (out != nullptr) out += static_cast<long long>(blockIdx.x) * n;
     pdl_wait();
     const float total = sum_squares<DT, VEC>(x, n);
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(n)), eps)));
@@ -248,9 +251,9 @@ static int quantize_q8_impl(const void* x, int8_t* xq, float* scales, int K, cud
 
 template <int DT, bool QUANT>
 static int rmsnorm_impl(const void* x, const void* w, void* out, int8_t* xq, float* scales, int n, float eps,
-                        cudaStream_t st) {
+                        cudaStream_t st, int rows = 1) {
     if (!x || !w) return set_status(NVE_ERR_BAD_POINTER);
-    if (n <= 0) return set_status(NVE_ERR_BAD_SHAPE);
+    if (n <= 0 || rows <= 0 || (QUANT && rows != 1)) return set_status(NVE_ERR_BAD_SHAPE);
     if (QUANT) {
         if (!xq || !scales) return set_status(NVE_ERR_BAD_POINTER);
         if ((n % 32) != 0) return set_status(NVE_ERR_BAD_SHAPE);
@@ -261,7 +264,7 @@ static int rmsnorm_impl(const void* x, const void* w, void* out, int8_t* xq, flo
     const bool vec = (n % 8) == 0 && aligned(x, 16) && aligned(w, 16) && (out == nullptr || aligned(out, 16));
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    launch_cfg(cfg, attr, 1, st);
+    launch_cfg(cfg, attr, rows, st);
     const uint16_t* x16 = static_cast<const uint16_t*>(x);
     const uint16_t* w16 = static_cast<const uint16_t*>(w);
     uint16_t* o16 = static_cast<uint16_t*>(out);
@@ -343,6 +346,15 @@ extern "C" int nve_b200_rms_norm(const void* x, const void* weight, void* out, i
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return NVE_DISPATCH_16(dtype, (rmsnorm_impl<NVE_DT_F16, false>(x, weight, out, nullptr, nullptr, n, eps, st)),
                            (rmsnorm_impl<NVE_DT_BF16, false>(x, weight, out, nullptr, nullptr, n, eps, st)));
+}
+
+/* RMSNorm of every row of x [rows, n] with one weight vector (the reference runs its kernel once per token in prefill,
+ * src/gpu_layer.rs:137): one launch, a CTA per row, each row bit-identical to nve_b200_rms_norm on it. */
+extern "C" int nve_b200_rms_norm_rows(const void* x, const void* weight, void* out, int rows, int n, float eps, int dtype,
+                                      nve_stream_t stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return NVE_DISPATCH_16(dtype, (rmsnorm_impl<NVE_DT_F16, false>(x, weight, out, nullptr, nullptr, n, eps, st, rows)),
+                           (rmsnorm_impl<NVE_DT_BF16, false>(x, weight, out, nullptr, nullptr, n, eps, st, rows)));
 }
 
 extern "C" void nve_rms_norm_f16(const uint16_t* x, const uint16_t* weight, uint16_t* out, int n, float eps,

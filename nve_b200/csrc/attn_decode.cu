@@ -41,6 +41,9 @@ struct AttnParams {
     float* out_scales;        // [nh*hd/32]
     int num_heads, num_kv_heads, kv_stride;
     float scale;
+    // un-fused form only: blockIdx.y selects one of `rows` query rows; row r reads q + r * row_stride, writes
+    // out + r * row_stride and attends to seq_len + r positions (causal attention over a block of new positions)
+    int rows, row_stride;
 };
 
 template <int HD, int QH, bool FUSED>
@@ -66,6 +69,15 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
 
     const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
     const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
+    const uint16_t* q_row = p.q;
+    uint16_t* out_row = p.out;
+    int seq_len_row = p.seq_len;
+    if constexpr (!FUSED) {
+        const int row = blockIdx.y;
+        q_row += static_cast<long long>(row) * p.row_stride;
+        out_row += static_cast<long long>(row) * p.row_stride;
+        seq_len_row += row;
+    }
 
     // Fused form: the cache rows of earlier positions were written by earlier steps, so the first batches of K/V
     // loads can be in flight while the kernel still waits for its predecessor (which produces q and the new k/v,
@@ -95,7 +107,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     // The position scalars are read again now that the producer has finished; q / k / v / the RoPE row are staged
     // with the position read before the wait at the same time (one memory round trip instead of two) and staged again
     // in the rare case that the scalars changed in between.
-    int seq_len = p.d_seq_len != nullptr ? *reinterpret_cast<const volatile int*>(p.d_seq_len) : p.seq_len;
+    int seq_len = p.d_seq_len != nullptr ? *reinterpret_cast<const volatile int*>(p.d_seq_len) : seq_len_row;
     int pos = -1;
     if constexpr (FUSED) pos = *reinterpret_cast<const volatile int*>(p.d_pos);
     if constexpr (FUSED) {
@@ -107,7 +119,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const bool pre_ok = FUSED && pre_seq == seq_len && pre_pos == pos;
     if (!FUSED || pos != pre_pos) {  // uniform over the grid
         if constexpr (FUSED) __syncthreads();
-        attn_stage_q<HD, QH, FUSED>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
+        attn_stage_q<HD, QH, FUSED>(sh, tid, q_row, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
     }
     __syncthreads();
     pdl_launch_dependents();
@@ -152,7 +164,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
         const int h = i / HD, d = i % HD;
         const uint16_t o16 = attn_merge_ranks<HD, QH>(parts, h, d);
         const long long oi = static_cast<long long>(h0 + h) * HD + d;
-        p.out[oi] = o16;
+        out_row[oi] = o16;
         if (p.out_q != nullptr) {
             // i advances by whole warps and HD is a multiple of 32: the 32 lanes of a warp hold one group
             float scale;
@@ -166,7 +178,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
 template <int HD, int QH, bool FUSED> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
     const int clusters = p.num_heads / QH;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(clusters * kAdCluster);
+    cfg.gridDim = dim3(clusters * kAdCluster, FUSED ? 1 : max(1, p.rows));
     cfg.blockDim = dim3(kAdThreads);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -244,6 +256,33 @@ extern "C" int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_n
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.kv_stride = max_seq_len; p.scale = scale;
     cudaError_t e = cudaSuccess;
     if (!attn_decode_dispatch<true>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
+    count_launch();
+    return set_cuda_status(e);
+}
+
+/* Causal attention of a block of S new positions against the cache (which already holds them): row r of q
+ * [S, num_heads * head_dim] attends to positions [0, start_pos + r]; out has q's layout.  One launch: the decode
+ * kernel with the row as second grid dimension, so every row equals a nve_flash_decode_f16 call of that length. */
+extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out,
+                                            int rows, int start_pos, int num_heads, int num_kv_heads, int head_dim,
+                                            int max_seq_len, float scale, nve_stream_t stream) {
+    if (!q || !k_cache || !v_cache || !out) return set_status(NVE_ERR_BAD_POINTER);
+    if (rows <= 0 || rows > 65535 || start_pos < 0 || num_heads <= 0 || num_kv_heads <= 0 || (num_heads % num_kv_heads) != 0 ||
+        max_seq_len <= 0 || start_pos + rows > max_seq_len)
+        return set_status(NVE_ERR_BAD_SHAPE);
+    if (head_dim != 64 && head_dim != 128) return set_status(NVE_ERR_BAD_SHAPE);
+    if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(q, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    AttnParams p = {};
+    p.q = q;
+    p.k_cache = const_cast<uint16_t*>(k_cache);
+    p.v_cache = const_cast<uint16_t*>(v_cache);
+    p.seq_len = start_pos + 1;
+    p.out = out;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.kv_stride = max_seq_len; p.scale = scale;
+    p.rows = rows;
+    p.row_stride = num_heads * head_dim;
+    cudaError_t e = cudaSuccess;
+    if (!attn_decode_dispatch<false>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
     count_launch();
     return set_cuda_status(e);
 }

@@ -325,6 +325,34 @@ extern "C" void nve_rope_f16_decode_dyn(uint16_t* q, uint16_t* k, const uint16_t
                 static_cast<cudaStream_t>(stream));
 }
 
+// cache[kvh, start_pos + s, :] = new[s, kvh, :] for a block of S new positions (K and V).
+__global__ void kv_write_rows_kernel(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new, uint16_t* v_cache, int rows,
+                                     int start_pos, int nkv, int hd, int max_seq) {
+    pdl_wait();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long n = static_cast<long long>(rows) * nkv * hd;
+    if (i >= n) return;
+    const int d = static_cast<int>(i % hd);
+    const int h = static_cast<int>((i / hd) % nkv);
+    const int s = static_cast<int>(i / (static_cast<long long>(hd) * nkv));
+    const long long dst = (static_cast<long long>(h) * max_seq + start_pos + s) * hd + d;
+    k_cache[dst] = k_new[i];
+    v_cache[dst] = v_new[i];
+}
+
+extern "C" int nve_b200_kv_cache_write_rows(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new, uint16_t* v_cache,
+                                            int rows, int start_pos, int num_kv_heads, int head_dim, int max_seq_len,
+                                            nve_stream_t stream) {
+    if (!k_new || !k_cache || !v_new || !v_cache) return set_status(NVE_ERR_BAD_POINTER);
+    if (rows <= 0 || start_pos < 0 || num_kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0 || start_pos + rows > max_seq_len)
+        return set_status(NVE_ERR_BAD_SHAPE);
+    const long long n = static_cast<long long>(rows) * num_kv_heads * head_dim;
+    kv_write_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        k_new, k_cache, v_new, v_cache, rows, start_pos, num_kv_heads, head_dim, max_seq_len);
+    count_launch();
+    return check_launch();
+}
+
 extern "C" void nve_kv_cache_write_f16(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new, uint16_t* v_cache,
                                        const int* d_pos, int num_kv_heads, int head_dim, int max_seq_len,
                                        nve_stream_t stream) {

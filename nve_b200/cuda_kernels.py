@@ -119,6 +119,38 @@ def fused_rope_prefill(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, seq_len: 
     _ffi.check_last("nve_rope_f16_prefill")
 
 
+def rms_norm_rows(x: Tensor, weight: Tensor, eps: float, out: Optional[Tensor] = None) -> Tensor:
+    """RMSNorm of every row of x [rows, n] in one launch (each row as rms_norm computes it)."""
+    if x.dim() != 2:
+        raise ValueError("x must be [rows, n]")
+    out = torch.empty_like(x) if out is None else out
+    _ffi.check("nve_b200_rms_norm_rows",
+               _lib().nve_b200_rms_norm_rows(_ptr(x, (torch.float16, torch.bfloat16), "x"), _ptr(weight, x.dtype),
+                                             _ptr(out, x.dtype), x.shape[0], x.shape[1], float(eps), _dt(x), stream()))
+    return out
+
+
+def kv_cache_write_rows(k_new: Tensor, k_cache: Tensor, v_new: Tensor, v_cache: Tensor, start_pos: int, num_kv_heads: int,
+                        head_dim: int, max_seq_len: int) -> None:
+    """cache[kvh, start_pos + s, :] = new[s, kvh, :] for the rows of k_new / v_new [S, nkv, hd]."""
+    rows = k_new.shape[0]
+    _ffi.check("nve_b200_kv_cache_write_rows",
+               _lib().nve_b200_kv_cache_write_rows(_ptr(k_new, _F16, "k_new"), _ptr(k_cache, _F16), _ptr(v_new, _F16, "v_new"),
+                                                   _ptr(v_cache, _F16), rows, start_pos, num_kv_heads, head_dim, max_seq_len,
+                                                   stream()))
+
+
+def attn_prefill_causal(q: Tensor, k_cache: Tensor, v_cache: Tensor, start_pos: int, num_heads: int, num_kv_heads: int,
+                        head_dim: int, max_seq_len: int, scale: float, out: Optional[Tensor] = None) -> Tensor:
+    """Row r of q [S, nh*hd] attends to cache positions [0, start_pos + r]; returns [S, nh*hd]."""
+    out = torch.empty_like(q) if out is None else out
+    _ffi.check("nve_b200_attn_prefill_causal",
+               _lib().nve_b200_attn_prefill_causal(_ptr(q, _F16, "q"), _ptr(k_cache, _F16), _ptr(v_cache, _F16),
+                                                   _ptr(out, _F16, "out"), q.shape[0], start_pos, num_heads, num_kv_heads,
+                                                   head_dim, max_seq_len, float(scale), stream()))
+    return out
+
+
 def fused_matvec(x: Tensor, w: Tensor, n: int, k: int) -> Tensor:
     """src/cuda_kernels.rs:441-457: dense f16 GEMV, returns [1, n]."""
     out = torch.empty((1, n), dtype=_F16, device=x.device)

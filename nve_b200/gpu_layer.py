@@ -64,6 +64,24 @@ def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None) -> Tensor:
     return out
 
 
+def matmul_x_multi(x: Tensor, ws: Sequence[GpuW4]) -> List[Tensor]:
+    """matmul_x for several projections of the same x (q/k/v, gate/up) in one GEMM launch per 64-row slice: their
+    tiles share the grid, so narrow projections do not run as few-CTA kernels.  M == 1 and weights with an
+    activation multiplier go through matmul_x one by one."""
+    m, k = x.shape
+    if m == 1 or any(w.awq_scales is not None for w in ws):
+        return [matmul_x(x, w) for w in ws]
+    outs = [torch.empty((m, w.n), dtype=x.dtype, device=x.device) for w in ws]
+    step = 64
+    ns = [w.n for w in ws]
+    scratch = torch.empty(max(16, ck.gemm_w4a16_multi_scratch_bytes(min(m, step), ns, k)), dtype=torch.uint8, device=x.device)
+    trip = [w.triple() for w in ws]
+    for r0 in range(0, m, step):
+        rows = min(step, m - r0)
+        ck.gemm_w4a16_multi(x[r0:r0 + rows], trip, k, outs=[o[r0:r0 + rows] for o in outs], scratch=scratch)
+    return outs
+
+
 @dataclass
 class GpuLayerWeights:
     """The W4 subset of src/gpu_layer.rs GpuLayerWeights (Llama-style block, no biases)."""
@@ -369,3 +387,38 @@ def gpu_layer_forward_decode(hidden: Tensor, layer_idx: int, state: GpuInference
     h = gpu_attn_decode(normed, w, state, layer_idx, d_pos, d_seqlen, use_w4a8, residual=hidden)
     normed2 = ck.fused_rms_norm(h, w.post_attn_norm, eps)  # :1074-1080
     return gpu_ffn(normed2, w, state, use_w4a8, residual=h)
+
+
+
+def gpu_layer_forward_prefill(hidden: Tensor, layer_idx: int, state: GpuInferenceState, start_pos: int) -> Tensor:
+    """src/gpu_layer.rs:1086-1160 with gpu_attn_prefill (:777-890) and the batch > 1 branch of gpu_ffn (:977-996) for
+    W4 weights: all S prompt positions of one sequence through one layer.  hidden [S, hidden] f16 -> same shape; the
+    K/V cache of the layer receives positions start_pos .. start_pos + S - 1.
+
+    The reference dequantises every projection to f16 and calls a dense GEMM, runs RMSNorm once per token and an
+    unfused masked attention; here the projections are the tcgen05 GEMM on the packed weights (q/k/v and gate/up one
+    launch each per 64-row slice), RMSNorm / KV write / causal attention are one launch each.  Like the reference's
+    prefill, every layer runs on 16-bit activations (the int8 route is a batch-1 path, :1017-1025)."""
+    if hidden.dim() != 2:
+        raise ValueError("hidden must be [S, hidden]")
+    w = state.layer_weights[layer_idx]
+    nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+    S = hidden.shape[0]
+    max_seq = state.kv_cache.max_seq
+    if start_pos < 0 or start_pos + S > max_seq:
+        raise ValueError("the block does not fit the K/V cache")
+    eps, scale = state.norm_eps, float(hd) ** -0.5
+    normed = ck.rms_norm_rows(hidden, w.input_norm, eps)
+    q, k, v = matmul_x_multi(normed, [w.q_proj, w.k_proj, w.v_proj])
+    ck.fused_rope_prefill(q, k, state.rope_cos, state.rope_sin, S, nh, nkv, hd, start_pos)
+    kc, vc = state.kv_cache.k[layer_idx], state.kv_cache.v[layer_idx]
+    ck.kv_cache_write_rows(k.view(S, nkv, hd), kc, v.view(S, nkv, hd), vc, start_pos, nkv, hd, max_seq)
+    attn = ck.attn_prefill_causal(q, kc, vc, start_pos, nh, nkv, hd, max_seq, scale)
+    h1 = matmul_x(attn, w.o_proj)
+    ck.add_inplace_any(h1, hidden)
+    normed2 = ck.rms_norm_rows(h1, w.post_attn_norm, eps)
+    gate, up = matmul_x_multi(normed2, [w.gate_proj, w.up_proj])
+    ck.silu_mul_inplace(gate, up)
+    out = matmul_x(gate, w.down_proj)
+    ck.add_inplace_any(out, h1)
+    return out

@@ -491,3 +491,85 @@ def test_five_launch_graph_equals_six_launch_graph(cuda, orc):
     for other in outs[1:]:
         for a, b in zip(outs[0], other):
             assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ prefill: a block of positions through one layer
+def test_rms_norm_rows_and_kv_rows_write(cuda, orc):
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    S, n = 7, 2048
+    x = dev(orc.to_act16(orc.fill_normal(S * n, 811, 1) * 2.0), torch.float16).view(S, n)
+    w = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(n, 811, 2)), torch.float16)
+    got = ck.rms_norm_rows(x, w, 1e-5)
+    for r in range(S):
+        assert torch.equal(got[r], ck.rms_norm(x[r].contiguous(), w, 1e-5))
+    nkv, hd, max_seq, start = 4, 64, 32, 9
+    k_new = dev(orc.to_act16(orc.fill_normal(S * nkv * hd, 811, 3)), torch.float16).view(S, nkv, hd)
+    v_new = dev(orc.to_act16(orc.fill_normal(S * nkv * hd, 811, 4)), torch.float16).view(S, nkv, hd)
+    kc = torch.zeros((nkv, max_seq, hd), dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    ck.kv_cache_write_rows(k_new, kc, v_new, vc, start, nkv, hd, max_seq)
+    want_k, want_v = torch.zeros_like(kc), torch.zeros_like(vc)
+    want_k[:, start:start + S] = k_new.transpose(0, 1)
+    want_v[:, start:start + S] = v_new.transpose(0, 1)
+    assert torch.equal(kc, want_k) and torch.equal(vc, want_v)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 8, 128), (8, 8, 64), (12, 4, 64)])
+def test_attn_prefill_causal_rows_equal_decode_calls(cuda, orc, nh, nkv, hd):
+    """Every row of the one-launch causal attention equals a flash-decode call of that row's length, bit for bit."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    S, start, max_seq = 9, 37, 64
+    q = dev(orc.to_act16(orc.fill_normal(S * nh * hd, 821, 1)), torch.float16).view(S, nh * hd)
+    kc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 821, 2)), torch.float16).view(nkv, max_seq, hd)
+    vc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 821, 3)), torch.float16).view(nkv, max_seq, hd)
+    got = ck.attn_prefill_causal(q, kc, vc, start, nh, nkv, hd, max_seq, hd ** -0.5)
+    d_len = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for r in range(S):
+        d_len.fill_(start + r + 1)
+        want = torch.empty((nh * hd,), dtype=torch.float16, device="cuda")
+        ck.flash_decode_dyn_into(q[r].contiguous(), kc, vc, want, nh, nkv, d_len.data_ptr(), hd, hd ** -0.5, max_seq)
+        torch.cuda.synchronize()
+        assert torch.equal(got[r], want), f"row {r}"
+
+
+def test_prefill_layers_match_sequential_decode(cuda, orc):
+    """gpu_layer_forward_prefill on a block of S positions against S sequential decode steps through the same two
+    layers (16-bit route on every layer, as in the reference's prefill): hidden states within the tolerance that
+    separates the f16-dequantised tensor-core GEMM from the integer GEMV, K/V caches likewise (the reference tests
+    prefill-vs-sequential agreement in tests/e2e.rs:440-479)."""
+    from nve_b200.gpu_layer import gpu_layer_forward_decode, gpu_layer_forward_prefill
+
+    torch = cuda
+    hidden, ffn, nh, nkv, hd, layers, max_seq, S, start = 1024, 2816, 16, 4, 64, 2, 32, 6, 3
+    st_d = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 831, True)
+    st_p = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 831, True)
+    st_d.routing.no_w4a8 = True
+    # both caches start with the same `start` earlier positions
+    for li in range(layers):
+        for t, sid in ((st_d.kv_cache.k, 1), (st_d.kv_cache.v, 2)):
+            t[li][:, :start] = dev(orc.to_act16(orc.fill_normal(nkv * start * hd, 832, 10 * li + sid)), torch.float16).view(
+                nkv, start, hd)
+        st_p.kv_cache.k[li].copy_(st_d.kv_cache.k[li])
+        st_p.kv_cache.v[li].copy_(st_d.kv_cache.v[li])
+    x = dev(orc.to_act16(orc.fill_normal(S * hidden, 833, 1)), torch.float16).view(S, hidden)
+    # sequential decode
+    seq_out = []
+    for s in range(S):
+        h = x[s:s + 1].contiguous()
+        for li in range(layers):
+            h = gpu_layer_forward_decode(h, li, st_d, start + s, False, 1.0)
+        seq_out.append(h)
+    seq_out = torch.cat(seq_out)
+    # block prefill
+    hp = x
+    for li in range(layers):
+        hp = gpu_layer_forward_prefill(hp, li, st_p, start)
+    torch.cuda.synchronize()
+    assert rel_rms_err(hp.float().cpu().numpy(), seq_out.float().cpu().numpy()) < 5e-3
+    for li in range(layers):
+        for a, b in ((st_p.kv_cache.k[li], st_d.kv_cache.k[li]), (st_p.kv_cache.v[li], st_d.kv_cache.v[li])):
+            assert rel_rms_err(a[:, :start + S].float().cpu().numpy(), b[:, :start + S].float().cpu().numpy()) < 5e-3
