@@ -177,6 +177,9 @@ def _main() -> None:
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
     ap.add_argument("--batch", type=int, default=1, help="> 1: the tcgen05 batched W4A16 GEMM with this many rows of X")
+    ap.add_argument("--fused-silu", action="store_true",
+                    help="--group gateup: the decode step's own launch (RMSNorm prologue, SiLU*up and the conversion for "
+                         "the down projection in the epilogue)")
     ap.add_argument("--persistent", action="store_true",
                     help="run whole decode steps of a --layers deep stack through the one-kernel form instead of one group")
     ap.add_argument("--context", type=int, default=1024)
@@ -242,6 +245,11 @@ def _main() -> None:
     outs = [torch.empty((1, n), dtype=torch.float16, device="cuda") for n in ns]
     nbytes = sum(w4_bytes(n, k) for n in ns)
 
+    norm_w = torch.ones(k, dtype=torch.float16, device="cuda")
+    fq = torch.zeros(ns[0], dtype=torch.int8, device="cuda")
+    flo = torch.zeros(ns[0], dtype=torch.uint8, device="cuda")
+    fs = torch.zeros(max(1, ns[0] // 32), dtype=torch.float32, device="cuda")
+    fcnt = torch.zeros(max(1, ns[0] // 32), dtype=torch.int32, device="cuda")
     xb = yb = scratch = None
     if a.batch > 1:
         xb = ck.fill_normal(a.batch * k, 1, 998, dtype=torch.float16).view(a.batch, k)
@@ -255,6 +263,12 @@ def _main() -> None:
                 ck.gemm_w4a16_multi(xb, [w.triple() for w in ws[li]], k, outs=yb, scratch=scratch)
                 continue
             trip = [w.triple() for w in ws[li]]
+            if a.fused_silu and a.group == "gateup":
+                q = ({"xq": fq, "xs": fs, "counters": fcnt} if a.route == "w4a8" else
+                     {"xlo": flo, "xhi": fq, "xs": fs, "counters": fcnt})
+                ck.rmsnorm_gateup_silu(x.view(1, -1), norm_w, 1e-5, None, trip[0], trip[1], k, a.route == "w4a8", mid=outs[0],
+                                       quant=q)
+                continue
             if a.route == "w4a8":
                 ck.matvec_w4a8_multi(xq, xs, trip, k, outs=outs)
             else:
