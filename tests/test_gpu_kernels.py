@@ -107,7 +107,7 @@ def test_w4a16_matvec(cuda, orc, N, K, bf):
     y32 = ck.matvec_w4a16_multi(dx, None, [(dn, ds, N)], K, out_dtype=torch.float32)[0].cpu().numpy().reshape(-1)
     exp32 = orc.w4a16_matvec_b200(x16, nib, sc, bf16=bf)
     assert np.array_equal(y32.view(np.uint32), exp32.view(np.uint32))
-    # the judged oracle: the reference CPU path on the same 16-bit-rounded activations
+    # the oracle that decides parity: the reference CPU path on the same 16-bit-rounded activations
     xf = orc.from_act16(x16, bf)
     cpu = orc.q4_matvec(orc.quantize_q4(W), xf, order="scalar")
     assert rel_rms_err(y32, cpu) < 1e-3
