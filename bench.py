@@ -465,6 +465,45 @@ def prefill_entry(torch, ck, state, shape, S: int = 256):
             "gemm_error": ck.gemm_error()}
 
 
+def batched_decode_entries(torch, ck, state, shape, batches=(8, 16, 32, 64)):
+    """One decode step of B independent sequences (context CONTEXT each) through all layers with
+    gpu_layer_forward_decode_batch: tcgen05 GEMM projections, one fused RoPE + K/V write + attention launch for all
+    sequences, RMSNorm over rows; recorded once into the library's graph (pre-allocated scratch) and replayed.  Tokens per
+    second are summed over the sequences.  The reference has no batched decode (its batch > 1 is prefill only)."""
+    from nve_b200.gpu_layer import BatchedDecodeScratch, BatchedKvCache, gpu_layer_forward_decode_batch
+
+    layers = len(state.layer_weights)
+    out = {}
+    for b in batches:
+        kv = BatchedKvCache.zeros(layers, b, shape.num_kv_heads, CONTEXT, shape.head_dim)
+        for li in range(layers):
+            n = kv.k[li].numel()
+            ck.fill_normal(n, SEED, 9600 + 2 * li, dtype=torch.float16, out=kv.k[li].view(-1))
+            ck.fill_normal(n, SEED, 9601 + 2 * li, dtype=torch.float16, out=kv.v[li].view(-1))
+        x = ck.fill_normal(b * shape.hidden, SEED, 9700, dtype=torch.float16).view(b, shape.hidden)
+        d_pos = torch.full((b,), CONTEXT - 1, dtype=torch.int32, device="cuda")
+        d_len = torch.full((b,), CONTEXT, dtype=torch.int32, device="cuda")
+        scratch = BatchedDecodeScratch.make(state, b, shape.hidden, shape.ffn)
+        last = {}
+
+        def rec(_a, _b):
+            h = x
+            for li in range(layers):
+                h = gpu_layer_forward_decode_batch(h, li, state, kv, d_pos, d_len, scratch)
+            last["h"] = h
+
+        us, launches = time_sequence(torch, rec, reps=5)
+        ms = us * 1e-3
+        finite = bool(torch.isfinite(last["h"].float()).all())
+        kv_bytes = 2 * b * shape.num_kv_heads * CONTEXT * shape.head_dim * 2 * layers
+        out[str(b)] = {"ms_per_step": round(ms, 3), "tok_s": round(b / (ms * 1e-3), 1), "launches_per_step": launches,
+                       "output_finite": finite, "kv_bytes_read_per_step": kv_bytes}
+        del kv, scratch
+        torch.cuda.empty_cache()
+    out["gemm_error"] = ck.gemm_error()
+    return out
+
+
 def lm_head_entries(torch, ck, state, shape, importance, h0, pos):
     """The same step with the final RMSNorm + lm_head on the device (the reference leaves them on the host): W4
     lm_head (328 MB per token) and dense f16 lm_head (1051 MB per token)."""
@@ -692,6 +731,7 @@ def run_ours(args) -> None:
         pers.destroy()
         extras["lm_head"] = lm_head_entries(torch, ck, state, shape, importance, h0, pos)
         extras["prefill"] = prefill_entry(torch, ck, state, shape)
+        extras["batched_decode"] = batched_decode_entries(torch, ck, state, shape)
         table, gerr = gemm_batch_table(torch, ck, state, shape, peak)
         extras["gemm_batch"] = {"rows": table, "error_word": gerr,
                                 "tensor_pipe_pct": {"value": 6.4, "source": "sm__pipe_tensor_cycles_active of the gate/up "

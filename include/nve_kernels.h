@@ -323,6 +323,16 @@ NVE_API int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_new,
                                        const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,
                                        int8_t* out_q, float* out_scales, int num_heads, int num_kv_heads,
                                        int head_dim, int max_seq_len, float scale, nve_stream_t stream);
+/* The same launch for `batch` independent sequences (batched decode; the reference has none): row b of q
+ * [batch, nh*hd] and of k_new / v_new [batch, nkv*hd] belongs to sequence b, whose caches are k_cache / v_cache +
+ * b * nkv * max_seq_len * hd, whose position is d_pos[b] and whose valid length is d_seq_len[b] (device arrays).
+ * Row b of out [batch, nh*hd] and the cache row written are bit-identical to a single-sequence call.  q / k_new /
+ * v_new and the caches 16-byte aligned. */
+NVE_API int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
+                                             uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
+                                             const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len,
+                                             uint16_t* out, int batch, int num_heads, int num_kv_heads, int head_dim,
+                                             int max_seq_len, float scale, nve_stream_t stream);
 
 /* Exact per-block integer dot products I[N, K/32] (int32) of the W4A8 GEMV, for bit-level checks. */
 NVE_API int nve_b200_w4a8_idot(const int8_t* xq, const uint8_t* nibbles, int32_t* I, int N, int K, nve_stream_t stream);

@@ -142,6 +142,7 @@ SIGNATURES = {
     "nve_b200_quantize_matvec_w4a8_multi": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _I, _P]),
     "nve_b200_quantize_matvec_w4a8_allreduce": (_I, [_P, _I, _P, C.POINTER(W4Matrix), _I, _P]),
     "nve_b200_attn_decode_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
+    "nve_b200_attn_decode_fused_batch": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "nve_b200_w4a8_idot": (_I, [_P, _P, _P, _I, _I, _P]),
     "nve_b200_dequant_w4a16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "nve_b200_q4_quantize": (_I, [_P, _P, _P, _P, _I, _I, _P]),

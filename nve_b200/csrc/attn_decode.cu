@@ -44,10 +44,26 @@ struct AttnParams {
     // un-fused form only: blockIdx.y selects one of `rows` query rows; row r reads q + r * row_stride, writes
     // out + r * row_stride and attends to seq_len + r positions (causal attention over a block of new positions)
     int rows, row_stride;
+    // batched fused form: `rows` independent sequences; elements between consecutive K (or V) caches
+    long long cache_stride;
 };
 
-template <int HD, int QH, bool FUSED>
-__global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParams p) {
+// BATCH (fused form only): blockIdx.y selects one of several independent sequences -- row b of q / k_new / v_new / out,
+// the b-th K/V cache and the b-th position and length words.
+template <int HD, int QH, bool FUSED, bool BATCH = false>
+__global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParams pin) {
+    AttnParams p = pin;
+    if constexpr (BATCH) {
+        const long long b = blockIdx.y;
+        p.q += b * (static_cast<long long>(p.num_heads) * HD);
+        p.out += b * (static_cast<long long>(p.num_heads) * HD);
+        p.k_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
+        p.v_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
+        p.k_cache += b * p.cache_stride;
+        p.v_cache += b * p.cache_stride;
+        p.d_pos += b;
+        p.d_seq_len += b;
+    }
     constexpr int DC = HD / 8;            // lanes per row
     constexpr int PL = kAdThreads / DC;   // position lanes
     cg::cluster_group cluster = cg::this_cluster();
@@ -72,7 +88,7 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     const uint16_t* q_row = p.q;
     uint16_t* out_row = p.out;
     int seq_len_row = p.seq_len;
-    if constexpr (!FUSED) {
+    if constexpr (!FUSED && !BATCH) {
         const int row = blockIdx.y;
         q_row += static_cast<long long>(row) * p.row_stride;
         out_row += static_cast<long long>(row) * p.row_stride;
@@ -175,10 +191,10 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     }
 }
 
-template <int HD, int QH, bool FUSED> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
+template <int HD, int QH, bool FUSED, bool BATCH = false> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
     const int clusters = p.num_heads / QH;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(clusters * kAdCluster, FUSED ? 1 : max(1, p.rows));
+    cfg.gridDim = dim3(clusters * kAdCluster, (FUSED && !BATCH) ? 1 : max(1, p.rows));
     cfg.blockDim = dim3(kAdThreads);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -193,20 +209,21 @@ template <int HD, int QH, bool FUSED> static cudaError_t launch_ad(const AttnPar
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs = 2;
     }
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, QH, FUSED>, p);
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, QH, FUSED, BATCH>, p);
 }
 
 // Returns false when the shape is not covered (the caller then uses the generic kernel).
-template <bool FUSED> static bool attn_decode_dispatch(const AttnParams& p, int hd, cudaStream_t st, cudaError_t& err) {
+template <bool FUSED, bool BATCH = false>
+static bool attn_decode_dispatch(const AttnParams& p, int hd, cudaStream_t st, cudaError_t& err) {
     const int groups = p.num_heads / p.num_kv_heads;
     if (!aligned(p.k_cache, 16) || !aligned(p.v_cache, 16)) return false;
     const int qh = (groups % 2 == 0) ? 2 : 1;
     if (hd == 128) {
-        err = qh == 2 ? launch_ad<128, 2, FUSED>(p, st) : launch_ad<128, 1, FUSED>(p, st);
+        err = qh == 2 ? launch_ad<128, 2, FUSED, BATCH>(p, st) : launch_ad<128, 1, FUSED, BATCH>(p, st);
         return true;
     }
     if (hd == 64) {
-        err = qh == 2 ? launch_ad<64, 2, FUSED>(p, st) : launch_ad<64, 1, FUSED>(p, st);
+        err = qh == 2 ? launch_ad<64, 2, FUSED, BATCH>(p, st) : launch_ad<64, 1, FUSED, BATCH>(p, st);
         return true;
     }
     return false;
@@ -283,6 +300,35 @@ extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k
     p.row_stride = num_heads * head_dim;
     cudaError_t e = cudaSuccess;
     if (!attn_decode_dispatch<false>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
+    count_launch();
+    return set_cuda_status(e);
+}
+
+/* nve_b200_attn_decode_fused for `batch` independent sequences in one launch: row b of q [batch, nh*hd] and of
+ * k_new / v_new [batch, nkv*hd] belongs to sequence b, whose caches are k_cache / v_cache + b * nkv * max_seq_len * hd,
+ * whose position is d_pos[b] and whose valid length is d_seq_len[b].  Row b of the result (and the cache row written)
+ * is bit-identical to a single-sequence call. */
+extern "C" int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
+                                                uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
+                                                const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,
+                                                int batch, int num_heads, int num_kv_heads, int head_dim, int max_seq_len,
+                                                float scale, nve_stream_t stream) {
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !cos_tab || !sin_tab || !d_pos || !d_seq_len || !out)
+        return set_status(NVE_ERR_BAD_POINTER);
+    if (batch <= 0 || batch > 65535 || num_heads <= 0 || num_kv_heads <= 0 || (num_heads % num_kv_heads) != 0 || max_seq_len <= 0)
+        return set_status(NVE_ERR_BAD_SHAPE);
+    if (head_dim != 64 && head_dim != 128) return set_status(NVE_ERR_BAD_SHAPE);
+    if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16))
+        return set_status(NVE_ERR_BAD_ALIGNMENT);
+    AttnParams p = {};
+    p.q = q; p.k_new = k_new; p.v_new = v_new; p.k_cache = k_cache; p.v_cache = v_cache;
+    p.cos_tab = cos_tab; p.sin_tab = sin_tab; p.d_pos = d_pos; p.d_seq_len = d_seq_len; p.seq_len = 0;
+    p.out = out;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.kv_stride = max_seq_len; p.scale = scale;
+    p.rows = batch;
+    p.cache_stride = static_cast<long long>(num_kv_heads) * max_seq_len * head_dim;
+    cudaError_t e = cudaSuccess;
+    if (!attn_decode_dispatch<true, true>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
     count_launch();
     return set_cuda_status(e);
 }

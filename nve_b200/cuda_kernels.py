@@ -583,6 +583,24 @@ def attn_decode_fused(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, 
                                                  num_kv_heads, head_dim, max_seq_len, float(scale), stream()))
 
 
+def attn_decode_fused_batch(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, cos_tab: Tensor,
+                            sin_tab: Tensor, d_pos: Tensor, d_seq_len: Tensor, num_heads: int, num_kv_heads: int,
+                            head_dim: int, max_seq_len: int, scale: float, out: Optional[Tensor] = None) -> Tensor:
+    """attn_decode_fused for B independent sequences in one launch: q [B, nh*hd], k_new / v_new [B, nkv*hd], caches
+    [B, nkv, max_seq, hd], d_pos / d_seq_len int32 [B] on the device; returns [B, nh*hd]."""
+    b = q.shape[0]
+    if k_cache.shape[0] != b or d_pos.numel() != b or d_seq_len.numel() != b:
+        raise ValueError("one cache, position and length per row of q")
+    out = torch.empty_like(q) if out is None else out
+    _ffi.check("nve_b200_attn_decode_fused_batch",
+               _lib().nve_b200_attn_decode_fused_batch(
+                   _ptr(q, _F16, "q"), _ptr(k_new, _F16, "k_new"), _ptr(v_new, _F16, "v_new"), _ptr(k_cache, _F16),
+                   _ptr(v_cache, _F16), _ptr(cos_tab, _F16), _ptr(sin_tab, _F16), _ptr(d_pos, torch.int32, "d_pos"),
+                   _ptr(d_seq_len, torch.int32, "d_seq_len"), _ptr(out, _F16, "out"), b, num_heads, num_kv_heads, head_dim,
+                   max_seq_len, float(scale), stream()))
+    return out
+
+
 # --------------------------------------------------------------------------- whole step in one kernel
 def decode_step_workspace_bytes(model: "_ffi.DecodeModel") -> int:
     n = int(_lib().nve_b200_decode_step_workspace_bytes(C.byref(model)))

@@ -39,7 +39,7 @@ class GpuW4:
         return (self.nibbles, self.scales, self.n)
 
 
-def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None) -> Tensor:
+def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None, out: Optional[Tensor] = None) -> Tensor:
     """`GpuWeight::matmul_x` for W4 weights (src/gpu_layer.rs:220-239): x [M, K] -> [M, N].
 
     The reference sends M == 1 to `fused_matvec_w4a16` and M > 1 through `dequant_w4a16` + a dense matmul (the whole
@@ -49,11 +49,13 @@ def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None) -> Tensor:
     if x.dim() != 2 or x.shape[1] != w.k:
         raise ValueError(f"x must be [M, {w.k}]")
     m = x.shape[0]
-    if m == 1:
+    if m == 1 and out is None:
         return ck.fused_matvec_w4a16(x, w.nibbles, w.scales, w.awq_scales, w.n, w.k)
+    if m == 1:
+        return ck.matvec_w4a16_multi(x, w.awq_scales, [w.triple()], w.k, outs=[out])[0]
     if w.awq_scales is not None:
         x = (x.float() * w.awq_scales.view(1, -1)).to(x.dtype)
-    out = torch.empty((m, w.n), dtype=x.dtype, device=x.device)
+    out = torch.empty((m, w.n), dtype=x.dtype, device=x.device) if out is None else out
     step = 64
     if scratch is None:
         nbytes = ck.gemm_w4a16_scratch_bytes(min(m, step), w.n, w.k)
@@ -64,17 +66,20 @@ def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None) -> Tensor:
     return out
 
 
-def matmul_x_multi(x: Tensor, ws: Sequence[GpuW4]) -> List[Tensor]:
+def matmul_x_multi(x: Tensor, ws: Sequence[GpuW4], scratch: Optional[Tensor] = None,
+                   outs: Optional[Sequence[Tensor]] = None) -> List[Tensor]:
     """matmul_x for several projections of the same x (q/k/v, gate/up) in one GEMM launch per 64-row slice: their
     tiles share the grid, so narrow projections do not run as few-CTA kernels.  M == 1 and weights with an
     activation multiplier go through matmul_x one by one."""
     m, k = x.shape
     if m == 1 or any(w.awq_scales is not None for w in ws):
-        return [matmul_x(x, w) for w in ws]
-    outs = [torch.empty((m, w.n), dtype=x.dtype, device=x.device) for w in ws]
+        return [matmul_x(x, w, scratch, None if outs is None else outs[i]) for i, w in enumerate(ws)]
+    outs = [torch.empty((m, w.n), dtype=x.dtype, device=x.device) for w in ws] if outs is None else list(outs)
     step = 64
     ns = [w.n for w in ws]
-    scratch = torch.empty(max(16, ck.gemm_w4a16_multi_scratch_bytes(min(m, step), ns, k)), dtype=torch.uint8, device=x.device)
+    if scratch is None:
+        scratch = torch.empty(max(16, ck.gemm_w4a16_multi_scratch_bytes(min(m, step), ns, k)), dtype=torch.uint8,
+                              device=x.device)
     trip = [w.triple() for w in ws]
     for r0 in range(0, m, step):
         rows = min(step, m - r0)
@@ -420,5 +425,80 @@ def gpu_layer_forward_prefill(hidden: Tensor, layer_idx: int, state: GpuInferenc
     gate, up = matmul_x_multi(normed2, [w.gate_proj, w.up_proj])
     ck.silu_mul_inplace(gate, up)
     out = matmul_x(gate, w.down_proj)
+    ck.add_inplace_any(out, h1)
+    return out
+
+
+@dataclass
+class BatchedKvCache:
+    """Static K/V caches of B independent sequences: per layer k / v [B, nkv, max_seq, hd] f16 (the reference has no
+    batched decode; this is the single-sequence layout of src/decode_graph.rs:183-184 with a batch dimension in front)."""
+
+    k: List[Tensor]
+    v: List[Tensor]
+    batch: int
+    max_seq: int
+
+    @staticmethod
+    def zeros(num_layers: int, batch: int, num_kv_heads: int, max_seq: int, head_dim: int, device="cuda") -> "BatchedKvCache":
+        mk = lambda: [torch.zeros((batch, num_kv_heads, max_seq, head_dim), dtype=torch.float16, device=device)
+                      for _ in range(num_layers)]
+        return BatchedKvCache(mk(), mk(), batch, max_seq)
+
+
+@dataclass
+class BatchedDecodeScratch:
+    """Every intermediate of gpu_layer_forward_decode_batch for a fixed batch, so that a step allocates nothing (and can
+    be recorded into a CUDA graph)."""
+
+    normed: Tensor
+    q: Tensor
+    k: Tensor
+    v: Tensor
+    attn: Tensor
+    h1: Tensor
+    gate: Tensor
+    up: Tensor
+    out: List[Tensor]   # two output rows buffers, alternated between layers (a layer reads the previous layer's output)
+    gemm: Tensor        # workspace of the batched GEMM (largest of the four projection groups)
+
+    @staticmethod
+    def make(state: GpuInferenceState, batch: int, hidden: int, ffn: int, device="cuda") -> "BatchedDecodeScratch":
+        nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+        f16 = torch.float16
+        z = lambda n: torch.zeros((batch, n), dtype=f16, device=device)
+        groups = [([nh * hd, nkv * hd, nkv * hd], hidden), ([hidden], nh * hd), ([ffn, ffn], hidden), ([hidden], ffn)]
+        nbytes = max(ck.gemm_w4a16_multi_scratch_bytes(min(batch, 64), ns, k) for ns, k in groups) if batch > 1 else 0
+        return BatchedDecodeScratch(z(hidden), z(nh * hd), z(nkv * hd), z(nkv * hd), z(nh * hd), z(hidden), z(ffn), z(ffn),
+                                    [z(hidden), z(hidden)], torch.empty(max(16, nbytes), dtype=torch.uint8, device=device))
+
+
+def gpu_layer_forward_decode_batch(hidden: Tensor, layer_idx: int, state: GpuInferenceState, kv: BatchedKvCache,
+                                   d_pos: Tensor, d_seqlen: Tensor, scratch: Optional[BatchedDecodeScratch] = None) -> Tensor:
+    """One decode step of B independent sequences through one layer: hidden [B, hidden] f16 -> same shape.  Row b is the
+    next token of sequence b at position d_pos[b] (int32 device tensors [B]); kv holds the sequences' caches.
+
+    The projections are the tcgen05 GEMM on the packed weights (B <= 64 rows per launch; q/k/v and gate/up one launch
+    each), RoPE + K/V write + attention of all sequences is one launch of the fused decode kernel, RMSNorm one launch
+    over the rows.  16-bit activations on every layer, as in prefill.  Row b equals the single-sequence decode of that
+    sequence within the tolerance that separates the tensor-core GEMM from the integer GEMV.  With `scratch` nothing is
+    allocated and the result is one of scratch.out (alternating with the layer index)."""
+    if hidden.dim() != 2 or hidden.shape[0] != kv.batch:
+        raise ValueError("hidden must be [batch, hidden] with the cache's batch")
+    w = state.layer_weights[layer_idx]
+    nh, nkv, hd = state.num_heads, state.num_kv_heads, state.head_dim
+    eps, scale = state.norm_eps, float(hd) ** -0.5
+    s = scratch
+    ws = None if s is None else s.gemm
+    normed = ck.rms_norm_rows(hidden, w.input_norm, eps, out=None if s is None else s.normed)
+    q, k, v = matmul_x_multi(normed, [w.q_proj, w.k_proj, w.v_proj], ws, None if s is None else [s.q, s.k, s.v])
+    attn = ck.attn_decode_fused_batch(q, k, v, kv.k[layer_idx], kv.v[layer_idx], state.rope_cos, state.rope_sin, d_pos,
+                                      d_seqlen, nh, nkv, hd, kv.max_seq, scale, out=None if s is None else s.attn)
+    h1 = matmul_x(attn, w.o_proj, ws, None if s is None else s.h1)
+    ck.add_inplace_any(h1, hidden)
+    normed2 = ck.rms_norm_rows(h1, w.post_attn_norm, eps, out=None if s is None else s.normed)
+    gate, up = matmul_x_multi(normed2, [w.gate_proj, w.up_proj], ws, None if s is None else [s.gate, s.up])
+    ck.silu_mul_inplace(gate, up)
+    out = matmul_x(gate, w.down_proj, ws, None if s is None else s.out[layer_idx & 1])
     ck.add_inplace_any(out, h1)
     return out

@@ -101,6 +101,11 @@ extern "C" {
     pub fn nve_b200_rmsnorm_gateup_silu_w4a16(h: *const CVoid, norm_weight: *const CVoid, eps: f32, act_dtype: i32,
                                               awq: *const f32, gate: *const NveB200W4Matrix, up: *const NveB200W4Matrix,
                                               mid_out: *mut CVoid, k: i32, stream: Stream) -> i32;
+    pub fn nve_b200_attn_decode_fused_batch(q: *const u16, k_new: *const u16, v_new: *const u16, k_cache: *mut u16,
+                                            v_cache: *mut u16, cos_tab: *const u16, sin_tab: *const u16, d_pos: *const i32,
+                                            d_seq_len: *const i32, out: *mut u16, batch: i32, num_heads: i32,
+                                            num_kv_heads: i32, head_dim: i32, max_seq_len: i32, scale: f32,
+                                            stream: Stream) -> i32;
     pub fn nve_b200_rms_norm_rows(x: *const CVoid, weight: *const CVoid, out: *mut CVoid, rows: i32, n: i32, eps: f32,
                                   dtype: i32, stream: Stream) -> i32;
     pub fn nve_b200_kv_cache_write_rows(k_new: *const u16, k_cache: *mut u16, v_new: *const u16, v_cache: *mut u16,

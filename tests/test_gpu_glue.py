@@ -573,3 +573,84 @@ def test_prefill_layers_match_sequential_decode(cuda, orc):
     for li in range(layers):
         for a, b in ((st_p.kv_cache.k[li], st_d.kv_cache.k[li]), (st_p.kv_cache.v[li], st_d.kv_cache.v[li])):
             assert rel_rms_err(a[:, :start + S].float().cpu().numpy(), b[:, :start + S].float().cpu().numpy()) < 5e-3
+
+
+# ------------------------------------------------------------------ batched decode: several sequences per step
+def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc):
+    """Every row of the batched fused attention (RoPE + K/V write + attention) equals the single-sequence launch on
+    that sequence's cache, position and length, bit for bit -- output and the cache row written."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    B, nh, nkv, hd, max_seq = 5, 32, 8, 128, 40
+    pos = [0, 7, 39, 18, 3]
+    q = dev(orc.to_act16(orc.fill_normal(B * nh * hd, 851, 1)), torch.float16).view(B, nh * hd)
+    k = dev(orc.to_act16(orc.fill_normal(B * nkv * hd, 851, 2)), torch.float16).view(B, nkv * hd)
+    v = dev(orc.to_act16(orc.fill_normal(B * nkv * hd, 851, 3)), torch.float16).view(B, nkv * hd)
+    kc = dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 851, 4)), torch.float16).view(B, nkv, max_seq, hd)
+    vc = dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 851, 5)), torch.float16).view(B, nkv, max_seq, hd)
+    cos, sin = orc.rope_tables_f32(hd, max_seq, 10000.0)
+    cos, sin = dev(orc.to_act16(cos), torch.float16), dev(orc.to_act16(sin), torch.float16)
+    d_pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
+    d_len = d_pos + 1
+    kc_b, vc_b = kc.clone(), vc.clone()
+    got = ck.attn_decode_fused_batch(q, k, v, kc_b, vc_b, cos, sin, d_pos, d_len, nh, nkv, hd, max_seq, hd ** -0.5)
+    for b in range(B):
+        kc_s, vc_s = kc[b].clone(), vc[b].clone()
+        want = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
+        ck.attn_decode_fused(q[b].view(nh, hd).contiguous(), k[b].view(nkv, hd).contiguous(), v[b].view(nkv, hd).contiguous(),
+                             kc_s, vc_s, cos, sin, d_pos[b:b + 1].data_ptr(), d_len[b:b + 1].data_ptr(), want, nh, nkv, hd,
+                             max_seq, hd ** -0.5)
+        torch.cuda.synchronize()
+        assert torch.equal(got[b].view(nh, hd), want), f"sequence {b}"
+        assert torch.equal(kc_b[b], kc_s) and torch.equal(vc_b[b], vc_s), f"cache of sequence {b}"
+
+
+def test_batched_decode_layers_match_single_sequence_decode(cuda, orc):
+    """gpu_layer_forward_decode_batch on B sequences at different positions against B single-sequence decode steps
+    (16-bit route) through the same two layers."""
+    from nve_b200.gpu_layer import BatchedKvCache, gpu_layer_forward_decode, gpu_layer_forward_decode_batch
+
+    torch = cuda
+    hidden, ffn, nh, nkv, hd, layers, max_seq, B = 1024, 2816, 16, 4, 64, 2, 32, 4
+    pos = [5, 0, 31, 12]
+    st = _make_state(torch, orc, hidden, ffn, nh, nkv, hd, layers, max_seq, 861, True)
+    st.routing.no_w4a8 = True
+    kvb = BatchedKvCache.zeros(layers, B, nkv, max_seq, hd)
+    for li in range(layers):
+        kvb.k[li].copy_(dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 862, 2 * li)), torch.float16).view(B, nkv, max_seq, hd))
+        kvb.v[li].copy_(dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 862, 2 * li + 1)), torch.float16).view(B, nkv, max_seq, hd))
+    x = dev(orc.to_act16(orc.fill_normal(B * hidden, 863, 1)), torch.float16).view(B, hidden)
+    # single-sequence reference: one state per sequence, its cache = that sequence's slice
+    want = []
+    caches = []
+    for b in range(B):
+        for li in range(layers):
+            st.kv_cache.k[li].copy_(kvb.k[li][b])
+            st.kv_cache.v[li].copy_(kvb.v[li][b])
+        h = x[b:b + 1].contiguous()
+        for li in range(layers):
+            h = gpu_layer_forward_decode(h, li, st, pos[b], False, 1.0)
+        want.append(h)
+        caches.append([(st.kv_cache.k[li].clone(), st.kv_cache.v[li].clone()) for li in range(layers)])
+    want = torch.cat(want)
+    d_pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
+    d_len = d_pos + 1
+    # the allocation-free form (pre-allocated scratch) on a copy of the caches gives the same bits as the allocating one
+    from nve_b200.gpu_layer import BatchedDecodeScratch
+
+    kvb2 = BatchedKvCache([t.clone() for t in kvb.k], [t.clone() for t in kvb.v], B, max_seq)
+    scratch = BatchedDecodeScratch.make(st, B, hidden, ffn)
+    hb2 = x
+    for li in range(layers):
+        hb2 = gpu_layer_forward_decode_batch(hb2, li, st, kvb2, d_pos, d_len, scratch)
+    hb = x
+    for li in range(layers):
+        hb = gpu_layer_forward_decode_batch(hb, li, st, kvb, d_pos, d_len)
+    torch.cuda.synchronize()
+    assert torch.equal(hb, hb2)
+    assert rel_rms_err(hb.float().cpu().numpy(), want.float().cpu().numpy()) < 5e-3
+    for b in range(B):
+        for li in range(layers):
+            assert rel_rms_err(kvb.k[li][b].float().cpu().numpy(), caches[b][li][0].float().cpu().numpy()) < 5e-3
+            assert rel_rms_err(kvb.v[li][b].float().cpu().numpy(), caches[b][li][1].float().cpu().numpy()) < 5e-3
