@@ -102,7 +102,9 @@ struct AdPrefetch {
 // `sync()` synchronises the threads of the virtual CTA (all of them call this function together).
 // kh / vh: cache rows of this KV head.  With FUSED the row at `pos` is taken from shared memory (the new token);
 // `pre` holds rows loaded before the wait when `pre_ok` (same addresses as this pass would use).
-template <int HD, int QH, bool FUSED, bool PRE, class Sync, class Sink>
+// STREAM: the rows of batch it + 1 are requested before batch it is reduced (two register buffers) -- for long position
+// ranges read at HBM speed (batched decode); same per-thread arithmetic and order as the plain form.
+template <int HD, int QH, bool FUSED, bool PRE, class Sync, class Sink, bool STREAM = false>
 __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, const uint16_t* kh, const uint16_t* vh,
                                              int t_begin, int t_end, int pos, float scale, bool pre_ok,
                                              const AdPrefetch* pre, Sync sync, Sink sink) {
@@ -127,14 +129,11 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
 
     const int span = PL * kAdUnroll;
     const int iters = (max(0, t_end - t_begin) + span - 1) / span;  // uniform over the virtual CTA
-    auto batch = [&](int it, bool use_pre, int pre_idx) {
-        uint4 kraw[kAdUnroll], vraw[kAdUnroll];
-        bool valid[kAdUnroll];
+    auto load = [&](int it, bool use_pre, int pre_idx, uint4 (&kraw)[kAdUnroll], uint4 (&vraw)[kAdUnroll]) {
 #pragma unroll
         for (int u = 0; u < kAdUnroll; u++) {
             const int t = t_begin + it * span + u * PL + pl;
-            valid[u] = t < t_end;
-            const int tc = valid[u] ? t : t_begin;
+            const int tc = t < t_end ? t : t_begin;
             if (FUSED && tc == pos) {
                 kraw[u] = reinterpret_cast<const uint4*>(sh.knew_s)[dc];
                 vraw[u] = reinterpret_cast<const uint4*>(sh.vnew_s)[dc];
@@ -146,6 +145,11 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
                 vraw[u] = ld_stream_u4(vh + static_cast<long long>(tc) * HD + dc * 8);
             }
         }
+    };
+    auto reduce = [&](int it, const uint4 (&kraw)[kAdUnroll], const uint4 (&vraw)[kAdUnroll]) {
+        bool valid[kAdUnroll];
+#pragma unroll
+        for (int u = 0; u < kAdUnroll; u++) valid[u] = t_begin + it * span + u * PL + pl < t_end;
         float sc[kAdUnroll][QH];
 #pragma unroll
         for (int u = 0; u < kAdUnroll; u++) {
@@ -188,10 +192,27 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
         }
     };
 
-    static_assert(kAdPre == 2, "the first two batches are peeled so that prefetched rows stay in registers");
-    if (iters > 0) batch(0, pre_ok, 0);
-    if (iters > 1) batch(1, pre_ok, 1);
-    for (int it = kAdPre; it < iters; it++) batch(it, false, 0);
+    if constexpr (STREAM) {
+        // two register buffers: batch it + 1 is in flight while batch it is reduced
+        uint4 ka[kAdUnroll], va[kAdUnroll], kb[kAdUnroll], vb[kAdUnroll];
+        if (iters > 0) load(0, false, 0, ka, va);
+        for (int it = 0; it < iters; it += 2) {
+            if (it + 1 < iters) load(it + 1, false, 0, kb, vb);
+            reduce(it, ka, va);
+            if (it + 2 < iters) load(it + 2, false, 0, ka, va);
+            if (it + 1 < iters) reduce(it + 1, kb, vb);
+        }
+    } else {
+        static_assert(kAdPre == 2, "the first two batches are peeled so that prefetched rows stay in registers");
+        auto batch = [&](int it, bool use_pre, int pre_idx) {
+            uint4 kraw[kAdUnroll], vraw[kAdUnroll];
+            load(it, use_pre, pre_idx, kraw, vraw);
+            reduce(it, kraw, vraw);
+        };
+        if (iters > 0) batch(0, pre_ok, 0);
+        if (iters > 1) batch(1, pre_ok, 1);
+        for (int it = kAdPre; it < iters; it++) batch(it, false, 0);
+    }
 
     // ---- level 1: merge the position lanes of this virtual CTA in ascending lane order
 #pragma unroll

@@ -654,3 +654,36 @@ def test_batched_decode_layers_match_single_sequence_decode(cuda, orc):
         for li in range(layers):
             assert rel_rms_err(kvb.k[li][b].float().cpu().numpy(), caches[b][li][0].float().cpu().numpy()) < 5e-3
             assert rel_rms_err(kvb.v[li][b].float().cpu().numpy(), caches[b][li][1].float().cpu().numpy()) < 5e-3
+
+
+def test_attn_decode_fused_batch_streaming_form(cuda, orc):
+    """With enough sequences the batched attention runs one CTA per (sequence, head pair) over all positions (streaming
+    form): rows agree with single-sequence launches within f32 re-association of the softmax merge, and the cache rows
+    written are bit-identical."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    B, nh, nkv, hd, max_seq = 24, 32, 8, 128, 96
+    assert B * (nh // 2) >= 2 * torch.cuda.get_device_properties(0).multi_processor_count
+    pos = [(7 * b + 3) % max_seq for b in range(B)]
+    pos[0], pos[1] = 0, max_seq - 1
+    q = dev(orc.to_act16(orc.fill_normal(B * nh * hd, 871, 1)), torch.float16).view(B, nh * hd)
+    k = dev(orc.to_act16(orc.fill_normal(B * nkv * hd, 871, 2)), torch.float16).view(B, nkv * hd)
+    v = dev(orc.to_act16(orc.fill_normal(B * nkv * hd, 871, 3)), torch.float16).view(B, nkv * hd)
+    kc = dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 871, 4)), torch.float16).view(B, nkv, max_seq, hd)
+    vc = dev(orc.to_act16(orc.fill_normal(B * nkv * max_seq * hd, 871, 5)), torch.float16).view(B, nkv, max_seq, hd)
+    cos, sin = orc.rope_tables_f32(hd, max_seq, 10000.0)
+    cos, sin = dev(orc.to_act16(cos), torch.float16), dev(orc.to_act16(sin), torch.float16)
+    d_pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
+    d_len = d_pos + 1
+    kc_b, vc_b = kc.clone(), vc.clone()
+    got = ck.attn_decode_fused_batch(q, k, v, kc_b, vc_b, cos, sin, d_pos, d_len, nh, nkv, hd, max_seq, hd ** -0.5)
+    for b in range(B):
+        kc_s, vc_s = kc[b].clone(), vc[b].clone()
+        want = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
+        ck.attn_decode_fused(q[b].view(nh, hd).contiguous(), k[b].view(nkv, hd).contiguous(), v[b].view(nkv, hd).contiguous(),
+                             kc_s, vc_s, cos, sin, d_pos[b:b + 1].data_ptr(), d_len[b:b + 1].data_ptr(), want, nh, nkv, hd,
+                             max_seq, hd ** -0.5)
+        torch.cuda.synchronize()
+        assert rel_rms_err(got[b].float().cpu().numpy().reshape(-1), want.float().cpu().numpy().reshape(-1)) < 5e-3, f"sequence {b}"
+        assert torch.equal(kc_b[b], kc_s) and torch.equal(vc_b[b], vc_s), f"cache of sequence {b}"
