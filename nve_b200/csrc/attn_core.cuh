@@ -56,8 +56,8 @@ template <bool L2ONLY> __device__ __forceinline__ uint16_t attn_ld16(const uint1
     if constexpr (L2ONLY) return __ldcg(p);
     else return *p;
 }
-template <int HD, int QH, bool FUSED, bool L2ONLY = false>
-__device__ __forceinline__ void attn_stage_q(AdShared<HD, QH>& sh, int tid, const uint16_t* q, const uint16_t* k_new,
+template <int HD, int QH, bool FUSED, bool L2ONLY = false, class SH = AdShared<HD, QH>>
+__device__ __forceinline__ void attn_stage_q(SH& sh, int tid, const uint16_t* q, const uint16_t* k_new,
                                              const uint16_t* v_new, const uint16_t* cos_tab, const uint16_t* sin_tab,
                                              int h0, int kvh, int pos, bool pos_ok) {
     constexpr int HALF = HD / 2;
@@ -102,9 +102,7 @@ struct AdPrefetch {
 // `sync()` synchronises the threads of the virtual CTA (all of them call this function together).
 // kh / vh: cache rows of this KV head.  With FUSED the row at `pos` is taken from shared memory (the new token);
 // `pre` holds rows loaded before the wait when `pre_ok` (same addresses as this pass would use).
-// STREAM: the rows of batch it + 1 are requested before batch it is reduced (two register buffers) -- for long position
-// ranges read at HBM speed (batched decode); same per-thread arithmetic and order as the plain form.
-template <int HD, int QH, bool FUSED, bool PRE, class Sync, class Sink, bool STREAM = false>
+template <int HD, int QH, bool FUSED, bool PRE, class Sync, class Sink>
 __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, const uint16_t* kh, const uint16_t* vh,
                                              int t_begin, int t_end, int pos, float scale, bool pre_ok,
                                              const AdPrefetch* pre, Sync sync, Sink sink) {
@@ -192,17 +190,7 @@ __device__ __forceinline__ void attn_partial(AdShared<HD, QH>& sh, int tid, cons
         }
     };
 
-    if constexpr (STREAM) {
-        // two register buffers: batch it + 1 is in flight while batch it is reduced
-        uint4 ka[kAdUnroll], va[kAdUnroll], kb[kAdUnroll], vb[kAdUnroll];
-        if (iters > 0) load(0, false, 0, ka, va);
-        for (int it = 0; it < iters; it += 2) {
-            if (it + 1 < iters) load(it + 1, false, 0, kb, vb);
-            reduce(it, ka, va);
-            if (it + 2 < iters) load(it + 2, false, 0, ka, va);
-            if (it + 1 < iters) reduce(it + 1, kb, vb);
-        }
-    } else {
+    {
         static_assert(kAdPre == 2, "the first two batches are peeled so that prefetched rows stay in registers");
         auto batch = [&](int it, bool use_pre, int pre_idx) {
             uint4 kraw[kAdUnroll], vraw[kAdUnroll];

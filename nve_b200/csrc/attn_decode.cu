@@ -20,33 +20,12 @@
 #include <cooperative_groups.h>
 
 #include "attn_core.cuh"
+#include "attn_params.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace nve {
 
-struct AttnParams {
-    const uint16_t* q;        // [nh, hd]
-    const uint16_t* k_new;    // [nkv, hd] (fused form)
-    const uint16_t* v_new;    // [nkv, hd]
-    uint16_t* k_cache;        // [nkv, kv_stride, hd]
-    uint16_t* v_cache;
-    const uint16_t* cos_tab;  // [max_seq, hd/2]
-    const uint16_t* sin_tab;
-    const int* d_pos;         // fused form: position of the new token
-    const int* d_seq_len;     // valid length (device scalar) or NULL
-    int seq_len;              // valid length when d_seq_len == NULL
-    uint16_t* out;            // [nh, hd] f16
-    int8_t* out_q;            // optional int8 codes of out, group 32
-    float* out_scales;        // [nh*hd/32]
-    int num_heads, num_kv_heads, kv_stride;
-    float scale;
-    // un-fused form only: blockIdx.y selects one of `rows` query rows; row r reads q + r * row_stride, writes
-    // out + r * row_stride and attends to seq_len + r positions (causal attention over a block of new positions)
-    int rows, row_stride;
-    // batched fused form: `rows` independent sequences; elements between consecutive K (or V) caches
-    long long cache_stride;
-};
 
 // BATCH (fused form only): blockIdx.y selects one of several independent sequences -- row b of q / k_new / v_new / out,
 // the b-th K/V cache and the b-th position and length words.
@@ -191,71 +170,6 @@ __global__ void __launch_bounds__(kAdThreads) attn_decode_kernel(const AttnParam
     }
 }
 
-// Batched decode with enough sequences to fill the GPU without splitting one: a CTA serves QH query heads of ONE
-// sequence over ALL its positions (no cluster, no cross-CTA merge), with the K/V rows of the next batch of positions in
-// flight while the current one is reduced -- a bandwidth-oriented form of the same arithmetic.  RoPE, the K/V write and
-// the use of the fresh k/v row are the fused kernel's.  grid = (num_heads / QH, batch).
-template <int HD, int QH>
-__global__ void __launch_bounds__(kAdThreads) attn_batch_stream_kernel(const AttnParams pin) {
-    AttnParams p = pin;
-    {
-        const long long b = blockIdx.y;
-        p.q += b * (static_cast<long long>(p.num_heads) * HD);
-        p.out += b * (static_cast<long long>(p.num_heads) * HD);
-        p.k_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
-        p.v_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
-        p.k_cache += b * p.cache_stride;
-        p.v_cache += b * p.cache_stride;
-        p.d_pos += b;
-        p.d_seq_len += b;
-    }
-    constexpr int DC = HD / 8;
-    __shared__ AdShared<HD, QH> sh;
-    const int tid = threadIdx.x;
-    const int groups = p.num_heads / p.num_kv_heads;
-    const int per_kv = groups / QH;
-    const int kvh = blockIdx.x / per_kv;
-    const int h0 = kvh * groups + (blockIdx.x % per_kv) * QH;
-    const uint16_t* kh = p.k_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
-    const uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
-    pdl_wait();
-    const int seq_len = max(0, min(*p.d_seq_len, p.kv_stride));
-    const int pos = *p.d_pos;
-    const bool pos_ok = pos >= 0 && pos < p.kv_stride;
-    attn_stage_q<HD, QH, true>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
-    __syncthreads();
-    pdl_launch_dependents();
-    if (pos_ok && (blockIdx.x % per_kv) == 0 && tid < 2 * DC) {  // one CTA per KV head stores the new row
-        const int which = tid / DC, d = tid % DC;
-        uint16_t* dst = (which == 0 ? p.k_cache : p.v_cache) + (static_cast<long long>(kvh) * p.kv_stride + pos) * HD;
-        reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
-    }
-    uint16_t* out = p.out;
-    auto sync = [] { __syncthreads(); };
-    auto sink = [&](int h, int d, float mm, float ss, float a) {
-        (void)mm;
-        const float inv = ss > 0.0f ? __fdiv_rn(1.0f, ss) : 0.0f;
-        out[static_cast<long long>(h0 + h) * HD + d] = Act16<NVE_DT_F16>::from_f32(__fmul_rn(a, inv));
-    };
-    attn_partial<HD, QH, true, false, decltype(sync), decltype(sink), true>(sh, tid, kh, vh, 0, seq_len, pos_ok ? pos : -1,
-                                                                            p.scale, false, nullptr, sync, sink);
-}
-
-template <int HD, int QH> static cudaError_t launch_batch_stream(const AttnParams& p, cudaStream_t st) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.num_heads / QH, p.rows);
-    cfg.blockDim = dim3(kAdThreads);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    if (pdl_enabled()) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-    }
-    return cudaLaunchKernelEx(&cfg, attn_batch_stream_kernel<HD, QH>, p);
-}
-
 template <int HD, int QH, bool FUSED, bool BATCH = false> static cudaError_t launch_ad(const AttnParams& p, cudaStream_t st) {
     const int clusters = p.num_heads / QH;
     cudaLaunchConfig_t cfg = {};
@@ -371,8 +285,8 @@ extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k
 
 /* nve_b200_attn_decode_fused for `batch` independent sequences in one launch: row b of q [batch, nh*hd] and of
  * k_new / v_new [batch, nkv*hd] belongs to sequence b, whose caches are k_cache / v_cache + b * nkv * max_seq_len * hd,
- * whose position is d_pos[b] and whose valid length is d_seq_len[b].  Row b of the result (and the cache row written)
- * is bit-identical to a single-sequence call. */
+ * whose position is d_pos[b] and whose valid length is d_seq_len[b].  Small batches run the clustered kernel (row b
+ * bit-identical to a single-sequence call), large ones the tensor-core kernel of attn_batch_mma.cu. */
 extern "C" int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
                                                 uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
                                                 const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,
@@ -396,9 +310,10 @@ extern "C" int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     // enough (sequence, head pair) units to fill every SM twice: one CTA per unit over all positions, streaming;
     // otherwise the clustered kernel, which splits a sequence's positions over eight CTAs
-    const int groups = num_heads / num_kv_heads;
-    if ((groups % 2) == 0 && static_cast<long long>(batch) * (num_heads / 2) >= 2ll * sm_count()) {
-        e = head_dim == 128 ? launch_batch_stream<128, 2>(p, cs) : launch_batch_stream<64, 2>(p, cs);
+    // one CTA per (sequence, KV head) on the tensor cores (attn_batch_mma.cu) from 64 such units on: measured at 8
+    // KV heads and context 1024, 8 sequences take 23 us there against 29 us on the clustered kernel, 64 sequences 63
+    // against 188; below that the clustered kernel, which splits a sequence's positions over eight CTAs, is faster
+    if (static_cast<long long>(batch) * num_kv_heads >= 64 && attn_batch_mma_try(p, head_dim, cs, e)) {
         count_launch();
         return set_cuda_status(e);
     }

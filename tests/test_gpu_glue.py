@@ -656,15 +656,18 @@ def test_batched_decode_layers_match_single_sequence_decode(cuda, orc):
             assert rel_rms_err(kvb.v[li][b].float().cpu().numpy(), caches[b][li][1].float().cpu().numpy()) < 5e-3
 
 
-def test_attn_decode_fused_batch_streaming_form(cuda, orc):
-    """With enough sequences the batched attention runs one CTA per (sequence, head pair) over all positions (streaming
-    form): rows agree with single-sequence launches within f32 re-association of the softmax merge, and the cache rows
+@pytest.mark.parametrize("B,nh,nkv,hd", [(24, 32, 8, 128), (20, 16, 16, 64), (24, 64, 8, 64), (80, 4, 2, 128),
+                                         (24, 24, 8, 128)])
+def test_attn_decode_fused_batch_large_batch_forms(cuda, orc, B, nh, nkv, hd):
+    """With enough sequences the batched attention runs one CTA per (sequence, KV head) over all positions on the
+    tensor cores (group sizes 1, 2, 4, 8; the probabilities are rounded to f16 for the p.V product; other group sizes
+    stay on the clustered kernel): rows agree with single-sequence launches within that rounding, and the cache rows
     written are bit-identical."""
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    B, nh, nkv, hd, max_seq = 24, 32, 8, 128, 96
-    assert B * (nh // 2) >= 2 * torch.cuda.get_device_properties(0).multi_processor_count
+    max_seq = 96
+    assert B * nkv >= 64  # the dispatch threshold of nve_b200_attn_decode_fused_batch
     pos = [(7 * b + 3) % max_seq for b in range(B)]
     pos[0], pos[1] = 0, max_seq - 1
     q = dev(orc.to_act16(orc.fill_normal(B * nh * hd, 871, 1)), torch.float16).view(B, nh * hd)
