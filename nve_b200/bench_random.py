@@ -177,6 +177,9 @@ def _main() -> None:
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
     ap.add_argument("--batch", type=int, default=1, help="> 1: the tcgen05 batched W4A16 GEMM with this many rows of X")
+    ap.add_argument("--attn-batch", type=int, default=0,
+                    help="instead of a GEMV group: the fused attention of this many independent sequences in one launch "
+                         "(RoPE + K/V write + attention at --context), rotating over --layers cache sets")
     ap.add_argument("--fused-silu", action="store_true",
                     help="--group gateup: the decode step's own launch (RMSNorm prologue, SiLU*up and the conversion for "
                          "the down projection in the epilogue)")
@@ -190,6 +193,45 @@ def _main() -> None:
     from .decode_graph import CapturedSequence, PersistentDecode
 
     ck.set_pdl(bool(a.pdl))
+    if a.attn_batch > 0:
+        shape, b, ctx = SHAPES[a.model], a.attn_batch, a.context
+        nh, nkv, hd = shape.num_heads, shape.num_kv_heads, shape.head_dim
+        cos, sin = rope_tables(hd, ctx, 10000.0, "cuda")
+        kcs = [ck.fill_normal(b * nkv * ctx * hd, 1, 10 + i, dtype=torch.float16).view(b, nkv, ctx, hd) for i in range(a.layers)]
+        vcs = [ck.fill_normal(b * nkv * ctx * hd, 1, 50 + i, dtype=torch.float16).view(b, nkv, ctx, hd) for i in range(a.layers)]
+        q = ck.fill_normal(b * nh * hd, 1, 1, dtype=torch.float16).view(b, nh * hd)
+        k = ck.fill_normal(b * nkv * hd, 1, 2, dtype=torch.float16).view(b, nkv * hd)
+        v = ck.fill_normal(b * nkv * hd, 1, 3, dtype=torch.float16).view(b, nkv * hd)
+        out = torch.empty_like(q)
+        d_pos = torch.full((b,), ctx - 1, dtype=torch.int32, device="cuda")
+        d_len = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
+        nbytes = 2 * b * nkv * ctx * hd * 2
+
+        def attn_launches(_a=None, _b=None):
+            for i in range(a.layers):
+                ck.attn_decode_fused_batch(q, k, v, kcs[i], vcs[i], cos, sin, d_pos, d_len, nh, nkv, hd, ctx, hd ** -0.5, out=out)
+
+        torch.cuda.synchronize()
+        if not a.time:
+            for _ in range(a.reps):
+                attn_launches()
+            torch.cuda.synchronize()
+            print(f"{a.model} attention of {b} sequences at context {ctx}: {a.reps * a.layers} launches of {nbytes / 1e6:.1f} MB")
+            return
+        seq = CapturedSequence(attn_launches)
+        for _ in range(3):
+            seq.replay(0, 1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.reps):
+            seq.replay(0, 1)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (a.reps * a.layers)
+        seq.destroy()
+        print(f"{a.model} attention of {b} sequences at context {ctx}: {us:.2f} us, {nbytes / us / 1e3:.1f} GB/s ({nbytes / 1e6:.1f} MB)")
+        return
     if a.persistent:
         import dataclasses
 

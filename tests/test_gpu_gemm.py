@@ -1,5 +1,10 @@
-"""GPU parity: the tcgen05 batched W4A16 GEMM against the reference's CPU semantics (q4_linear: one f32 GEMV per
-row of X, src/quantize.rs:1057-1075) on the same 16-bit-rounded activations."""
+"""GPU parity: the batched W4A16 GEMM (mma.sync kernel up to 8 batch rows, tcgen05 kernel above) against the
+reference's CPU semantics (q4_linear: one f32 GEMV per row of X, src/quantize.rs:1057-1075) on the same
+16-bit-rounded activations."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -21,7 +26,9 @@ def _case(orc, M, N, K, seed, bf):
 @pytest.mark.parametrize("M,N,K", [(16, 128, 64), (16, 128, 512), (1, 256, 1024), (8, 384, 2048), (32, 1024, 4096),
                                     (64, 512, 4096), (33, 200, 1024), (64, 4096, 4096), (16, 2048, 14336),
                                     # more tiles than SMs: a CTA's run crosses tile boundaries (partial first and last segments)
-                                    (16, 25600, 512), (32, 20480, 1024), (8, 19000, 768)])
+                                    (16, 25600, 512), (32, 20480, 1024), (8, 19000, 768),
+                                    # narrow batches (the mma.sync kernel): K not a multiple of 256, ragged N, split tiles
+                                    (4, 300, 320), (8, 128, 64), (7, 1000, 4096), (2, 19000, 1280)])
 @pytest.mark.parametrize("bf", [False, True])
 def test_gemm_w4a16_tensor_core(cuda, orc, M, N, K, bf):
     from nve_b200 import cuda_kernels as ck
@@ -128,3 +135,17 @@ def test_matmul_x_matches_q4_linear(cuda, orc, M, with_awq):
     assert tuple(y.shape) == (M, N)
     ref = orc.q4_linear(blocks, orc.from_act16(X16), awq_inv=awq)
     assert rel_rms_err(y.float().cpu().numpy(), ref) < TOL
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
+def test_gemm_parity_with_each_kernel_forced(cuda, kernel):
+    """The library picks the kernel by batch size; NVE_B200_GEMM_KERNEL (read once per process) forces one.  The
+    parity cases above are run again in a child process with each kernel forced, so that the mma.sync kernel is
+    also checked at 16 and 32 batch rows and the tcgen05 kernel at 8 and fewer."""
+    if os.environ.get("NVE_B200_GEMM_KERNEL_CHILD"):
+        pytest.skip("already inside the forced-kernel child run")
+    env = dict(os.environ, NVE_B200_GEMM_KERNEL=kernel, NVE_B200_GEMM_KERNEL_CHILD="1")
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-m", "gpu", "-k",
+                          "tensor_core or multi_matrix", "-p", "no:cacheprovider"],
+                         env=env, capture_output=True, text=True, timeout=900, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
