@@ -13,7 +13,7 @@ the CPU restatement of the reference (oracle/) on a bounded sample with all host
 
 Besides the contract keys the line carries: `gemv_shapes` (every GEMV launch of the step per shape and route),
 `config1` / `config2` (the single 8192x2048 W4A16 GEMV and the Llama-3.2-1B W4A8 layer set), `gemm_batch` (the
-tcgen05 batched W4A16 GEMM at batch 1..64), `persistent_step` (the same token through the one-kernel form) and
+batched W4A16 GEMM at batch 1..64), `persistent_step` (the same token through the one-kernel form) and
 `lm_head` (tokens/s when the final RMSNorm + lm_head GEMV run on the device too).
 """
 from __future__ import annotations
@@ -403,7 +403,7 @@ def config5_entry(torch, ck, peak, steps: int):
 
 
 def gemm_batch_table(torch, ck, state, shape, peak):
-    """Measurement configuration 4: the batched W4A16 path at batch 1 (GEMV) and 8..64 (tcgen05 GEMM) on the four 8B
+    """Measurement configuration 4: the batched W4A16 path at batch 1 (GEMV) and 8..64 (tensor-core GEMM: mma.sync at 8, tcgen05 above) on the four 8B
     projection groups, rotating over the 32 layers' weights."""
     from nve_b200.bench_random import proj_dims, w4_bytes
 
@@ -442,7 +442,7 @@ def gemm_batch_table(torch, ck, state, shape, peak):
 
 
 def prefill_entry(torch, ck, state, shape, S: int = 256):
-    """A prompt block of S positions through all layers with gpu_layer_forward_prefill (tcgen05 GEMM projections in
+    """A prompt block of S positions through all layers with gpu_layer_forward_prefill (tensor-core GEMM projections in
     64-row slices, one-launch RMSNorm rows / KV rows / causal attention).  Eager launches, allocations included: the
     reference has no graph for prefill either (src/gpu_layer.rs:1086-1160)."""
     from nve_b200.gpu_layer import gpu_layer_forward_prefill
@@ -467,7 +467,7 @@ def prefill_entry(torch, ck, state, shape, S: int = 256):
 
 def batched_decode_entries(torch, ck, state, shape, batches=(8, 16, 32, 64)):
     """One decode step of B independent sequences (context CONTEXT each) through all layers with
-    gpu_layer_forward_decode_batch: tcgen05 GEMM projections, one fused RoPE + K/V write + attention launch for all
+    gpu_layer_forward_decode_batch: tensor-core GEMM projections, one fused RoPE + K/V write + attention launch for all
     sequences, RMSNorm over rows; recorded once into the library's graph (pre-allocated scratch) and replayed.  Tokens per
     second are summed over the sequences.  The reference has no batched decode (its batch > 1 is prefill only)."""
     from nve_b200.gpu_layer import BatchedDecodeScratch, BatchedKvCache, gpu_layer_forward_decode_batch

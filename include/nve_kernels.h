@@ -363,12 +363,15 @@ NVE_API int nve_b200_fill_normal(float* out, long long n, unsigned long long see
 NVE_API int nve_b200_fill_normal_16(void* out, long long n, unsigned long long seed, unsigned long long stream_id,
                             unsigned long long first, float scale, int dtype, nve_stream_t stream);
 
-/* Batched W4A16 GEMM for decode batches 1 < M <= 64 on the tcgen05 tensor cores: Y[M,N] = X[M,K] . W^T with the
- * packed weights dequantised on the fly into tensor memory (replaces nve_dequant_w4a16 + dense GEMM,
- * src/gpu_layer.rs:220-239).
+/* Batched W4A16 GEMM for decode batches 1 < M <= 64 on the tensor cores: Y[M,N] = X[M,K] . W^T with the packed
+ * weights read once and dequantised on the fly (replaces nve_dequant_w4a16 + dense GEMM,
+ * src/gpu_layer.rs:220-239).  Above 8 rows the weights go to tensor memory and tcgen05.mma; up to 8 rows a kernel
+ * that keeps them in registers and issues mma.sync is faster and is used instead (same arguments, same work split
+ * and workspace, results equal up to the order of the f32 additions).  The environment variable
+ * NVE_B200_GEMM_KERNEL = tc | mma, read at the first call, forces one kernel (mma: M <= 32 only).
  * X and Y are row-major; x_dtype f16 or bf16, y_dtype = x_dtype or f32; K % 64 == 0; X and nibbles 16-byte aligned,
  * scales 8-byte aligned.  Weights are rounded to f16 as (q-8)*scale like the reference's dequantisation;
- * accumulation is f32 in tensor memory.
+ * accumulation is f32.
  * `scratch` (may be NULL for f16 activations) holds, in this order, an f16 copy of bf16 activations (exact up to
  * +-65504, saturating beyond) and f32 partial tiles: with a workspace the (tile, 256-weight K slice) units are dealt
  * to the SMs in equal contiguous runs, so that few tiles still fill all SMs and a tile count that is not a multiple

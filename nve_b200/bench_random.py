@@ -176,7 +176,7 @@ def _main() -> None:
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="time the launches with CUDA events inside a captured graph")
-    ap.add_argument("--batch", type=int, default=1, help="> 1: the tcgen05 batched W4A16 GEMM with this many rows of X")
+    ap.add_argument("--batch", type=int, default=1, help="> 1: the batched W4A16 GEMM with this many rows of X")
     ap.add_argument("--attn-batch", type=int, default=0,
                     help="instead of a GEMV group: the fused attention of this many independent sequences in one launch "
                          "(RoPE + K/V write + attention at --context), rotating over --layers cache sets")

@@ -43,7 +43,7 @@ def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None, out: Optiona
     """`GpuWeight::matmul_x` for W4 weights (src/gpu_layer.rs:220-239): x [M, K] -> [M, N].
 
     The reference sends M == 1 to `fused_matvec_w4a16` and M > 1 through `dequant_w4a16` + a dense matmul (the whole
-    matrix materialised in f16, 4.6 bytes of traffic per weight).  Here M > 1 goes to the tcgen05 GEMM that reads the
+    matrix materialised in f16, 4.6 bytes of traffic per weight).  Here M > 1 goes to the tensor-core GEMM that reads the
     packed weights once per slice of up to 64 rows of x (prefill-sized M is walked in such slices); the activation
     multiplier `awq_scales`, which the GEMM has no argument for, is applied to x first as the GEMV does per element."""
     if x.dim() != 2 or x.shape[1] != w.k:
@@ -401,7 +401,7 @@ def gpu_layer_forward_prefill(hidden: Tensor, layer_idx: int, state: GpuInferenc
     K/V cache of the layer receives positions start_pos .. start_pos + S - 1.
 
     The reference dequantises every projection to f16 and calls a dense GEMM, runs RMSNorm once per token and an
-    unfused masked attention; here the projections are the tcgen05 GEMM on the packed weights (q/k/v and gate/up one
+    unfused masked attention; here the projections are the tensor-core GEMM on the packed weights (q/k/v and gate/up one
     launch each per 64-row slice), RMSNorm / KV write / causal attention are one launch each.  Like the reference's
     prefill, every layer runs on 16-bit activations (the int8 route is a batch-1 path, :1017-1025)."""
     if hidden.dim() != 2:
@@ -478,7 +478,7 @@ def gpu_layer_forward_decode_batch(hidden: Tensor, layer_idx: int, state: GpuInf
     """One decode step of B independent sequences through one layer: hidden [B, hidden] f16 -> same shape.  Row b is the
     next token of sequence b at position d_pos[b] (int32 device tensors [B]); kv holds the sequences' caches.
 
-    The projections are the tcgen05 GEMM on the packed weights (B <= 64 rows per launch; q/k/v and gate/up one launch
+    The projections are the tensor-core GEMM on the packed weights (B <= 64 rows per launch; q/k/v and gate/up one launch
     each), RoPE + K/V write + attention of all sequences is one launch of the fused decode kernel, RMSNorm one launch
     over the rows.  16-bit activations on every layer, as in prefill.  Row b equals the single-sequence decode of that
     sequence within the tolerance that separates the tensor-core GEMM from the integer GEMV.  With `scratch` nothing is
