@@ -441,28 +441,33 @@ def gemm_batch_table(torch, ck, state, shape, peak):
     return table, err
 
 
-def prefill_entry(torch, ck, state, shape, S: int = 256):
-    """A prompt block of S positions through all layers with gpu_layer_forward_prefill (tensor-core GEMM projections in
-    64-row slices, one-launch RMSNorm rows / KV rows / causal attention).  Eager launches, allocations included: the
-    reference has no graph for prefill either (src/gpu_layer.rs:1086-1160)."""
-    from nve_b200.gpu_layer import gpu_layer_forward_prefill
+def prefill_entry(torch, ck, state, shape, lengths=(64, 256, 1024)):
+    """A prompt block of S positions through all layers with gpu_layer_forward_prefill: projections through
+    matmul_x (the fused tensor-core GEMM in 64-row slices up to 128 rows, dequantisation + dense GEMM above, as the
+    reference does for every prompt), one-launch RMSNorm rows / KV rows / causal attention.  Eager launches,
+    allocations included: the reference has no graph for prefill either (src/gpu_layer.rs:1086-1160)."""
+    from nve_b200.gpu_layer import DENSE_ROWS, gpu_layer_forward_prefill
 
-    x = ck.fill_normal(S * shape.hidden, SEED, 9500, dtype=torch.float16).view(S, shape.hidden)
     layers = len(state.layer_weights)
+    res = {}
+    for S in lengths:
+        x = ck.fill_normal(S * shape.hidden, SEED, 9500, dtype=torch.float16).view(S, shape.hidden)
 
-    def run(_i):
-        h = x
-        for li in range(layers):
-            h = gpu_layer_forward_prefill(h, li, state, 0)
-        return h
+        def run(_i):
+            h = x
+            for li in range(layers):
+                h = gpu_layer_forward_prefill(h, li, state, 0)
+            return h
 
-    out = run(0)
-    torch.cuda.synchronize()
-    finite = bool(torch.isfinite(out.float()).all())
-    ms = time_events(torch, run, 3)
-    return {"workload": f"prompt block of {S} positions through all {layers} layers (positions 0..{S - 1}, 16-bit route)",
-            "ms": round(ms, 3), "prompt_tok_s": round(S / (ms * 1e-3), 1), "output_finite": finite,
-            "gemm_error": ck.gemm_error()}
+        out = run(0)
+        torch.cuda.synchronize()
+        finite = bool(torch.isfinite(out.float()).all())
+        ms = time_events(torch, run, 3)
+        res[str(S)] = {"ms": round(ms, 3), "prompt_tok_s": round(S / (ms * 1e-3), 1), "output_finite": finite,
+                       "projections": "dequantise + dense GEMM" if S > DENSE_ROWS else "fused W4A16 GEMM, 64-row slices"}
+    res["workload"] = f"prompt block of S positions through all {layers} layers (positions 0..S-1, 16-bit route)"
+    res["gemm_error"] = ck.gemm_error()
+    return res
 
 
 def batched_decode_entries(torch, ck, state, shape, batches=(8, 16, 32, 64)):

@@ -218,8 +218,11 @@ NVE_API int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_
  *   src/gpu_layer.rs:814-818.
  * nve_b200_attn_prefill_causal: row r of q [rows, num_heads * head_dim] attends to positions [0, start_pos + r] of the
  *   caches (which already hold the block); out has q's layout.  Replaces the unfused masked SDPA of
- *   src/gpu_layer.rs:846-885; every row equals a nve_flash_decode_f16 call of length start_pos + r + 1 bit for bit
- *   (the decode kernel with the row as second grid dimension).  head_dim 64 or 128; q and caches 16-byte aligned. */
+ *   src/gpu_layer.rs:846-885.  Blocks of fewer than 64 (row, KV head) pairs run the decode kernel with the row as
+ *   second grid dimension: every row equals a nve_flash_decode_f16 call of length start_pos + r + 1 bit for bit.
+ *   Larger blocks run a tensor-core kernel (one CTA per row and KV head; f16 probabilities, another summation
+ *   order): equal to those calls within 5e-3 of the largest output.  head_dim 64 or 128; q and caches 16-byte
+ *   aligned. */
 NVE_API int nve_b200_rms_norm_rows(const void* x, const void* weight, void* out, int rows, int n, float eps, int dtype,
                                    nve_stream_t stream);
 NVE_API int nve_b200_kv_cache_write_rows(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new,

@@ -48,7 +48,7 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int HD, int G>
+template <int HD, int G, bool FUSED>
 __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const AttnParams pin) {
     constexpr int DC = HD / 8;        // 16-byte chunks per row
     constexpr int DPT = HD / 4;       // dims of a K row per lane
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
     constexpr int KK = HD / 16;       // MMAs per score tile
     static_assert(VQ >= 1 && KQ >= 1 && G >= 1 && G <= 8, "head_dim 64 or 128, up to 8 query heads per KV head");
     AttnParams p = pin;
-    {
+    if constexpr (FUSED) {
         const long long b = blockIdx.y;
         p.q += b * (static_cast<long long>(p.num_heads) * HD);
         p.out += b * (static_cast<long long>(p.num_heads) * HD);
@@ -68,6 +68,9 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
         p.v_cache += b * p.cache_stride;
         p.d_pos += b;
         p.d_seq_len += b;
+    } else {  // causal block: row blockIdx.y of q attends to seq_len + row positions of the one cache
+        p.q += static_cast<long long>(blockIdx.y) * p.row_stride;
+        p.out += static_cast<long long>(blockIdx.y) * p.row_stride;
     }
     __shared__ AmShared<HD, G> sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -78,18 +81,25 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
     uint16_t* vh = p.v_cache + static_cast<long long>(kvh) * p.kv_stride * HD;
 
     pdl_wait();
-    const int seq_len = max(0, min(*p.d_seq_len, p.kv_stride));
-    const int pos = *p.d_pos;
-    const bool pos_ok = pos >= 0 && pos < p.kv_stride;
-    attn_stage_q<HD, G, true>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
-    __syncthreads();
-    pdl_launch_dependents();
-    // the new row goes to the cache first and is read back from there like every other row (same CTA: the barrier
-    // orders the store before the loads, which are ordinary coherent loads)
-    if (pos_ok && tid < 2 * DC) {
-        const int which = tid / DC, d = tid % DC;
-        uint16_t* dst = (which == 0 ? kh : vh) + static_cast<long long>(pos) * HD;
-        reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
+    int seq_len;
+    if constexpr (FUSED) {
+        seq_len = max(0, min(*p.d_seq_len, p.kv_stride));
+        const int pos = *p.d_pos;
+        const bool pos_ok = pos >= 0 && pos < p.kv_stride;
+        attn_stage_q<HD, G, true>(sh, tid, p.q, p.k_new, p.v_new, p.cos_tab, p.sin_tab, h0, kvh, pos, pos_ok);
+        __syncthreads();
+        pdl_launch_dependents();
+        // the new row goes to the cache first and is read back from there like every other row (same CTA: the barrier
+        // orders the store before the loads, which are ordinary coherent loads)
+        if (pos_ok && tid < 2 * DC) {
+            const int which = tid / DC, d = tid % DC;
+            uint16_t* dst = (which == 0 ? kh : vh) + static_cast<long long>(pos) * HD;
+            reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
+        }
+    } else {
+        seq_len = max(0, min(p.seq_len + static_cast<int>(blockIdx.y), p.kv_stride));
+        attn_stage_q<HD, G, false>(sh, tid, p.q, nullptr, nullptr, nullptr, nullptr, h0, kvh, 0, false);
+        pdl_launch_dependents();
     }
     __syncthreads();
 
@@ -213,7 +223,7 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
     }
 }
 
-template <int HD, int G> static cudaError_t launch_am(const AttnParams& p, cudaStream_t st) {
+template <int HD, int G> static cudaError_t launch_am(const AttnParams& p, cudaStream_t st, bool fused) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.num_kv_heads, p.rows);
     cfg.blockDim = dim3(kAmThreads);
@@ -225,26 +235,27 @@ template <int HD, int G> static cudaError_t launch_am(const AttnParams& p, cudaS
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    return cudaLaunchKernelEx(&cfg, attn_batch_mma_kernel<HD, G>, p);
+    return fused ? cudaLaunchKernelEx(&cfg, attn_batch_mma_kernel<HD, G, true>, p)
+                 : cudaLaunchKernelEx(&cfg, attn_batch_mma_kernel<HD, G, false>, p);
 }
 
-bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err) {
+bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err, bool fused) {
     const int groups = p.num_heads / p.num_kv_heads;
     if (head_dim == 128) {
         switch (groups) {
-            case 1: err = launch_am<128, 1>(p, st); return true;
-            case 2: err = launch_am<128, 2>(p, st); return true;
-            case 4: err = launch_am<128, 4>(p, st); return true;
-            case 8: err = launch_am<128, 8>(p, st); return true;
+            case 1: err = launch_am<128, 1>(p, st, fused); return true;
+            case 2: err = launch_am<128, 2>(p, st, fused); return true;
+            case 4: err = launch_am<128, 4>(p, st, fused); return true;
+            case 8: err = launch_am<128, 8>(p, st, fused); return true;
             default: return false;
         }
     }
     if (head_dim == 64) {
         switch (groups) {
-            case 1: err = launch_am<64, 1>(p, st); return true;
-            case 2: err = launch_am<64, 2>(p, st); return true;
-            case 4: err = launch_am<64, 4>(p, st); return true;
-            case 8: err = launch_am<64, 8>(p, st); return true;
+            case 1: err = launch_am<64, 1>(p, st, fused); return true;
+            case 2: err = launch_am<64, 2>(p, st, fused); return true;
+            case 4: err = launch_am<64, 4>(p, st, fused); return true;
+            case 8: err = launch_am<64, 8>(p, st, fused); return true;
             default: return false;
         }
     }

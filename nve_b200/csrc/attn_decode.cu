@@ -257,8 +257,10 @@ extern "C" int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_n
 }
 
 /* Causal attention of a block of S new positions against the cache (which already holds them): row r of q
- * [S, num_heads * head_dim] attends to positions [0, start_pos + r]; out has q's layout.  One launch: the decode
- * kernel with the row as second grid dimension, so every row equals a nve_flash_decode_f16 call of that length. */
+ * [S, num_heads * head_dim] attends to positions [0, start_pos + r]; out has q's layout.  One launch.  Small blocks
+ * (fewer than 64 (row, KV head) pairs) run the decode kernel with the row as second grid dimension, so every row
+ * equals a nve_flash_decode_f16 call of that length bit for bit; larger ones run the tensor-core kernel of
+ * attn_batch_mma.cu (one CTA per row and KV head, scores and outputs on mma.sync), equal to it within rounding. */
 extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out,
                                             int rows, int start_pos, int num_heads, int num_kv_heads, int head_dim,
                                             int max_seq_len, float scale, nve_stream_t stream) {
@@ -278,6 +280,10 @@ extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k
     p.rows = rows;
     p.row_stride = num_heads * head_dim;
     cudaError_t e = cudaSuccess;
+    if (static_cast<long long>(rows) * num_kv_heads >= 64 && attn_batch_mma_try(p, head_dim, static_cast<cudaStream_t>(stream), e, false)) {
+        count_launch();
+        return set_cuda_status(e);
+    }
     if (!attn_decode_dispatch<false>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
     count_launch();
     return set_cuda_status(e);

@@ -27,7 +27,8 @@ struct AttnParams {
     long long cache_stride;
 };
 
-// attn_batch_mma.cu: false when the shape is not covered (the caller then uses another kernel)
-bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err);
+// attn_batch_mma.cu: false when the shape is not covered (the caller then uses another kernel).  fused: `rows`
+// independent sequences with RoPE and the K/V write inside; else the un-fused causal block described above.
+bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err, bool fused = true);
 
 }  // namespace nve

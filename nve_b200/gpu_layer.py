@@ -39,16 +39,43 @@ class GpuW4:
         return (self.nibbles, self.scales, self.n)
 
 
+# Rows of x above which matmul_x materialises the weights in f16 and calls the library GEMM.  The sliced kernel
+# reads 0.625 bytes per weight per 64 rows (gate+up of an 8B model: 44 us per slice), the dense route writes and
+# reads 2 bytes per weight once plus a compute-bound GEMM: level at about two slices, ahead from three.
+DENSE_ROWS = 128
+
+
+def _matmul_dense(x: Tensor, w: GpuW4, out: Optional[Tensor]) -> Tensor:
+    """x [M, K] . W^T through `nve_b200_dequant_w4a16` + a dense library GEMM, as src/gpu_layer.rs:220-239 does for
+    every M > 1.  Weights are dequantised to f16 (the reference's type); bf16 activations are converted to f16 with
+    saturation, like the pre-pass of the fused GEMM, and the result is rounded once to x's type."""
+    wf = ck.dequant_w4a16_any(w.nibbles, w.scales, None, w.n, w.k, out_dtype=torch.float16)
+    xf = x if x.dtype == torch.float16 else x.float().clamp_(-65504.0, 65504.0).to(torch.float16)
+    if out is not None and out.dtype == torch.float16 and out.is_contiguous():
+        return torch.matmul(xf, wf.t(), out=out)
+    y = torch.matmul(xf, wf.t())
+    if out is None:
+        return y if y.dtype == x.dtype else y.to(x.dtype)
+    out.copy_(y)
+    return out
+
+
 def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None, out: Optional[Tensor] = None) -> Tensor:
     """`GpuWeight::matmul_x` for W4 weights (src/gpu_layer.rs:220-239): x [M, K] -> [M, N].
 
     The reference sends M == 1 to `fused_matvec_w4a16` and M > 1 through `dequant_w4a16` + a dense matmul (the whole
     matrix materialised in f16, 4.6 bytes of traffic per weight).  Here M > 1 goes to the tensor-core GEMM that reads the
-    packed weights once per slice of up to 64 rows of x (prefill-sized M is walked in such slices); the activation
-    multiplier `awq_scales`, which the GEMM has no argument for, is applied to x first as the GEMV does per element."""
+    packed weights once per slice of up to 64 rows of x; above DENSE_ROWS rows, where the product is bound by
+    arithmetic and re-reading the packed weights for every slice costs more than materialising them once, it takes
+    the reference's own route (`_matmul_dense`).  The activation multiplier `awq_scales`, which the GEMM has no
+    argument for, is applied to x first as the GEMV does per element."""
     if x.dim() != 2 or x.shape[1] != w.k:
         raise ValueError(f"x must be [M, {w.k}]")
     m = x.shape[0]
+    if m > DENSE_ROWS:
+        if w.awq_scales is not None:
+            x = (x.float() * w.awq_scales.view(1, -1)).to(x.dtype)
+        return _matmul_dense(x, w, out)
     if m == 1 and out is None:
         return ck.fused_matvec_w4a16(x, w.nibbles, w.scales, w.awq_scales, w.n, w.k)
     if m == 1:
@@ -69,10 +96,10 @@ def matmul_x(x: Tensor, w: GpuW4, scratch: Optional[Tensor] = None, out: Optiona
 def matmul_x_multi(x: Tensor, ws: Sequence[GpuW4], scratch: Optional[Tensor] = None,
                    outs: Optional[Sequence[Tensor]] = None) -> List[Tensor]:
     """matmul_x for several projections of the same x (q/k/v, gate/up) in one GEMM launch per 64-row slice: their
-    tiles share the grid, so narrow projections do not run as few-CTA kernels.  M == 1 and weights with an
-    activation multiplier go through matmul_x one by one."""
+    tiles share the grid, so narrow projections do not run as few-CTA kernels.  M == 1, M > DENSE_ROWS and weights
+    with an activation multiplier go through matmul_x one by one."""
     m, k = x.shape
-    if m == 1 or any(w.awq_scales is not None for w in ws):
+    if m == 1 or m > DENSE_ROWS or any(w.awq_scales is not None for w in ws):
         return [matmul_x(x, w, scratch, None if outs is None else outs[i]) for i, w in enumerate(ws)]
     outs = [torch.empty((m, w.n), dtype=x.dtype, device=x.device) for w in ws] if outs is None else list(outs)
     step = 64

@@ -116,10 +116,11 @@ def test_gemm_rejects_bad_arguments(cuda):
         ck.gemm_w4a16(x[:8, :32].contiguous(), nib, sc, 128, 32)  # K % 64 != 0
 
 
-@pytest.mark.parametrize("M", [1, 5, 64, 130])
+@pytest.mark.parametrize("M", [1, 5, 64, 100, 130, 300])
 @pytest.mark.parametrize("with_awq", [False, True])
 def test_matmul_x_matches_q4_linear(cuda, orc, M, with_awq):
-    """gpu_layer.matmul_x (the batch > 1 call site: GEMV at M == 1, the tcgen05 GEMM walked in 64-row slices above)
+    """gpu_layer.matmul_x (the batch > 1 call site: GEMV at M == 1, the fused GEMM walked in 64-row slices up to
+    128 rows, dequantisation + dense GEMM above)
     against the reference's CPU semantics q4_linear on the same 16-bit activations."""
     from nve_b200.gpu_layer import GpuW4, matmul_x
 
@@ -135,6 +136,25 @@ def test_matmul_x_matches_q4_linear(cuda, orc, M, with_awq):
     assert tuple(y.shape) == (M, N)
     ref = orc.q4_linear(blocks, orc.from_act16(X16), awq_inv=awq)
     assert rel_rms_err(y.float().cpu().numpy(), ref) < TOL
+
+
+def test_matmul_x_dense_route_bf16(cuda, orc):
+    """Above 128 rows matmul_x dequantises to f16 and calls the dense GEMM; bf16 activations are converted to f16
+    for it and the result is rounded to bf16 once (judged on the f32 reference within bf16's own rounding)."""
+    from nve_b200.gpu_layer import DENSE_ROWS, GpuW4, matmul_x
+
+    torch = cuda
+    M, N, K = DENSE_ROWS + 72, 512, 1024
+    nib, sc, X16, ref = _case(orc, M, N, K, 977, True)
+    w = GpuW4(dev(nib), dev(sc), None, N, K)
+    y = matmul_x(dev(X16, torch.bfloat16), w)
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N)
+    yf = y.float().cpu().numpy().astype(np.float64)
+    rms = np.sqrt(np.mean(ref * ref))
+    assert np.all(np.abs(yf - ref) <= np.abs(ref) * 2.0 ** -8 + 3e-3 * rms)  # half a bf16 ulp + the f16 GEMM's tolerance
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    assert matmul_x(dev(X16, torch.bfloat16), w, out=out) is out
+    assert torch.equal(out, y)
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tc"])

@@ -518,11 +518,12 @@ def test_rms_norm_rows_and_kv_rows_write(cuda, orc):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(32, 8, 128), (8, 8, 64), (12, 4, 64)])
 def test_attn_prefill_causal_rows_equal_decode_calls(cuda, orc, nh, nkv, hd):
-    """Every row of the one-launch causal attention equals a flash-decode call of that row's length, bit for bit."""
+    """Every row of the one-launch causal attention equals a flash-decode call of that row's length, bit for bit
+    (blocks of fewer than 64 (row, KV head) pairs, which run the decode kernel)."""
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    S, start, max_seq = 9, 37, 64
+    S, start, max_seq = 7, 37, 64
     q = dev(orc.to_act16(orc.fill_normal(S * nh * hd, 821, 1)), torch.float16).view(S, nh * hd)
     kc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 821, 2)), torch.float16).view(nkv, max_seq, hd)
     vc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 821, 3)), torch.float16).view(nkv, max_seq, hd)
@@ -534,6 +535,28 @@ def test_attn_prefill_causal_rows_equal_decode_calls(cuda, orc, nh, nkv, hd):
         ck.flash_decode_dyn_into(q[r].contiguous(), kc, vc, want, nh, nkv, d_len.data_ptr(), hd, hd ** -0.5, max_seq)
         torch.cuda.synchronize()
         assert torch.equal(got[r], want), f"row {r}"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,S,start,max_seq", [(32, 8, 128, 40, 21, 64), (8, 8, 64, 130, 0, 160), (12, 4, 64, 33, 300, 333),
+                                                       (8, 1, 128, 64, 5, 80)])
+def test_attn_prefill_causal_large_blocks_match_decode_calls(cuda, orc, nh, nkv, hd, S, start, max_seq):
+    """Blocks of 64 or more (row, KV head) pairs run the tensor-core kernel: every row within rounding of the
+    flash-decode call of that row's length (f16 probabilities and a different summation order)."""
+    from nve_b200 import cuda_kernels as ck
+
+    torch = cuda
+    q = dev(orc.to_act16(orc.fill_normal(S * nh * hd, 841, 1)), torch.float16).view(S, nh * hd)
+    kc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 841, 2)), torch.float16).view(nkv, max_seq, hd)
+    vc = dev(orc.to_act16(orc.fill_normal(nkv * max_seq * hd, 841, 3)), torch.float16).view(nkv, max_seq, hd)
+    got = ck.attn_prefill_causal(q, kc, vc, start, nh, nkv, hd, max_seq, hd ** -0.5)
+    d_len = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = torch.empty((S, nh * hd), dtype=torch.float16, device="cuda")
+    for r in range(S):
+        d_len.fill_(start + r + 1)
+        ck.flash_decode_dyn_into(q[r].contiguous(), kc, vc, want[r], nh, nkv, d_len.data_ptr(), hd, hd ** -0.5, max_seq)
+        torch.cuda.synchronize()
+    err = (got.float() - want.float()).abs().max().item()
+    assert err < 5e-3 * max(1.0, want.float().abs().max().item()), err
 
 
 def test_prefill_layers_match_sequential_decode(cuda, orc):
