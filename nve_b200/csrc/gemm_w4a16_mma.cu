@@ -181,31 +181,28 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemm_w4a16_mma_kernel(const Ge
                 const DequantScale s0 = make_dequant_scale(ws[d][0]), s1 = make_dequant_scale(ws[d][1]);
                 const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&wq[d][0]);
                 const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&wq[d][1]);
-                uint32_t a[8][4];  // MMA 2w: elements 4w..4w+3 of the group, MMA 2w+1: elements 16+4w..16+4w+3
-#pragma unroll
-                for (int w = 0; w < 4; w++) {
-                    dequant_word(w0[w], s0, dc, a[2 * w][0], a[2 * w][2], a[2 * w + 1][0], a[2 * w + 1][2]);
-                    dequant_word(w1[w], s1, dc, a[2 * w][1], a[2 * w][3], a[2 * w + 1][1], a[2 * w + 1][3]);
-                }
-                // the MMAs of one word go to the two accumulator chains of every batch group in turn, so that
-                // consecutive instructions do not wait for each other's result
                 uint4 xq[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                     for (int q = 0; q < 4; q++) xq[nt][q] = *reinterpret_cast<const uint4*>(xs + ((nt * 4 + q) * 32) * 16);
+                // word w of the two rows -> MMA 2w (elements 4w..4w+3 of the group) and MMA 2w+1 (16+4w..16+4w+3);
+                // the two go to different accumulator chains, so consecutive instructions do not wait for each other
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
+                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                    dequant_word(w0[w], s0, dc, a0, a2, b0, b2);
+                    dequant_word(w1[w], s1, dc, a1, a3, b1, b3);
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
                         const uint4& lo = xq[nt][w >> 1];       // elements 8 (w/2) .. +7 hold 4w .. 4w+3
                         const uint4& hi = xq[nt][2 + (w >> 1)];  // and 16 + 4w .. 16 + 4w+3
                         if ((w & 1) == 0) {
-                            mma_f16_m16n8k16(acc[nt][0], a[2 * w][0], a[2 * w][1], a[2 * w][2], a[2 * w][3], lo.x, lo.y);
-                            mma_f16_m16n8k16(acc[nt][C - 1], a[2 * w + 1][0], a[2 * w + 1][1], a[2 * w + 1][2], a[2 * w + 1][3], hi.x, hi.y);
+                            mma_f16_m16n8k16(acc[nt][0], a0, a1, a2, a3, lo.x, lo.y);
+                            mma_f16_m16n8k16(acc[nt][C - 1], b0, b1, b2, b3, hi.x, hi.y);
                         } else {
-                            mma_f16_m16n8k16(acc[nt][0], a[2 * w][0], a[2 * w][1], a[2 * w][2], a[2 * w][3], lo.z, lo.w);
-                            mma_f16_m16n8k16(acc[nt][C - 1], a[2 * w + 1][0], a[2 * w + 1][1], a[2 * w + 1][2], a[2 * w + 1][3], hi.z, hi.w);
+                            mma_f16_m16n8k16(acc[nt][0], a0, a1, a2, a3, lo.z, lo.w);
+                            mma_f16_m16n8k16(acc[nt][C - 1], b0, b1, b2, b3, hi.z, hi.w);
                         }
                     }
                 }
