@@ -117,6 +117,7 @@ SIGNATURES = {
     "nve_b200_version": (C.c_char_p, []),
     "nve_b200_launch_count": (_ULL, []),
     "nve_b200_set_pdl": (_I, [_I]),
+    "nve_b200_set_attn_decode_kernel": (_I, [_I]),
     "nve_b200_quantize_q8": (_I, [_P, _P, _P, _I, _I, _P]),
     "nve_b200_quantize_q8_awq": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "nve_b200_rmsnorm_quantize_q8": (_I, [_P, _P, _P, _P, _P, _I, _F, _I, _P]),

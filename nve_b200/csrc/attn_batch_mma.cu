@@ -21,42 +21,16 @@
 // Eight warps take the 16-position tiles of the sequence round-robin, each with a private online-softmax state;
 // their partials meet in shared memory at the end.  16 warps per SM x 8 KB of rows in flight per warp tile keep HBM
 // busy without software pipelining.
-#include "attn_core.cuh"
+#include "attn_mma.cuh"
 #include "attn_params.cuh"
 
 namespace nve {
 
-constexpr int kAmThreads = 256;
-constexpr int kAmWarps = kAmThreads / 32;
-
-template <int HD, int G> struct AmShared {
-    float q_s[G][HD];
-    __align__(16) uint16_t knew_s[HD];
-    __align__(16) uint16_t vnew_s[HD];
-    float wm[kAmWarps][G], wl[kAmWarps][G];
-    float wo[kAmWarps][G][HD];
-};
-
-__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 template <int HD, int G, bool FUSED>
 __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const AttnParams pin) {
     constexpr int DC = HD / 8;        // 16-byte chunks per row
-    constexpr int DPT = HD / 4;       // dims of a K row per lane
-    constexpr int KQ = DPT / 8;       // 128-bit loads per K row and lane
     constexpr int NT = HD / 8;        // output dim tiles = dims of a V row per lane
-    constexpr int VQ = NT / 8;        // 128-bit loads per V row and lane
-    constexpr int KK = HD / 16;       // MMAs per score tile
-    static_assert(VQ >= 1 && KQ >= 1 && G >= 1 && G <= 8, "head_dim 64 or 128, up to 8 query heads per KV head");
+    static_assert((HD == 64 || HD == 128) && G >= 1 && G <= 8, "head_dim 64 or 128, up to 8 query heads per KV head");
     AttnParams p = pin;
     if constexpr (FUSED) {
         const long long b = blockIdx.y;
@@ -103,21 +77,8 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
     }
     __syncthreads();
 
-    // q fragments (rows g < G are heads, the other rows are zero)
-    uint32_t qa[KK][4];
-#pragma unroll
-    for (int kk = 0; kk < KK; kk++) {
-        qa[kk][1] = 0;
-        qa[kk][3] = 0;
-        if (g < G) {
-            const float* qp = &sh.q_s[g][DPT * t + 4 * kk];
-            qa[kk][0] = pack_f16x2(qp[0], qp[1]);  // exact: q_s holds f16-rounded values
-            qa[kk][2] = pack_f16x2(qp[2], qp[3]);
-        } else {
-            qa[kk][0] = 0;
-            qa[kk][2] = 0;
-        }
-    }
+    uint32_t qa[HD / 16][4];
+    am_q_fragments<HD, G>(sh, g, t, qa);
 
     float m = -1e30f, l = 0.0f;  // running maximum (equal on the four lanes of a row) and this lane's share of the sum
     float o[NT][4];
@@ -125,99 +86,18 @@ __global__ void __launch_bounds__(kAmThreads, 2) attn_batch_mma_kernel(const Att
     for (int j = 0; j < NT; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
 
     for (int p0 = warp * 16; p0 < seq_len; p0 += kAmWarps * 16) {
-        const int last = seq_len - 1;
-        // ---- loads of the tile: K rows p0 + g, p0 + 8 + g; V rows p0 + {2t, 2t+1, 2t+8, 2t+9}
-        uint4 kr[2][KQ], vr[4][VQ];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const uint16_t* row = kh + static_cast<long long>(min(p0 + 8 * r + g, last)) * HD + DPT * t;
-#pragma unroll
-            for (int i = 0; i < KQ; i++) kr[r][i] = *reinterpret_cast<const uint4*>(row + 8 * i);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int pr = p0 + 2 * t + (r & 1) + 8 * (r >> 1);
-            const uint16_t* row = vh + static_cast<long long>(min(pr, last)) * HD + NT * g;
-#pragma unroll
-            for (int i = 0; i < VQ; i++) vr[r][i] = *reinterpret_cast<const uint4*>(row + 8 * i);
-        }
-        // ---- scores of the two 8-position halves
-        float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
-#pragma unroll
-        for (int kk = 0; kk < KK; kk++) {
-            const uint32_t* k0 = reinterpret_cast<const uint32_t*>(&kr[0][0]);
-            const uint32_t* k1 = reinterpret_cast<const uint32_t*>(&kr[1][0]);
-            mma_f16_16816(s0, qa[kk], k0[2 * kk], k0[2 * kk + 1]);
-            mma_f16_16816(s1, qa[kk], k1[2 * kk], k1[2 * kk + 1]);
-        }
-        // this lane's four scores of row g: positions p0 + 2t, +1 (s0[0], s0[1]) and p0 + 8 + 2t, +1 (s1[0], s1[1])
-        float sc[4];
-        sc[0] = p0 + 2 * t < seq_len ? s0[0] * p.scale : -1e30f;
-        sc[1] = p0 + 2 * t + 1 < seq_len ? s0[1] * p.scale : -1e30f;
-        sc[2] = p0 + 8 + 2 * t < seq_len ? s1[0] * p.scale : -1e30f;
-        sc[3] = p0 + 9 + 2 * t < seq_len ? s1[1] * p.scale : -1e30f;
-        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m, mx);
-        const float corr = __expf(m - m_new);
-        float pe[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) pe[i] = sc[i] > -1e29f ? __expf(sc[i] - m_new) : 0.0f;
-        l = l * corr + ((pe[0] + pe[1]) + (pe[2] + pe[3]));
-        m = m_new;
-#pragma unroll
-        for (int j = 0; j < NT; j++) {
-            o[j][0] *= corr;
-            o[j][1] *= corr;
-        }
-        // ---- outputs: p (f16) . V
-        uint32_t pa[4];
-        pa[0] = pack_f16x2(pe[0], pe[1]);
-        pa[1] = 0;
-        pa[2] = pack_f16x2(pe[2], pe[3]);
-        pa[3] = 0;
-        const uint32_t* v0 = reinterpret_cast<const uint32_t*>(&vr[0][0]);  // row p0 + 2t
-        const uint32_t* v1 = reinterpret_cast<const uint32_t*>(&vr[1][0]);  // row p0 + 2t + 1
-        const uint32_t* v2 = reinterpret_cast<const uint32_t*>(&vr[2][0]);  // row p0 + 8 + 2t
-        const uint32_t* v3 = reinterpret_cast<const uint32_t*>(&vr[3][0]);  // row p0 + 9 + 2t
-#pragma unroll
-        for (int j = 0; j < NT; j++) {
-            // dim NT*g + j of the four rows: register j / 2, lower or upper half
-            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            const uint32_t b0 = __byte_perm(v0[j >> 1], v1[j >> 1], sel);
-            const uint32_t b1 = __byte_perm(v2[j >> 1], v3[j >> 1], sel);
-            mma_f16_16816(o[j], pa, b0, b1);
-        }
+        uint4 kr[2][HD / 32], vr[4][HD / 64];
+        am_load_tile<HD>(kh, vh, p0, seq_len - 1, g, t, kr, vr);
+        am_tile<HD>(qa, kr, vr, p0, seq_len, p.scale, t, m, l, o);
     }
 
-    // ---- the warps' partials meet in shared memory: lane (g < G, t) holds head g, dims NT*(2t) + j and NT*(2t+1) + j
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (g < G) {
-        if (t == 0) {
-            sh.wm[warp][g] = m;
-            sh.wl[warp][g] = l;
-        }
-#pragma unroll
-        for (int j = 0; j < NT; j++) {
-            sh.wo[warp][g][NT * (2 * t) + j] = o[j][0];
-            sh.wo[warp][g][NT * (2 * t + 1) + j] = o[j][1];
-        }
-    }
+    // ---- the warps' partials meet in shared memory
+    am_store_warp_partial<HD, G>(sh, warp, g, t, m, l, o);
     __syncthreads();
     for (int i = tid; i < G * HD; i += kAmThreads) {
         const int h = i / HD, d = i % HD;
-        float mm = -1e30f;
-#pragma unroll
-        for (int w = 0; w < kAmWarps; w++) mm = fmaxf(mm, sh.wm[w][h]);
-        float ss = 0.0f, a = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kAmWarps; w++) {
-            const float c = __expf(sh.wm[w][h] - mm);
-            ss = fmaf(sh.wl[w][h], c, ss);
-            a = fmaf(sh.wo[w][h][d], c, a);
-        }
+        float mm, ss, a;
+        am_merge_warps<HD, G>(sh, h, d, mm, ss, a);
         const float inv = ss > 0.0f ? 1.0f / ss : 0.0f;
         p.out[static_cast<long long>(h0 + h) * HD + d] = Act16<NVE_DT_F16>::from_f32(a * inv);
     }

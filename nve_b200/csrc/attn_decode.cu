@@ -19,6 +19,8 @@
 //     instead of the cache, and one CTA per KV head writes them to the cache.
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "attn_core.cuh"
 #include "attn_params.cuh"
 
@@ -229,6 +231,8 @@ bool attn_decode_try(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, 
     return true;
 }
 
+static std::atomic<int> g_attn_decode_kernel{0};
+
 }  // namespace nve
 
 using namespace nve;
@@ -251,9 +255,22 @@ extern "C" int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_n
     p.out = out; p.out_q = out_q; p.out_scales = out_scales;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.kv_stride = max_seq_len; p.scale = scale;
     cudaError_t e = cudaSuccess;
+    if (g_attn_decode_kernel.load(std::memory_order_relaxed) == 0 && aligned(q, 16) && aligned(k_new, 16) && aligned(v_new, 16) &&
+        attn_decode_mma_try(p, head_dim, static_cast<cudaStream_t>(stream), e)) {
+        count_launch();
+        return set_cuda_status(e);
+    }
     if (!attn_decode_dispatch<true>(p, head_dim, static_cast<cudaStream_t>(stream), e)) return set_status(NVE_ERR_BAD_SHAPE);
     count_launch();
     return set_cuda_status(e);
+}
+
+/* Which kernel nve_b200_attn_decode_fused launches: 0 (default) = the tensor-core kernel where it covers the shape
+ * (head_dim 64 / 128, 1, 2 or 4 query heads per KV head), 1 = always the CUDA-core kernel, whose output equals the
+ * un-fused sequence RoPE -> K/V write -> nve_flash_decode_f16 bit for bit.  Process-wide; a captured graph keeps the
+ * kernel it was recorded with.  Returns the previous setting. */
+extern "C" int nve_b200_set_attn_decode_kernel(int mode) {
+    return g_attn_decode_kernel.exchange(mode == 1 ? 1 : 0, std::memory_order_relaxed);
 }
 
 /* Causal attention of a block of S new positions against the cache (which already holds them): row r of q

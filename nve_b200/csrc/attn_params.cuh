@@ -31,4 +31,8 @@ struct AttnParams {
 // independent sequences with RoPE and the K/V write inside; else the un-fused causal block described above.
 bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err, bool fused = true);
 
+// attn_decode_mma.cu: the fused decode attention of one sequence on the tensor cores; false when the shape is not
+// covered.
+bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err);
+
 }  // namespace nve

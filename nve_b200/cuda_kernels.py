@@ -12,6 +12,7 @@ Differences from the Rust wrappers, all on the host side:
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import threading
 from typing import Optional, Sequence, Tuple
@@ -346,6 +347,22 @@ def launch_count() -> int:
 
 def set_pdl(enabled: bool) -> bool:
     return bool(_lib().nve_b200_set_pdl(int(enabled)))
+
+
+def set_attn_decode_kernel(cuda_core: bool) -> bool:
+    """Which kernel attn_decode_fused launches: the tensor-core kernel (default) or, with cuda_core=True, the CUDA-core
+    kernel whose results equal the un-fused launch sequence bit for bit.  Returns the previous setting."""
+    return bool(_lib().nve_b200_set_attn_decode_kernel(1 if cuda_core else 0))
+
+
+@contextlib.contextmanager
+def attn_decode_kernel(cuda_core: bool):
+    """`with attn_decode_kernel(True): ...` runs (or captures) the block with the CUDA-core decode attention."""
+    prev = set_attn_decode_kernel(cuda_core)
+    try:
+        yield
+    finally:
+        set_attn_decode_kernel(prev)
 
 
 def quantize_q8(x: Tensor) -> Tuple[Tensor, Tensor]:

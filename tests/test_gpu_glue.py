@@ -206,9 +206,13 @@ def test_flash_decode(cuda, orc, nh, nkv, hd, seq):
     assert torch.equal(out2, out)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,pos", [(32, 8, 64, 0), (32, 8, 128, 100), (64, 8, 128, 1023), (8, 8, 64, 5), (6, 2, 128, 40)])
+@pytest.mark.parametrize("nh,nkv,hd,pos", [(32, 8, 64, 0), (32, 8, 128, 100), (64, 8, 128, 1023), (8, 8, 64, 5), (6, 2, 128, 40),
+                                           (32, 8, 128, 1023), (32, 8, 128, 127), (32, 8, 128, 128), (16, 8, 64, 129),
+                                           (8, 2, 128, 7), (4, 4, 128, 1000), (32, 8, 128, 15), (32, 8, 128, 16)])
 def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
-    """RoPE + KV write + attention + quantise in one launch == the four separate launches, bit for bit."""
+    """RoPE + KV write + attention + quantise in one launch against the four separate launches: bit for bit with
+    the CUDA-core kernel; with the default tensor-core kernel the cache rows bit for bit, the output within
+    rounding (f16 probabilities, another summation order) and the int8 codes equal to the quantiser's on that output."""
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
@@ -229,15 +233,29 @@ def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
     out1 = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
     ck.flash_decode_dyn_into(q1, kc1, vc1, out1, nh, nkv, d_len.data_ptr(), hd, scale, max_seq)
     xq1, xs1 = ck.quantize_f16_q8(out1)
-    # one launch
+    # one launch, CUDA-core kernel
     kc2, vc2 = kc.clone(), vc.clone()
     out2 = torch.empty_like(out1)
     xq2 = torch.empty(nh * hd, dtype=torch.int8, device="cuda")
     xs2 = torch.empty(nh * hd // 32, dtype=torch.float32, device="cuda")
-    ck.attn_decode_fused(q, k, v, kc2, vc2, dc, ds, d_pos.data_ptr(), d_len.data_ptr(), out2, nh, nkv, hd, max_seq, scale,
-                         out_q=xq2, out_scales=xs2)
+    with ck.attn_decode_kernel(cuda_core=True):
+        ck.attn_decode_fused(q, k, v, kc2, vc2, dc, ds, d_pos.data_ptr(), d_len.data_ptr(), out2, nh, nkv, hd, max_seq, scale,
+                             out_q=xq2, out_scales=xs2)
     assert torch.equal(out2, out1) and torch.equal(kc2, kc1) and torch.equal(vc2, vc1)
     assert torch.equal(xq2, xq1) and torch.equal(xs2, xs1)
+    # one launch, default kernel (tensor cores where the shape is covered)
+    kc3, vc3 = kc.clone(), vc.clone()
+    out3 = torch.empty_like(out1)
+    xq3, xs3 = torch.empty_like(xq2), torch.empty_like(xs2)
+    ck.attn_decode_fused(q, k, v, kc3, vc3, dc, ds, d_pos.data_ptr(), d_len.data_ptr(), out3, nh, nkv, hd, max_seq, scale,
+                         out_q=xq3, out_scales=xs3)
+    assert torch.equal(kc3, kc1) and torch.equal(vc3, vc1)
+    assert (out3.float() - out1.float()).abs().max().item() < 5e-3 * max(1.0, out1.float().abs().max().item())
+    xq3w, xs3w = ck.quantize_f16_q8(out3)
+    assert torch.equal(xq3, xq3w) and torch.equal(xs3, xs3w)
+    out4 = torch.empty_like(out1)  # without the quantised output
+    ck.attn_decode_fused(q, k, v, kc.clone(), vc.clone(), dc, ds, d_pos.data_ptr(), d_len.data_ptr(), out4, nh, nkv, hd, max_seq, scale)
+    assert torch.equal(out4, out3)
     # and against the oracle
     ref = orc.attn_decode(orc.from_act16(f16_bits(q1)).reshape(nh, hd), kc1.float().cpu().numpy(), vc1.float().cpu().numpy(),
                           pos + 1, scale)
@@ -326,7 +344,11 @@ def _oracle_layer(orc, h16, w, kc_f32, vc_f32, pos, nh, nkv, hd, cos16, sin16, u
 
 
 @pytest.mark.parametrize("use_w4a8", [True, False])
-def test_decode_layer_fused_equals_reference_sequence_and_oracle(cuda, orc, use_w4a8):
+@pytest.mark.parametrize("cuda_core_attention", [True, False])
+def test_decode_layer_fused_equals_reference_sequence_and_oracle(cuda, orc, use_w4a8, cuda_core_attention):
+    """The fused schedule against the reference's kernel sequence: bit for bit with the CUDA-core attention kernel,
+    within rounding with the default tensor-core one; both within tolerance of a host oracle layer."""
+    from nve_b200 import cuda_kernels as ck
     from nve_b200.gpu_layer import gpu_layer_forward_decode
 
     torch = cuda
@@ -341,8 +363,12 @@ def test_decode_layer_fused_equals_reference_sequence_and_oracle(cuda, orc, use_
     hs = [dev(h16, torch.float16).view(1, -1) for _ in states]
     h_or = h16
     for pos in range(3):
-        outs = [gpu_layer_forward_decode(h, 0, st, pos, False, importance) for h, st in zip(hs, states)]
-        assert torch.equal(outs[0], outs[1])  # fused schedule == the reference's kernel sequence, bit for bit
+        with ck.attn_decode_kernel(cuda_core=cuda_core_attention):
+            outs = [gpu_layer_forward_decode(h, 0, st, pos, False, importance) for h, st in zip(hs, states)]
+        if cuda_core_attention:
+            assert torch.equal(outs[0], outs[1])  # fused schedule == the reference's kernel sequence, bit for bit
+        else:
+            assert rel_rms_err(outs[0].float().cpu().numpy(), outs[1].float().cpu().numpy()) < 5e-3
         h_or = _oracle_layer(orc, h_or, states[0].layer_weights[0], kc, vc, pos, nh, nkv, hd, cos16, sin16, use_w4a8)
         assert rel_rms_err(outs[0].float().cpu().numpy(), orc.from_act16(h_or)) < TOL
         hs = outs
@@ -621,9 +647,10 @@ def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc):
     for b in range(B):
         kc_s, vc_s = kc[b].clone(), vc[b].clone()
         want = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
-        ck.attn_decode_fused(q[b].view(nh, hd).contiguous(), k[b].view(nkv, hd).contiguous(), v[b].view(nkv, hd).contiguous(),
-                             kc_s, vc_s, cos, sin, d_pos[b:b + 1].data_ptr(), d_len[b:b + 1].data_ptr(), want, nh, nkv, hd,
-                             max_seq, hd ** -0.5)
+        with ck.attn_decode_kernel(cuda_core=True):  # the batched launch of few sequences is the CUDA-core kernel
+            ck.attn_decode_fused(q[b].view(nh, hd).contiguous(), k[b].view(nkv, hd).contiguous(), v[b].view(nkv, hd).contiguous(),
+                                 kc_s, vc_s, cos, sin, d_pos[b:b + 1].data_ptr(), d_len[b:b + 1].data_ptr(), want, nh, nkv, hd,
+                                 max_seq, hd ** -0.5)
         torch.cuda.synchronize()
         assert torch.equal(got[b].view(nh, hd), want), f"sequence {b}"
         assert torch.equal(kc_b[b], kc_s) and torch.equal(vc_b[b], vc_s), f"cache of sequence {b}"
