@@ -8,11 +8,15 @@
 // them, and a tile is eight score MMAs and HD/8 output MMAs (attn_mma.cuh).  The first tile of every warp is loaded
 // before the grid dependency resolves (the cache rows of earlier positions do not depend on the producer kernel);
 // the row of the new token is taken from shared memory instead of the cache.  The eight warps' partials meet in
-// shared memory, every CTA pushes its partial into rank 0's shared memory with distributed-shared-memory stores and
-// arrives on the cluster barrier, rank 0 merges, normalises, stores and quantises -- the tail of attn_decode.cu.
+// shared memory; the CTAs of ranks 1..7 post their partial into rank 0's shared memory with asynchronous
+// distributed-shared-memory stores that count their bytes on an mbarrier of rank 0 (st.async ... complete_tx) and
+// leave; rank 0 waits for the bytes (bounded in time; an expired wait writes NaN so that the failure is visible),
+// merges, normalises, stores and quantises.
 // Probabilities are rounded to f16 for the second MMA and sums run in a different order, so results agree with the
 // CUDA-core kernel within rounding, not bit for bit.
 #include <cooperative_groups.h>
+
+#include <cstddef>
 
 #include "attn_mma.cuh"
 #include "attn_params.cuh"
@@ -32,20 +36,42 @@ template <int HD, int G> struct AdmShared {
     float wo[kAmWarps][G][am_wo_row(HD)];
 };
 
+__device__ __forceinline__ uint32_t adm_smem_addr(const void* ptr) { return static_cast<uint32_t>(__cvta_generic_to_shared(ptr)); }
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t adm_map_rank(uint32_t cta_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+    return r;
+}
+// posted 4-byte store into another CTA's shared memory that counts its bytes on that CTA's mbarrier when it lands
+__device__ __forceinline__ void adm_st_async(uint32_t cluster_addr, float v, uint32_t cluster_mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+                 "r"(__float_as_uint(v)), "r"(cluster_mbar)
+                 : "memory");
+}
+constexpr unsigned long long kAdmWaitLimitNs = 20ull * 1000 * 1000;  // a legitimate wait lasts a microsecond
+
 template <int HD, int G>
 __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const AttnParams p) {
     constexpr int DC = HD / 8;
     constexpr int NT = HD / 8;
     static_assert((HD == 64 || HD == 128) && G >= 1 && G <= 4, "head_dim 64 or 128, up to 4 query heads per KV head");
     cg::cluster_group cluster = cg::this_cluster();
-    // phase 1 of the cluster barrier: every CTA announces that it runs, so that the pushes into rank 0's shared memory
-    // never touch a CTA that has not started (matched by the wait in front of the push)
-    cluster.barrier_arrive();
-
     constexpr int HALF = HD / 2, DPT = HD / 4;
     static_assert(G * HALF <= kAmThreads && HD <= kAmThreads, "one element of q, k and v per thread");
     __shared__ AdmShared<HD, G> sh;
     __shared__ AdCtaPartial<HD, G> parts[kAdRanks];  // only rank 0's copy is used
+    __shared__ __align__(8) unsigned long long pbar;  // rank 0: counts the bytes of the other ranks' partials
+    constexpr uint32_t kPartBytes = (G * HD + 2 * G) * 4;
+    if (cluster.block_rank() == 0 && threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(adm_smem_addr(&pbar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(adm_smem_addr(&pbar)), "r"((kAdRanks - 1) * kPartBytes)
+                     : "memory");
+    }
+    // The cluster barrier: every CTA announces that it runs (and rank 0 that its mbarrier is set up), so that the
+    // pushes into rank 0's shared memory never touch a CTA that has not started (matched by the wait in front of the push)
+    cluster.barrier_arrive();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -149,23 +175,54 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
     // ---- level 1: the warps' partials meet in shared memory; level 2: every CTA's partial goes to rank 0
     am_store_warp_partial<HD, G>(sh, warp, g, t, m, l, o);
     __syncthreads();
-    cluster.barrier_wait();  // phase 1: all CTAs of the cluster run
-    AdCtaPartial<HD, G>* dst = cluster.map_shared_rank(&parts[rank], 0);
+    cluster.barrier_wait();  // all CTAs of the cluster run
+    // Ranks 1..7 post their partial into rank 0's parts[rank] with asynchronous stores that count their bytes on rank
+    // 0's mbarrier, and leave: no second cluster barrier, rank 0 waits for the bytes only.
+    using Part = AdCtaPartial<HD, G>;
+    const uint32_t remote = adm_map_rank(adm_smem_addr(&parts[rank]), 0);
+    const uint32_t remote_bar = adm_map_rank(adm_smem_addr(&pbar), 0);
 #pragma unroll
     for (int i = tid; i < G * HD; i += kAmThreads) {
         const int h = i / HD, d = i % HD;
         float mm, ss, a;
         am_merge_warps<HD, G>(sh, h, d, mm, ss, a);
-        dst->acc[h][d] = a;
-        if (d == 0) {
-            dst->m[h] = mm;
-            dst->s[h] = ss;
+        if (rank == 0) {
+            parts[0].acc[h][d] = a;
+            if (d == 0) {
+                parts[0].m[h] = mm;
+                parts[0].s[h] = ss;
+            }
+        } else {
+            adm_st_async(remote + static_cast<uint32_t>(offsetof(Part, acc) + (h * HD + d) * 4), a, remote_bar);
+            if (d == 0) {
+                adm_st_async(remote + static_cast<uint32_t>(offsetof(Part, m) + h * 4), mm, remote_bar);
+                adm_st_async(remote + static_cast<uint32_t>(offsetof(Part, s) + h * 4), ss, remote_bar);
+            }
         }
     }
-    // phase 2: release the stores / acquire everybody's; only rank 0 has anything left to do
-    cluster.barrier_arrive();
     if (rank != 0) return;
-    cluster.barrier_wait();
+    __syncthreads();  // rank 0's own partial
+    bool arrived = false;
+    {
+        const uint32_t bar = adm_smem_addr(&pbar);
+        unsigned long long t0 = 0, tn = 0;
+        for (int spin = 0; !arrived; spin++) {
+            uint32_t done;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(bar)
+                : "memory");
+            arrived = done != 0;
+            if (!arrived && (spin & 63) == 63) {  // bounded in time: a partial that never arrives poisons the output below
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tn));
+                if (t0 == 0) t0 = tn;
+                else if (tn - t0 > kAdmWaitLimitNs) break;
+            }
+        }
+    }
 #pragma unroll
     for (int i = tid; i < G * HD; i += kAmThreads) {
         const int h = i / HD, d = i % HD;
@@ -182,7 +239,7 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
             ss = fmaf(parts[r].s[h], c, ss);
             a = fmaf(parts[r].acc[h][d], c, a);
         }
-        const uint16_t o16 = Act16<NVE_DT_F16>::from_f32(ss > 0.0f ? a / ss : 0.0f);
+        const uint16_t o16 = arrived ? Act16<NVE_DT_F16>::from_f32(ss > 0.0f ? a / ss : 0.0f) : static_cast<uint16_t>(0x7E00);  // NaN
         const long long oi = static_cast<long long>(h0 + h) * HD + d;
         p.out[oi] = o16;
         if (p.out_q != nullptr) {
