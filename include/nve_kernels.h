@@ -322,7 +322,7 @@ NVE_API int nve_b200_quantize_matvec_w4a8_allreduce(const void* x, int x_dtype, 
  * the output is also quantised to int8 per group of 32 (the call at src/gpu_layer.rs:739).  head_dim 64 or
  * 128.  The cache row written is bit-identical to the separate RoPE and KV-write launches.  The attention itself
  * runs on the tensor cores (a cluster of 8 CTAs per KV head, all its query heads as rows of mma.sync, f16
- * probabilities) when there are 1, 2 or 4 query heads per KV head and q / k_new / v_new are 16-byte aligned: equal
+ * probabilities) when there are 1, 2, 4 or 8 query heads per KV head and q / k_new / v_new are 16-byte aligned: equal
  * to nve_flash_decode_f16 within 5e-3 of the largest output.  nve_b200_set_attn_decode_kernel(1) selects the
  * CUDA-core kernel instead (also used for other shapes), whose output -- and int8 codes -- are bit-identical to the
  * separate RoPE, KV-write, flash-decode and quantise launches; 0 restores the default.  The setting is process-wide,

@@ -266,7 +266,7 @@ extern "C" int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_n
 }
 
 /* Which kernel nve_b200_attn_decode_fused launches: 0 (default) = the tensor-core kernel where it covers the shape
- * (head_dim 64 / 128, 1, 2 or 4 query heads per KV head), 1 = always the CUDA-core kernel, whose output equals the
+ * (head_dim 64 / 128, 1, 2, 4 or 8 query heads per KV head), 1 = always the CUDA-core kernel, whose output equals the
  * un-fused sequence RoPE -> K/V write -> nve_flash_decode_f16 bit for bit.  Process-wide; a captured graph keeps the
  * kernel it was recorded with.  Returns the previous setting. */
 extern "C" int nve_b200_set_attn_decode_kernel(int mode) {

@@ -51,17 +51,25 @@ __device__ __forceinline__ void adm_st_async(uint32_t cluster_addr, float v, uin
 }
 constexpr unsigned long long kAdmWaitLimitNs = 20ull * 1000 * 1000;  // a legitimate wait lasts a microsecond
 
+template <int HD, int G> struct AdmSmem {
+    AdmShared<HD, G> sh;
+    AdCtaPartial<HD, G> parts[kAdRanks];
+    __align__(8) unsigned long long pbar;
+};
+
 template <int HD, int G>
 __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const AttnParams p) {
     constexpr int DC = HD / 8;
     constexpr int NT = HD / 8;
-    static_assert((HD == 64 || HD == 128) && G >= 1 && G <= 4, "head_dim 64 or 128, up to 4 query heads per KV head");
+    static_assert((HD == 64 || HD == 128) && G >= 1 && G <= 8, "head_dim 64 or 128, up to 8 query heads per KV head");
     cg::cluster_group cluster = cg::this_cluster();
     constexpr int HALF = HD / 2, DPT = HD / 4;
-    static_assert(G * HALF <= kAmThreads && HD <= kAmThreads, "one element of q, k and v per thread");
-    __shared__ AdmShared<HD, G> sh;
-    __shared__ AdCtaPartial<HD, G> parts[kAdRanks];  // only rank 0's copy is used
-    __shared__ __align__(8) unsigned long long pbar;  // rank 0: counts the bytes of the other ranks' partials
+    static_assert(HD <= kAmThreads, "one element of k and v per thread");
+    extern __shared__ __align__(16) unsigned char adm_smem[];
+    AdmSmem<HD, G>& sm = *reinterpret_cast<AdmSmem<HD, G>*>(adm_smem);
+    AdmShared<HD, G>& sh = sm.sh;
+    AdCtaPartial<HD, G>* parts = sm.parts;  // only rank 0's copy is used
+    unsigned long long& pbar = sm.pbar;     // rank 0: counts the bytes of the other ranks' partials
     constexpr uint32_t kPartBytes = (G * HD + 2 * G) * 4;
     if (cluster.block_rank() == 0 && threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(adm_smem_addr(&pbar)));
@@ -93,7 +101,10 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
         if (p0 < pe) am_load_tile<HD>(kh, vh, p0, pe - 1, g, t, kr, vr);
     }
     // the RoPE row of the guessed position does not depend on the producer either; rows g >= G of the q fragments are zero
-    const int qe = tid % HALF, qh = tid / HALF;  // this thread's element pair (qe, qe + HALF) of head qh (qh < G) ...
+    // this thread's element pairs (qe, qe + HALF) of the heads qh, qh + HPP, ... (those below G) ...
+    constexpr int HPP = kAmThreads / HALF;        // heads covered by one pass of the CTA's threads
+    constexpr int QI = (G + HPP - 1) / HPP;       // passes
+    const int qe = tid % HALF, qh = tid / HALF;
     const bool spec_ok = pre_pos >= 0 && pre_pos < p.kv_stride;
     uint16_t c16 = p.cos_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
     uint16_t s16 = p.sin_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
@@ -101,9 +112,15 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
     pdl_wait();
     // one round trip: the position words are read again while q, k and v of the new token come in; everything that
     // was addressed with the guess is redone in the rare case that the words changed
-    const uint16_t* qp = p.q + static_cast<long long>(h0 + (qh < G ? qh : 0)) * HD;
     const uint16_t* kp = p.k_new + static_cast<long long>(kvh) * HD;
-    uint16_t x0 = qp[qe], x1 = qp[qe + HALF];
+    uint16_t x0[QI], x1[QI];
+#pragma unroll
+    for (int j = 0; j < QI; j++) {
+        const int h = qh + j * HPP;
+        const uint16_t* qp = p.q + static_cast<long long>(h0 + (h < G ? h : 0)) * HD;
+        x0[j] = qp[qe];
+        x1[j] = qp[qe + HALF];
+    }
     uint16_t k0 = 0, k1 = 0, vv = 0;
     if (tid < HALF) {  // ... and, for the first HALF threads, of the new k
         k0 = kp[qe];
@@ -128,12 +145,16 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
             r0 = Act16<NVE_DT_F16>::from_f32(__fsub_rn(__fmul_rn(f0, c), __fmul_rn(f1, sn)));
             r1 = Act16<NVE_DT_F16>::from_f32(__fadd_rn(__fmul_rn(f0, sn), __fmul_rn(f1, c)));
         };
-        if (qh < G) {
-            uint16_t r0, r1;
-            rot(x0, x1, r0, r1);
-            const int d0 = qe, d1 = qe + HALF;  // dim d -> lane quarter t = d / DPT, MMA kk = (d % DPT) / 4, slot d % 4
-            sh.qf[(d0 % DPT) / 4][(d0 / DPT) * 8 + qh][d0 % 4] = r0;
-            sh.qf[(d1 % DPT) / 4][(d1 / DPT) * 8 + qh][d1 % 4] = r1;
+#pragma unroll
+        for (int j = 0; j < QI; j++) {
+            const int h = qh + j * HPP;
+            if (h < G) {
+                uint16_t r0, r1;
+                rot(x0[j], x1[j], r0, r1);
+                const int d0 = qe, d1 = qe + HALF;  // dim d -> lane quarter t = d / DPT, MMA kk = (d % DPT) / 4, slot d % 4
+                sh.qf[(d0 % DPT) / 4][(d0 / DPT) * 8 + h][d0 % 4] = r0;
+                sh.qf[(d1 % DPT) / 4][(d1 / DPT) * 8 + h][d1 % 4] = r1;
+            }
         }
         if (tid < HALF) rot(k0, k1, sh.knew_s[qe], sh.knew_s[qe + HALF]);
         if (tid < HD) sh.vnew_s[tid] = vv;
@@ -253,7 +274,10 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
 }
 
 template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cudaStream_t st) {
+    constexpr int smem = static_cast<int>(sizeof(AdmSmem<HD, G>));
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_mma_kernel<HD, G>), smem) != NVE_OK) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
+    cfg.dynamicSmemBytes = smem;
     cfg.gridDim = dim3(p.num_kv_heads * kAdCluster);
     cfg.blockDim = dim3(kAmThreads);
     cfg.stream = st;
@@ -272,8 +296,8 @@ template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cuda
     return cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, G>, p);
 }
 
-// Fused decode attention of one sequence; false when the shape is not covered (more than 4 query heads per KV head,
-// other head sizes): the caller then uses the CUDA-core kernel.
+// Fused decode attention of one sequence; false when the shape is not covered (query heads per KV head other than
+// 1, 2, 4 or 8, other head sizes): the caller then uses the CUDA-core kernel.
 bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err) {
     const int groups = p.num_heads / p.num_kv_heads;
     if (head_dim == 128) {
@@ -281,6 +305,7 @@ bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cud
             case 1: err = launch_adm<128, 1>(p, st); return true;
             case 2: err = launch_adm<128, 2>(p, st); return true;
             case 4: err = launch_adm<128, 4>(p, st); return true;
+            case 8: err = launch_adm<128, 8>(p, st); return true;
             default: return false;
         }
     }
@@ -289,6 +314,7 @@ bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cud
             case 1: err = launch_adm<64, 1>(p, st); return true;
             case 2: err = launch_adm<64, 2>(p, st); return true;
             case 4: err = launch_adm<64, 4>(p, st); return true;
+            case 8: err = launch_adm<64, 8>(p, st); return true;
             default: return false;
         }
     }

@@ -208,7 +208,8 @@ def test_flash_decode(cuda, orc, nh, nkv, hd, seq):
 
 @pytest.mark.parametrize("nh,nkv,hd,pos", [(32, 8, 64, 0), (32, 8, 128, 100), (64, 8, 128, 1023), (8, 8, 64, 5), (6, 2, 128, 40),
                                            (32, 8, 128, 1023), (32, 8, 128, 127), (32, 8, 128, 128), (16, 8, 64, 129),
-                                           (8, 2, 128, 7), (4, 4, 128, 1000), (32, 8, 128, 15), (32, 8, 128, 16)])
+                                           (8, 2, 128, 7), (4, 4, 128, 1000), (32, 8, 128, 15), (32, 8, 128, 16),
+                                           (64, 8, 64, 50), (16, 2, 128, 300), (8, 1, 64, 1)])
 def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
     """RoPE + KV write + attention + quantise in one launch against the four separate launches: bit for bit with
     the CUDA-core kernel; with the default tensor-core kernel the cache rows bit for bit, the output within
