@@ -68,6 +68,9 @@ extern "C" {
     pub fn nve_b200_last_cuda_error() -> i32;
     pub fn nve_b200_launch_count() -> u64;
     pub fn nve_b200_set_pdl(enabled: i32) -> i32;
+    /// 0 = tensor-core decode attention where the shape is covered (default), 1 = the CUDA-core kernel whose output
+    /// equals the un-fused launch sequence bit for bit; returns the previous setting.
+    pub fn nve_b200_set_attn_decode_kernel(mode: i32) -> i32;
 
     pub fn nve_b200_quantize_q8(x: *const CVoid, xq: *mut i8, scales: *mut f32, k: i32, x_dtype: i32, stream: Stream) -> i32;
     pub fn nve_b200_quantize_q8_awq(x: *const CVoid, awq_inv: *const f32, xq: *mut i8, scales: *mut f32, k: i32,
