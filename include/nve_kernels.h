@@ -337,7 +337,8 @@ NVE_API int nve_b200_set_attn_decode_kernel(int mode);
  * [batch, nh*hd] and of k_new / v_new [batch, nkv*hd] belongs to sequence b, whose caches are k_cache / v_cache +
  * b * nkv * max_seq_len * hd, whose position is d_pos[b] and whose valid length is d_seq_len[b] (device arrays).
  * The cache row written is bit-identical to a single-sequence call.  Up to 63 (sequence, KV head) units the clustered
- * decode kernel runs with the sequence as second grid dimension and row b of out [batch, nh*hd] is bit-identical too;
+ * decode kernel that nve_b200_attn_decode_fused would launch (see nve_b200_set_attn_decode_kernel) runs with the
+ * sequence as second grid dimension and row b of out [batch, nh*hd] is bit-identical too;
  * from 64 units on (and 1, 2, 4 or 8 query heads per KV head) one CTA per unit streams all positions and computes
  * q.K^T and p.V with mma.sync (probabilities rounded to f16): rows then agree with the single-sequence call to about
  * 1e-3 of their RMS.  q / k_new / v_new and the caches 16-byte aligned. */

@@ -308,8 +308,9 @@ extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k
 
 /* nve_b200_attn_decode_fused for `batch` independent sequences in one launch: row b of q [batch, nh*hd] and of
  * k_new / v_new [batch, nkv*hd] belongs to sequence b, whose caches are k_cache / v_cache + b * nkv * max_seq_len * hd,
- * whose position is d_pos[b] and whose valid length is d_seq_len[b].  Small batches run the clustered kernel (row b
- * bit-identical to a single-sequence call), large ones the tensor-core kernel of attn_batch_mma.cu. */
+ * whose position is d_pos[b] and whose valid length is d_seq_len[b].  Small batches run the clustered kernel that
+ * nve_b200_attn_decode_fused would run (row b bit-identical to a single-sequence call under the same
+ * nve_b200_set_attn_decode_kernel setting), large ones the streaming tensor-core kernel of attn_batch_mma.cu. */
 extern "C" int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
                                                 uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
                                                 const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,
@@ -334,9 +335,14 @@ extern "C" int nve_b200_attn_decode_fused_batch(const uint16_t* q, const uint16_
     // enough (sequence, head pair) units to fill every SM twice: one CTA per unit over all positions, streaming;
     // otherwise the clustered kernel, which splits a sequence's positions over eight CTAs
     // one CTA per (sequence, KV head) on the tensor cores (attn_batch_mma.cu) from 64 such units on: measured at 8
-    // KV heads and context 1024, 8 sequences take 23 us there against 29 us on the clustered kernel, 64 sequences 63
-    // against 188; below that the clustered kernel, which splits a sequence's positions over eight CTAs, is faster
+    // KV heads and context 1024, 8 sequences take 21 us there against 23 us on the clustered tensor-core kernel (29 us
+    // on the CUDA-core one), 16 sequences 22 against 41, 64 sequences 63 against 188; below that the clustered
+    // kernels, which split a sequence's positions over eight CTAs, are faster (2 sequences 8.7 us, 4 sequences 13.4 us)
     if (static_cast<long long>(batch) * num_kv_heads >= 64 && attn_batch_mma_try(p, head_dim, cs, e)) {
+        count_launch();
+        return set_cuda_status(e);
+    }
+    if (g_attn_decode_kernel.load(std::memory_order_relaxed) == 0 && attn_decode_mma_try(p, head_dim, cs, e)) {
         count_launch();
         return set_cuda_status(e);
     }

@@ -57,8 +57,22 @@ template <int HD, int G> struct AdmSmem {
     __align__(8) unsigned long long pbar;
 };
 
+// With `rows` > 1 (batched decode) blockIdx.y selects one of several independent sequences: row b of q / k_new /
+// v_new / out, the b-th K/V cache and the b-th position and length words.
 template <int HD, int G>
-__global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const AttnParams pin) {
+    AttnParams p = pin;
+    if (p.rows > 1) {
+        const long long b = blockIdx.y;
+        p.q += b * (static_cast<long long>(p.num_heads) * HD);
+        p.out += b * (static_cast<long long>(p.num_heads) * HD);
+        p.k_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
+        p.v_new += b * (static_cast<long long>(p.num_kv_heads) * HD);
+        p.k_cache += b * p.cache_stride;
+        p.v_cache += b * p.cache_stride;
+        p.d_pos += b;
+        p.d_seq_len += b;
+    }
     constexpr int DC = HD / 8;
     constexpr int NT = HD / 8;
     static_assert((HD == 64 || HD == 128) && G >= 1 && G <= 8, "head_dim 64 or 128, up to 8 query heads per KV head");
@@ -278,7 +292,7 @@ template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cuda
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_mma_kernel<HD, G>), smem) != NVE_OK) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.dynamicSmemBytes = smem;
-    cfg.gridDim = dim3(p.num_kv_heads * kAdCluster);
+    cfg.gridDim = dim3(p.num_kv_heads * kAdCluster, p.rows > 1 ? p.rows : 1);
     cfg.blockDim = dim3(kAmThreads);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

@@ -626,9 +626,11 @@ def test_prefill_layers_match_sequential_decode(cuda, orc):
 
 
 # ------------------------------------------------------------------ batched decode: several sequences per step
-def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc):
+@pytest.mark.parametrize("cuda_core", [False, True])
+def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc, cuda_core):
     """Every row of the batched fused attention (RoPE + K/V write + attention) equals the single-sequence launch on
-    that sequence's cache, position and length, bit for bit -- output and the cache row written."""
+    that sequence's cache, position and length, bit for bit -- output and the cache row written -- with either
+    clustered kernel (few sequences run the kernel a single sequence would)."""
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
@@ -644,11 +646,12 @@ def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc):
     d_pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
     d_len = d_pos + 1
     kc_b, vc_b = kc.clone(), vc.clone()
-    got = ck.attn_decode_fused_batch(q, k, v, kc_b, vc_b, cos, sin, d_pos, d_len, nh, nkv, hd, max_seq, hd ** -0.5)
+    with ck.attn_decode_kernel(cuda_core=cuda_core):
+        got = ck.attn_decode_fused_batch(q, k, v, kc_b, vc_b, cos, sin, d_pos, d_len, nh, nkv, hd, max_seq, hd ** -0.5)
     for b in range(B):
         kc_s, vc_s = kc[b].clone(), vc[b].clone()
         want = torch.empty((nh, hd), dtype=torch.float16, device="cuda")
-        with ck.attn_decode_kernel(cuda_core=True):  # the batched launch of few sequences is the CUDA-core kernel
+        with ck.attn_decode_kernel(cuda_core=cuda_core):
             ck.attn_decode_fused(q[b].view(nh, hd).contiguous(), k[b].view(nkv, hd).contiguous(), v[b].view(nkv, hd).contiguous(),
                                  kc_s, vc_s, cos, sin, d_pos[b:b + 1].data_ptr(), d_len[b:b + 1].data_ptr(), want, nh, nkv, hd,
                                  max_seq, hd ** -0.5)
