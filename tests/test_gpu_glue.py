@@ -209,7 +209,9 @@ def test_flash_decode(cuda, orc, nh, nkv, hd, seq):
 @pytest.mark.parametrize("nh,nkv,hd,pos", [(32, 8, 64, 0), (32, 8, 128, 100), (64, 8, 128, 1023), (8, 8, 64, 5), (6, 2, 128, 40),
                                            (32, 8, 128, 1023), (32, 8, 128, 127), (32, 8, 128, 128), (16, 8, 64, 129),
                                            (8, 2, 128, 7), (4, 4, 128, 1000), (32, 8, 128, 15), (32, 8, 128, 16),
-                                           (64, 8, 64, 50), (16, 2, 128, 300), (8, 1, 64, 1)])
+                                           (64, 8, 64, 50), (16, 2, 128, 300), (8, 1, 64, 1),
+                                           # long contexts: several 16-position tiles per warp of the tensor-core kernel
+                                           (32, 8, 128, 4000), (16, 2, 64, 2500), (16, 2, 128, 3071)])
 def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
     """RoPE + KV write + attention + quantise in one launch against the four separate launches: bit for bit with
     the CUDA-core kernel; with the default tensor-core kernel the cache rows bit for bit, the output within
@@ -217,7 +219,7 @@ def test_fused_attention_equals_separate_launches(cuda, orc, nh, nkv, hd, pos):
     from nve_b200 import cuda_kernels as ck
 
     torch = cuda
-    max_seq = 1024
+    max_seq = 1024 if pos < 1024 else 4096
     c16, s16, dc, ds = _rope_tables(orc, torch, hd, max_seq)
     q = dev(orc.to_act16(orc.fill_normal(nh * hd, 75, 1)), torch.float16).view(nh, hd)
     k = dev(orc.to_act16(orc.fill_normal(nkv * hd, 75, 2)), torch.float16).view(nkv, hd)
