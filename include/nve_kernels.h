@@ -320,13 +320,15 @@ NVE_API int nve_b200_quantize_matvec_w4a8_allreduce(const void* x, int x_dtype, 
  * src/decode_graph.rs:247-283).  q [nh,hd] and k_new/v_new [nkv,hd] are read, not modified; caches are
  * [nkv, max_seq_len, hd]; tables [max_seq_len, hd/2]; out [nh,hd] f16.  When out_q / out_scales are given
  * the output is also quantised to int8 per group of 32 (the call at src/gpu_layer.rs:739).  head_dim 64 or
- * 128.  The cache row written is bit-identical to the separate RoPE and KV-write launches.  The attention itself
- * runs on the tensor cores (a cluster of 8 CTAs per KV head, all its query heads as rows of mma.sync, f16
- * probabilities) when there are 1, 2, 4 or 8 query heads per KV head and q / k_new / v_new are 16-byte aligned: equal
- * to nve_flash_decode_f16 within 5e-3 of the largest output.  nve_b200_set_attn_decode_kernel(1) selects the
- * CUDA-core kernel instead (also used for other shapes), whose output -- and int8 codes -- are bit-identical to the
- * separate RoPE, KV-write, flash-decode and quantise launches; 0 restores the default.  The setting is process-wide,
- * a captured graph keeps the kernel it was recorded with; the previous setting is returned. */
+ * 128.  Results -- cache row, output and int8 codes -- are bit-identical to the separate RoPE, KV-write,
+ * flash-decode and quantise launches of this library.
+ * Two attention kernels exist and nve_flash_decode_f16 / _dyn, nve_b200_attn_prefill_causal (small blocks) and this
+ * entry point always run the same one: by default a tensor-core kernel (a cluster of 8 CTAs per KV head, all its
+ * query heads as rows of mma.sync, f16 probabilities) when there are 1, 2, 4 or 8 query heads per KV head and the
+ * pointers are 16-byte aligned; nve_b200_set_attn_decode_kernel(1) selects the CUDA-core kernel for all of them
+ * (also used for other shapes; it is the arithmetic of the persistent one-kernel step), 0 restores the default.  The
+ * two kernels agree within 5e-3 of the largest output.  The setting is process-wide, a captured graph keeps the
+ * kernel it was recorded with; the previous setting is returned. */
 NVE_API int nve_b200_attn_decode_fused(const uint16_t* q, const uint16_t* k_new, const uint16_t* v_new,
                                        uint16_t* k_cache, uint16_t* v_cache, const uint16_t* cos_tab,
                                        const uint16_t* sin_tab, const int* d_pos, const int* d_seq_len, uint16_t* out,

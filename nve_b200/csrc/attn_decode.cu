@@ -210,6 +210,9 @@ static bool attn_decode_dispatch(const AttnParams& p, int hd, cudaStream_t st, c
     return false;
 }
 
+// 0: tensor-core kernels where they cover the shape (default); 1: always the CUDA-core kernel (nve_b200_set_attn_decode_kernel)
+static std::atomic<int> g_attn_decode_kernel{0};
+
 // Used by the reference-signature flash-decode entry points (attn_glue.cu).
 bool attn_decode_try(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, uint16_t* out, int nh, int nkv, int seq_len,
                      const int* d_seq_len, int kv_stride, int hd, float scale, cudaStream_t st) {
@@ -225,13 +228,13 @@ bool attn_decode_try(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, 
     p.kv_stride = kv_stride;
     p.scale = scale;
     cudaError_t e = cudaSuccess;
-    if (!attn_decode_dispatch<false>(p, hd, st, e)) return false;
+    const bool mma = g_attn_decode_kernel.load(std::memory_order_relaxed) == 0 && aligned(q, 16) && aligned(kc, 16) && aligned(vc, 16) &&
+                     attn_decode_mma_try(p, hd, st, e, false);
+    if (!mma && !attn_decode_dispatch<false>(p, hd, st, e)) return false;
     count_launch();
     set_cuda_status(e);
     return true;
 }
-
-static std::atomic<int> g_attn_decode_kernel{0};
 
 }  // namespace nve
 
@@ -298,6 +301,10 @@ extern "C" int nve_b200_attn_prefill_causal(const uint16_t* q, const uint16_t* k
     p.row_stride = num_heads * head_dim;
     cudaError_t e = cudaSuccess;
     if (static_cast<long long>(rows) * num_kv_heads >= 64 && attn_batch_mma_try(p, head_dim, static_cast<cudaStream_t>(stream), e, false)) {
+        count_launch();
+        return set_cuda_status(e);
+    }
+    if (g_attn_decode_kernel.load(std::memory_order_relaxed) == 0 && attn_decode_mma_try(p, head_dim, static_cast<cudaStream_t>(stream), e, false)) {
         count_launch();
         return set_cuda_status(e);
     }

@@ -59,10 +59,19 @@ template <int HD, int G> struct AdmSmem {
 
 // With `rows` > 1 (batched decode) blockIdx.y selects one of several independent sequences: row b of q / k_new /
 // v_new / out, the b-th K/V cache and the b-th position and length words.
-template <int HD, int G>
+// FUSED = false is the plain flash-decode form (nve_flash_decode_f16 and the rows of a small causal block): q is
+// already rotated, nothing is written to the cache, the length is *d_seq_len or seq_len, and blockIdx.y selects one of
+// `rows` query rows, row r reading q + r * row_stride and attending to seq_len + r positions.
+template <int HD, int G, bool FUSED>
 __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const AttnParams pin) {
     AttnParams p = pin;
-    if (p.rows > 1) {
+    int seq_len_row = p.seq_len;
+    if constexpr (!FUSED) {
+        p.q += static_cast<long long>(blockIdx.y) * p.row_stride;
+        p.out += static_cast<long long>(blockIdx.y) * p.row_stride;
+        seq_len_row += static_cast<int>(blockIdx.y);
+    }
+    if (FUSED && p.rows > 1) {
         const long long b = blockIdx.y;
         p.q += b * (static_cast<long long>(p.num_heads) * HD);
         p.out += b * (static_cast<long long>(p.num_heads) * HD);
@@ -105,8 +114,8 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
 
     // ---- before the wait: this warp's first tile, addressed with the position words as they are now (read again
     // after the wait; the tile is loaded again if they changed)
-    const int pre_seq = max(0, min(*p.d_seq_len, p.kv_stride));
-    const int pre_pos = *p.d_pos;
+    const int pre_seq = max(0, min(p.d_seq_len != nullptr ? *p.d_seq_len : seq_len_row, p.kv_stride));
+    const int pre_pos = FUSED ? *p.d_pos : -1;
     uint4 kr[2][HD / 32], vr[4][HD / 64];
     {
         const int pchunk = (pre_seq + kAdRanks - 1) / kAdRanks;
@@ -120,13 +129,15 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
     constexpr int QI = (G + HPP - 1) / HPP;       // passes
     const int qe = tid % HALF, qh = tid / HALF;
     const bool spec_ok = pre_pos >= 0 && pre_pos < p.kv_stride;
-    uint16_t c16 = p.cos_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
-    uint16_t s16 = p.sin_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
+    uint16_t c16 = 0, s16 = 0;
+    if constexpr (FUSED) {
+        c16 = p.cos_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
+        s16 = p.sin_tab[static_cast<long long>(spec_ok ? pre_pos : 0) * HALF + qe];
+    }
     for (int i = tid; i < (HD / 16) * 32 * 2; i += kAmThreads) reinterpret_cast<uint32_t*>(sh.qf)[i] = 0;
     pdl_wait();
     // one round trip: the position words are read again while q, k and v of the new token come in; everything that
     // was addressed with the guess is redone in the rare case that the words changed
-    const uint16_t* kp = p.k_new + static_cast<long long>(kvh) * HD;
     uint16_t x0[QI], x1[QI];
 #pragma unroll
     for (int j = 0; j < QI; j++) {
@@ -136,17 +147,21 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
         x1[j] = qp[qe + HALF];
     }
     uint16_t k0 = 0, k1 = 0, vv = 0;
-    if (tid < HALF) {  // ... and, for the first HALF threads, of the new k
-        k0 = kp[qe];
-        k1 = kp[qe + HALF];
+    if constexpr (FUSED) {
+        const uint16_t* kp = p.k_new + static_cast<long long>(kvh) * HD;
+        if (tid < HALF) {  // ... and, for the first HALF threads, of the new k
+            k0 = kp[qe];
+            k1 = kp[qe + HALF];
+        }
+        if (tid < HD) vv = p.v_new[static_cast<long long>(kvh) * HD + tid];
     }
-    if (tid < HD) vv = p.v_new[static_cast<long long>(kvh) * HD + tid];
-    int seq_len = *reinterpret_cast<const volatile int*>(p.d_seq_len);
-    const int pos = *reinterpret_cast<const volatile int*>(p.d_pos);
+    int seq_len = p.d_seq_len != nullptr ? *reinterpret_cast<const volatile int*>(p.d_seq_len) : seq_len_row;
+    int pos = -1;
+    if constexpr (FUSED) pos = *reinterpret_cast<const volatile int*>(p.d_pos);
     seq_len = max(0, min(seq_len, p.kv_stride));
-    const bool pos_ok = pos >= 0 && pos < p.kv_stride;
+    const bool pos_ok = FUSED && pos >= 0 && pos < p.kv_stride;
     const bool pre_ok = pre_seq == seq_len && pre_pos == pos;
-    if (pos != pre_pos) {  // uniform over the grid
+    if (FUSED && pos != pre_pos) {  // uniform over the grid
         c16 = p.cos_tab[static_cast<long long>(pos_ok ? pos : 0) * HALF + qe];
         s16 = p.sin_tab[static_cast<long long>(pos_ok ? pos : 0) * HALF + qe];
     }
@@ -163,20 +178,22 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
         for (int j = 0; j < QI; j++) {
             const int h = qh + j * HPP;
             if (h < G) {
-                uint16_t r0, r1;
-                rot(x0[j], x1[j], r0, r1);
+                uint16_t r0 = x0[j], r1 = x1[j];
+                if constexpr (FUSED) rot(x0[j], x1[j], r0, r1);
                 const int d0 = qe, d1 = qe + HALF;  // dim d -> lane quarter t = d / DPT, MMA kk = (d % DPT) / 4, slot d % 4
                 sh.qf[(d0 % DPT) / 4][(d0 / DPT) * 8 + h][d0 % 4] = r0;
                 sh.qf[(d1 % DPT) / 4][(d1 / DPT) * 8 + h][d1 % 4] = r1;
             }
         }
-        if (tid < HALF) rot(k0, k1, sh.knew_s[qe], sh.knew_s[qe + HALF]);
-        if (tid < HD) sh.vnew_s[tid] = vv;
+        if constexpr (FUSED) {
+            if (tid < HALF) rot(k0, k1, sh.knew_s[qe], sh.knew_s[qe + HALF]);
+            if (tid < HD) sh.vnew_s[tid] = vv;
+        }
     }
     __syncthreads();
     pdl_launch_dependents();
     // one CTA per KV head stores the new row; the tiles that cover `pos` take it from shared memory
-    if (pos_ok && rank == 0 && tid < 2 * DC) {
+    if (FUSED && pos_ok && rank == 0 && tid < 2 * DC) {
         const int which = tid / DC, d = tid % DC;
         uint16_t* dst = (which == 0 ? p.k_cache : p.v_cache) + (static_cast<long long>(kvh) * p.kv_stride + pos) * HD;
         reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(which == 0 ? sh.knew_s : sh.vnew_s)[d];
@@ -287,12 +304,12 @@ __global__ void __launch_bounds__(kAmThreads, 1) attn_decode_mma_kernel(const At
     }
 }
 
-template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cudaStream_t st) {
+template <int HD, int G, bool FUSED> static cudaError_t launch_adm_f(const AttnParams& p, cudaStream_t st) {
     constexpr int smem = static_cast<int>(sizeof(AdmSmem<HD, G>));
-    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_mma_kernel<HD, G>), smem) != NVE_OK) return cudaErrorInvalidValue;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_mma_kernel<HD, G, FUSED>), smem) != NVE_OK) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.dynamicSmemBytes = smem;
-    cfg.gridDim = dim3(p.num_kv_heads * kAdCluster, p.rows > 1 ? p.rows : 1);
+    cfg.gridDim = dim3(p.num_kv_heads * kAdCluster, p.rows > 1 ? p.rows : 1);  // fused: sequences; else: query rows
     cfg.blockDim = dim3(kAmThreads);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -307,28 +324,31 @@ template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cuda
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs = 2;
     }
-    return cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, G>, p);
+    return cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, G, FUSED>, p);
+}
+template <int HD, int G> static cudaError_t launch_adm(const AttnParams& p, cudaStream_t st, bool fused) {
+    return fused ? launch_adm_f<HD, G, true>(p, st) : launch_adm_f<HD, G, false>(p, st);
 }
 
 // Fused decode attention of one sequence; false when the shape is not covered (query heads per KV head other than
 // 1, 2, 4 or 8, other head sizes): the caller then uses the CUDA-core kernel.
-bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err) {
+bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err, bool fused) {
     const int groups = p.num_heads / p.num_kv_heads;
     if (head_dim == 128) {
         switch (groups) {
-            case 1: err = launch_adm<128, 1>(p, st); return true;
-            case 2: err = launch_adm<128, 2>(p, st); return true;
-            case 4: err = launch_adm<128, 4>(p, st); return true;
-            case 8: err = launch_adm<128, 8>(p, st); return true;
+            case 1: err = launch_adm<128, 1>(p, st, fused); return true;
+            case 2: err = launch_adm<128, 2>(p, st, fused); return true;
+            case 4: err = launch_adm<128, 4>(p, st, fused); return true;
+            case 8: err = launch_adm<128, 8>(p, st, fused); return true;
             default: return false;
         }
     }
     if (head_dim == 64) {
         switch (groups) {
-            case 1: err = launch_adm<64, 1>(p, st); return true;
-            case 2: err = launch_adm<64, 2>(p, st); return true;
-            case 4: err = launch_adm<64, 4>(p, st); return true;
-            case 8: err = launch_adm<64, 8>(p, st); return true;
+            case 1: err = launch_adm<64, 1>(p, st, fused); return true;
+            case 2: err = launch_adm<64, 2>(p, st, fused); return true;
+            case 4: err = launch_adm<64, 4>(p, st, fused); return true;
+            case 8: err = launch_adm<64, 8>(p, st, fused); return true;
             default: return false;
         }
     }

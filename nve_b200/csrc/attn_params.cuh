@@ -33,6 +33,6 @@ bool attn_batch_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cuda
 
 // attn_decode_mma.cu: the fused decode attention of one sequence on the tensor cores; false when the shape is not
 // covered.
-bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err);
+bool attn_decode_mma_try(const AttnParams& p, int head_dim, cudaStream_t st, cudaError_t& err, bool fused = true);
 
 }  // namespace nve
