@@ -492,9 +492,10 @@ def batched_decode_entries(torch, ck, state, shape, batches=(8, 16, 32, 64)):
         last = {}
 
         def rec(_a, _b):
-            h = x
-            for li in range(layers):
-                h = gpu_layer_forward_decode_batch(h, li, state, kv, d_pos, d_len, scratch)
+            h, res = x, None
+            for li in range(layers):  # the add at the end of a layer rides on the next layer's first launch
+                r = gpu_layer_forward_decode_batch(h, li, state, kv, d_pos, d_len, scratch, residual=res, defer_add=li < layers - 1)
+                h, res = r if li < layers - 1 else (r, None)
             last["h"] = h
 
         us, launches = time_sequence(torch, rec, reps=5)

@@ -225,6 +225,12 @@ NVE_API int nve_b200_silu_mul(void* gate, const void* up, int n, int dtype, nve_
  *   aligned. */
 NVE_API int nve_b200_rms_norm_rows(const void* x, const void* weight, void* out, int rows, int n, float eps, int dtype,
                                    nve_stream_t stream);
+/* x[r] += delta[r] in place (nve_b200_add_inplace's arithmetic) and out[r] = RMSNorm(x[r]) for every row, one launch:
+ * the residual add and the norm between two projections of a batched layer (src/gpu_layer.rs:1139-1147 runs them as
+ * separate kernels per token).  Bit-identical to nve_b200_add_inplace followed by nve_b200_rms_norm_rows.  n % 8 == 0,
+ * 16-byte aligned pointers. */
+NVE_API int nve_b200_add_rms_norm_rows(void* x, const void* delta, const void* weight, void* out, int rows, int n,
+                                       float eps, int dtype, nve_stream_t stream);
 NVE_API int nve_b200_kv_cache_write_rows(const uint16_t* k_new, uint16_t* k_cache, const uint16_t* v_new,
                                          uint16_t* v_cache, int rows, int start_pos, int num_kv_heads, int head_dim,
                                          int max_seq_len, nve_stream_t stream);

@@ -135,6 +135,7 @@ SIGNATURES = {
     "nve_b200_rmsnorm_gateup_silu_w4a8": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
     "nve_b200_rmsnorm_gateup_silu_w4a16": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P]),
     "nve_b200_rms_norm_rows": (_I, [_P, _P, _P, _I, _I, _F, _I, _P]),
+    "nve_b200_add_rms_norm_rows": (_I, [_P, _P, _P, _P, _I, _I, _F, _I, _P]),
     "nve_b200_kv_cache_write_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "nve_b200_attn_prefill_causal": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "nve_b200_rmsnorm_gateup_silu_q8_w4a8": (_I, [_P, _P, _F, _I, _P, C.POINTER(W4Matrix), C.POINTER(W4Matrix), _P, _I, _P, _P, _P, _P]),

@@ -134,6 +134,40 @@ __global__ void __launch_bounds__(kActThreads) rmsnorm_kernel(const uint16_t* x,
     }
 }
 
+// x[row] += delta[row] (the residual add, stored in place with add_inplace_kernel's arithmetic) followed by the RMSNorm
+// of the updated row into out: one launch for the pair of launches between two projections of a batched layer.  The
+// CTA reads back what it stored (ordered by the CTA barrier), so the bits are those of the two separate kernels.
+template <int DT> __global__ void __launch_bounds__(kActThreads) add_rmsnorm_rows_kernel(uint16_t* x, const uint16_t* delta,
+                                                                                         const uint16_t* w, uint16_t* out, int n,
+                                                                                         float eps) {
+    x += static_cast<long long>(blockIdx.x) * n;
+    delta += static_cast<long long>(blockIdx.x) * n;
+    out += static_cast<long long>(blockIdx.x) * n;
+    pdl_wait();
+    const int chunks = n / 8;
+    for (int c = threadIdx.x; c < chunks; c += kActThreads) {
+        uint16_t hd[8], hs[8];
+        load_chunk<true>(x, c, n, hd);
+        load_chunk<true>(delta, c, n, hs);
+#pragma unroll
+        for (int e = 0; e < 8; e++) hd[e] = Act16<DT>::from_f32(__fadd_rn(Act16<DT>::to_f32(hd[e]), Act16<DT>::to_f32(hs[e])));
+        store_chunk<true>(x, c, n, hd);
+    }
+    __syncthreads();
+    const float total = sum_squares<DT, true>(x, n);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(n)), eps)));
+    pdl_launch_dependents();
+    for (int c = threadIdx.x; c < chunks; c += kActThreads) {
+        uint16_t hx[8], hw[8], ho[8];
+        load_chunk<true>(x, c, n, hx);
+        load_chunk<true>(w, c, n, hw);
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            ho[e] = Act16<DT>::from_f32(__fmul_rn(__fmul_rn(Act16<DT>::to_f32(hx[e]), r), Act16<DT>::to_f32(hw[e])));
+        store_chunk<true>(out, c, n, ho);
+    }
+}
+
 // QUANT: 0 = 16-bit output only, 1 = + int8 codes (W4A8 route), 2 = + 16-bit fixed-point planes (W4A16 route; `awq`,
 // if given, multiplies each element first, as the W4A16 GEMV's own staging does).
 template <int DT, int QUANT>
@@ -355,6 +389,27 @@ extern "C" int nve_b200_rms_norm_rows(const void* x, const void* weight, void* o
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return NVE_DISPATCH_16(dtype, (rmsnorm_impl<NVE_DT_F16, false>(x, weight, out, nullptr, nullptr, n, eps, st, rows)),
                            (rmsnorm_impl<NVE_DT_BF16, false>(x, weight, out, nullptr, nullptr, n, eps, st, rows)));
+}
+
+template <int DT> static int add_rmsnorm_rows_impl(void* x, const void* delta, const void* weight, void* out, int rows, int n, float eps,
+                                                   cudaStream_t st) {
+    if (!x || !delta || !weight || !out) return set_status(NVE_ERR_BAD_POINTER);
+    if (rows <= 0 || rows > 65535 || n <= 0 || (n % 8) != 0) return set_status(NVE_ERR_BAD_SHAPE);
+    if (!aligned(x, 16) || !aligned(delta, 16) || !aligned(weight, 16) || !aligned(out, 16)) return set_status(NVE_ERR_BAD_ALIGNMENT);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    launch_cfg(cfg, attr, rows, st);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, add_rmsnorm_rows_kernel<DT>, static_cast<uint16_t*>(x), static_cast<const uint16_t*>(delta),
+                                       static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(out), n, eps);
+    count_launch();
+    return set_cuda_status(e);
+}
+
+extern "C" int nve_b200_add_rms_norm_rows(void* x, const void* delta, const void* weight, void* out, int rows, int n, float eps,
+                                          int dtype, nve_stream_t stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return NVE_DISPATCH_16(dtype, (add_rmsnorm_rows_impl<NVE_DT_F16>(x, delta, weight, out, rows, n, eps, st)),
+                           (add_rmsnorm_rows_impl<NVE_DT_BF16>(x, delta, weight, out, rows, n, eps, st)));
 }
 
 extern "C" void nve_rms_norm_f16(const uint16_t* x, const uint16_t* weight, uint16_t* out, int n, float eps,

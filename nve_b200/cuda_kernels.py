@@ -131,6 +131,19 @@ def rms_norm_rows(x: Tensor, weight: Tensor, eps: float, out: Optional[Tensor] =
     return out
 
 
+def add_rms_norm_rows(x: Tensor, delta: Tensor, weight: Tensor, eps: float, out: Optional[Tensor] = None) -> Tensor:
+    """x += delta in place, then RMSNorm of every row of x into `out` (returned): add_inplace_any + rms_norm_rows in one
+    launch, same bits."""
+    if x.dim() != 2 or delta.shape != x.shape:
+        raise ValueError("x and delta must be [rows, n]")
+    out = torch.empty_like(x) if out is None else out
+    _ffi.check("nve_b200_add_rms_norm_rows",
+               _lib().nve_b200_add_rms_norm_rows(_ptr(x, (torch.float16, torch.bfloat16), "x"), _ptr(delta, x.dtype),
+                                                 _ptr(weight, x.dtype), _ptr(out, x.dtype), x.shape[0], x.shape[1], float(eps),
+                                                 _dt(x), stream()))
+    return out
+
+
 def kv_cache_write_rows(k_new: Tensor, k_cache: Tensor, v_new: Tensor, v_cache: Tensor, start_pos: int, num_kv_heads: int,
                         head_dim: int, max_seq_len: int) -> None:
     """cache[kvh, start_pos + s, :] = new[s, kvh, :] for the rows of k_new / v_new [S, nkv, hd]."""

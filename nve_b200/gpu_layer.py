@@ -501,7 +501,8 @@ class BatchedDecodeScratch:
 
 
 def gpu_layer_forward_decode_batch(hidden: Tensor, layer_idx: int, state: GpuInferenceState, kv: BatchedKvCache,
-                                   d_pos: Tensor, d_seqlen: Tensor, scratch: Optional[BatchedDecodeScratch] = None) -> Tensor:
+                                   d_pos: Tensor, d_seqlen: Tensor, scratch: Optional[BatchedDecodeScratch] = None,
+                                   residual: Optional[Tensor] = None, defer_add: bool = False):
     """One decode step of B independent sequences through one layer: hidden [B, hidden] f16 -> same shape.  Row b is the
     next token of sequence b at position d_pos[b] (int32 device tensors [B]); kv holds the sequences' caches.
 
@@ -509,7 +510,12 @@ def gpu_layer_forward_decode_batch(hidden: Tensor, layer_idx: int, state: GpuInf
     each), RoPE + K/V write + attention of all sequences is one launch of the fused decode kernel, RMSNorm one launch
     over the rows.  16-bit activations on every layer, as in prefill.  Row b equals the single-sequence decode of that
     sequence within the tolerance that separates the tensor-core GEMM from the integer GEMV.  With `scratch` nothing is
-    allocated and the result is one of scratch.out (alternating with the layer index)."""
+    allocated and the result is one of scratch.out (alternating with the layer index).
+
+    The residual adds ride on the RMSNorm launches (add_rms_norm_rows, same bits as the separate kernels).  For the
+    add at the end of a layer that needs the next layer's norm: with defer_add the layer returns (out, h1) without
+    adding, and the next layer is called with hidden = out, residual = h1 and adds them (in place, into `hidden`)
+    inside its first launch."""
     if hidden.dim() != 2 or hidden.shape[0] != kv.batch:
         raise ValueError("hidden must be [batch, hidden] with the cache's batch")
     w = state.layer_weights[layer_idx]
@@ -517,15 +523,19 @@ def gpu_layer_forward_decode_batch(hidden: Tensor, layer_idx: int, state: GpuInf
     eps, scale = state.norm_eps, float(hd) ** -0.5
     s = scratch
     ws = None if s is None else s.gemm
-    normed = ck.rms_norm_rows(hidden, w.input_norm, eps, out=None if s is None else s.normed)
+    if residual is not None:
+        normed = ck.add_rms_norm_rows(hidden, residual, w.input_norm, eps, out=None if s is None else s.normed)
+    else:
+        normed = ck.rms_norm_rows(hidden, w.input_norm, eps, out=None if s is None else s.normed)
     q, k, v = matmul_x_multi(normed, [w.q_proj, w.k_proj, w.v_proj], ws, None if s is None else [s.q, s.k, s.v])
     attn = ck.attn_decode_fused_batch(q, k, v, kv.k[layer_idx], kv.v[layer_idx], state.rope_cos, state.rope_sin, d_pos,
                                       d_seqlen, nh, nkv, hd, kv.max_seq, scale, out=None if s is None else s.attn)
     h1 = matmul_x(attn, w.o_proj, ws, None if s is None else s.h1)
-    ck.add_inplace_any(h1, hidden)
-    normed2 = ck.rms_norm_rows(h1, w.post_attn_norm, eps, out=None if s is None else s.normed)
+    normed2 = ck.add_rms_norm_rows(h1, hidden, w.post_attn_norm, eps, out=None if s is None else s.normed)
     gate, up = matmul_x_multi(normed2, [w.gate_proj, w.up_proj], ws, None if s is None else [s.gate, s.up])
     ck.silu_mul_inplace(gate, up)
     out = matmul_x(gate, w.down_proj, ws, None if s is None else s.out[layer_idx & 1])
+    if defer_add:
+        return out, h1
     ck.add_inplace_any(out, h1)
     return out

@@ -658,6 +658,7 @@ def test_attn_decode_fused_batch_rows_equal_single_calls(cuda, orc, cuda_core):
 def test_batched_decode_layers_match_single_sequence_decode(cuda, orc):
     """gpu_layer_forward_decode_batch on B sequences at different positions against B single-sequence decode steps
     (16-bit route) through the same two layers."""
+    from nve_b200 import cuda_kernels as ck
     from nve_b200.gpu_layer import BatchedKvCache, gpu_layer_forward_decode, gpu_layer_forward_decode_batch
 
     torch = cuda
@@ -698,6 +699,23 @@ def test_batched_decode_layers_match_single_sequence_decode(cuda, orc):
         hb = gpu_layer_forward_decode_batch(hb, li, st, kvb, d_pos, d_len)
     torch.cuda.synchronize()
     assert torch.equal(hb, hb2)
+    # the residual add at the end of a layer deferred into the next layer's first launch: same bits
+    kvb3 = BatchedKvCache([t.clone() for t in kvb2.k], [t.clone() for t in kvb2.v], B, max_seq)
+    hb3, res = x, None
+    for li in range(layers):
+        r = gpu_layer_forward_decode_batch(hb3, li, st, kvb3, d_pos, d_len, scratch, residual=res, defer_add=li < layers - 1)
+        hb3, res = r if li < layers - 1 else (r, None)
+    torch.cuda.synchronize()
+    assert torch.equal(hb3, hb)
+    # the fused add + RMSNorm launch against the two kernels
+    xa = dev(orc.to_act16(orc.fill_normal(B * hidden, 861, 1)), torch.float16).view(B, hidden)
+    da = dev(orc.to_act16(orc.fill_normal(B * hidden, 861, 2)), torch.float16).view(B, hidden)
+    wn = dev(orc.to_act16(1.0 + 0.1 * orc.fill_normal(hidden, 861, 3)), torch.float16)
+    x1, x2 = xa.clone(), xa.clone()
+    n1 = ck.add_rms_norm_rows(x1, da, wn, 1e-5)
+    ck.add_inplace_any(x2, da)
+    n2 = ck.rms_norm_rows(x2, wn, 1e-5)
+    assert torch.equal(x1, x2) and torch.equal(n1, n2)
     assert rel_rms_err(hb.float().cpu().numpy(), want.float().cpu().numpy()) < 5e-3
     for b in range(B):
         for li in range(layers):
