@@ -111,8 +111,8 @@ extern "C" {
                                             stream: Stream) -> i32;
     pub fn nve_b200_rms_norm_rows(x: *const CVoid, weight: *const CVoid, out: *mut CVoid, rows: i32, n: i32, eps: f32,
                                   dtype: i32, stream: Stream) -> i32;
-    pub fn nve_b200_add_rms_norm_rows(x: *mut c_void, delta: *const c_void, weight: *const c_void, out: *mut c_void, rows: i32,
-                                      n: i32, eps: f32, dtype: i32, stream: *mut c_void) -> i32;
+    pub fn nve_b200_add_rms_norm_rows(x: *mut CVoid, delta: *const CVoid, weight: *const CVoid, out: *mut CVoid, rows: i32,
+                                      n: i32, eps: f32, dtype: i32, stream: Stream) -> i32;
     pub fn nve_b200_kv_cache_write_rows(k_new: *const u16, k_cache: *mut u16, v_new: *const u16, v_cache: *mut u16,
                                         rows: i32, start_pos: i32, num_kv_heads: i32, head_dim: i32, max_seq_len: i32,
                                         stream: Stream) -> i32;
