@@ -1,5 +1,8 @@
-// Decode attention of ONE sequence on the tensor cores: RoPE + K/V write + single-query GQA attention + optional
-// int8 quantisation of the output, the fused step between the q/k/v GEMV and o_proj of a decode layer.
+// Decode attention on the tensor cores, one cluster per KV head: RoPE + K/V write + single-query GQA attention +
+// optional int8 quantisation of the output, the fused step between the q/k/v GEMV and o_proj of a decode layer
+// (FUSED); the plain flash-decode form of the same arithmetic (nve_flash_decode_f16, the rows of a small causal
+// block), so that the fused launch equals the un-fused launch sequence bit for bit; and a few independent sequences
+// in one launch (batched decode).
 //
 // Same interface and the same place in the step as the clustered CUDA-core kernel (attn_decode.cu), which spends
 // most of its time on dot products with shuffle reductions (about 1200 instructions per thread for 1024 positions).
