@@ -447,8 +447,7 @@ def gpu_layer_forward_prefill(hidden: Tensor, layer_idx: int, state: GpuInferenc
     ck.kv_cache_write_rows(k.view(S, nkv, hd), kc, v.view(S, nkv, hd), vc, start_pos, nkv, hd, max_seq)
     attn = ck.attn_prefill_causal(q, kc, vc, start_pos, nh, nkv, hd, max_seq, scale)
     h1 = matmul_x(attn, w.o_proj)
-    ck.add_inplace_any(h1, hidden)
-    normed2 = ck.rms_norm_rows(h1, w.post_attn_norm, eps)
+    normed2 = ck.add_rms_norm_rows(h1, hidden, w.post_attn_norm, eps)  # residual add + norm in one launch
     gate, up = matmul_x_multi(normed2, [w.gate_proj, w.up_proj])
     ck.silu_mul_inplace(gate, up)
     out = matmul_x(gate, w.down_proj)
